@@ -1,0 +1,116 @@
+// Shared helpers of the kernel files: element types, error reporting,
+// warp/block reductions.  Every kernel file is built into a shared library
+// of its own with plain `extern "C"` launchers (no Python or torch headers),
+// which the Python side loads with ctypes.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdarg.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#define MLXB_EXPORT extern "C" __attribute__((visibility("default")))
+
+// dtype codes shared with mlx_lm_b200/ops (0 = float32, 1 = bfloat16)
+enum { MLXB_F32 = 0, MLXB_BF16 = 1 };
+
+// error codes beyond cudaError_t (returned negative)
+enum {
+  MLXB_OK = 0,
+  MLXB_BAD_ARG = -1,       // a size or option the kernel refuses
+  MLXB_BAD_DTYPE = -2,
+};
+
+// status word bits that kernels set instead of faulting on bad indices
+enum {
+  MLXB_ST_TOKEN_RANGE = 1,     // token id outside the vocabulary
+  MLXB_ST_POSITION_RANGE = 2,  // position outside the table / block table
+  MLXB_ST_PAGE_RANGE = 4,      // page id outside the pool
+  MLXB_ST_WAIT_TIMEOUT = 8,    // a bounded spin-wait gave up
+};
+
+static thread_local char g_mlxb_err[512];
+
+static inline int mlxb_fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_mlxb_err, sizeof(g_mlxb_err), fmt, ap);
+  va_end(ap);
+  return code;
+}
+
+static inline int mlxb_check_launch(const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) {
+    snprintf(g_mlxb_err, sizeof(g_mlxb_err), "%s: %s", what, cudaGetErrorString(e));
+    return (int)e;
+  }
+  return 0;
+}
+
+#define MLXB_DEFINE_LAST_ERROR()                                   \
+  MLXB_EXPORT const char* mlxb_last_error() { return g_mlxb_err; }
+
+template <typename T>
+__device__ __forceinline__ float to_f(T v);
+template <>
+__device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f(float v);
+template <>
+__device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Block-wide sum; every thread gets the result.  `red` is shared memory of at
+// least 33 floats.  The order of additions is fixed by the block size alone.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) red[wid] = v;
+  __syncthreads();
+  if (wid == 0) {
+    float t = lane < nw ? red[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+  v = warp_max(v);
+  __syncthreads();
+  if (lane == 0) red[wid] = v;
+  __syncthreads();
+  if (wid == 0) {
+    float t = lane < nw ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    if (lane == 0) red[32] = t;
+  }
+  __syncthreads();
+  return red[32];
+}
+
+// gelu_new: 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))
+__device__ __forceinline__ float gelu_new_f(float x) {
+  const float k0 = 0.7978845608028654f, k1 = 0.044715f;
+  return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
+}

@@ -1,0 +1,276 @@
+"""The step function: one batch of (request, its next tokens) through the
+model, from the cache, returning logits at the wanted places.
+
+mlx-lm runs prompt processing and decoding as two rectangular model calls
+(``PromptProcessingBatch.prompt`` on right-padded ``[B, L]`` slices and
+``GenerationBatch._step`` on ``[B, 1]``: mlx_lm/generate.py:1208-1254,
+1402-1460).  Here a step is one flat list of tokens: every entry brings the
+next ``n >= 1`` tokens of one request — a portion of a prompt cut anywhere,
+or a single decoded token — and they all run as one batch.  Each token knows
+its request and its position; keys and values are appended to the request's
+pages and attention reads them back through the block table, so a step runs
+only the tokens it is given.
+
+All integer inputs of a step (tokens, positions, request of each token, rows
+whose logits are wanted, block tables, slots, per-request offsets) are packed
+into one pinned host buffer and reach the device in one copy.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..cache import CacheManager
+from ..ops import build as kernel_build
+from ..parts.model import Model, RunEntry
+
+
+@dataclass
+class StepEntry:
+    rid: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = ()      # indices into ``tokens`` whose logits are asked for
+
+
+class Workspace:
+    """Activation buffers by name, kept between steps and grown on demand."""
+
+    def __init__(self, device):
+        self.device = device
+        self._bufs: Dict[tuple, torch.Tensor] = {}
+
+    def get(self, tag: str, rows: int, cols: int, dtype: torch.dtype) -> torch.Tensor:
+        key = (tag, cols, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.shape[0] < rows:
+            cap = max(rows, 16)
+            if buf is not None:
+                cap = max(cap, 2 * buf.shape[0])
+            buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
+            self._bufs[key] = buf
+        return buf[:rows]
+
+    def nbytes(self) -> int:
+        return sum(b.numel() * b.element_size() for b in self._bufs.values())
+
+
+@dataclass
+class LayerCacheView:
+    """What one run of a block sees of its cache in this step."""
+    kind: str                      # "kv", "state" or "none"
+    write: bool = True
+    k: Optional[torch.Tensor] = None             # [n_pages, heads, page, head_dim]
+    v: Optional[torch.Tensor] = None
+    block_table: Optional[torch.Tensor] = None   # int32 [R, table_width] on the device
+    page_size: int = 0
+    state: Optional[torch.Tensor] = None         # [n_slots, *shape] float32
+    slots: Optional[torch.Tensor] = None         # int32 [R] on the device
+
+
+@dataclass
+class RequestSpan:
+    """One entry of the step as parts with sequential state need it (host side)."""
+    rid: Hashable
+    slot: int
+    first_token: int     # row of the entry's first token among the step's tokens
+    n_tokens: int
+    first_position: int
+
+
+class StepContext:
+    """Everything a part may read while a step runs."""
+
+    def __init__(self, engine: "Engine"):
+        self.engine = engine
+        self.ws = engine.ws
+        self.dtype, self.device = engine.model.dtype, engine.model.device
+        self.status = engine.status
+        self.stream = 0
+        self.n_tokens = 0
+        self.n_requests = 0
+        self.n_logit_rows = 0
+        self.tokens = self.positions = self.token_req = self.logit_rows = None
+        self.req_first_token = self.req_first_position = None
+        self.spans: List[RequestSpan] = []
+        self.max_q_len = 0
+        self._tables: List[torch.Tensor] = []
+        self._slots: Optional[torch.Tensor] = None
+
+    def cache_view(self, entry: RunEntry) -> LayerCacheView:
+        mgr = self.engine.cache
+        if entry.cache_id not in mgr._where:
+            return LayerCacheView("none", write=False)
+        kind, gi = mgr.where(entry.cache_id)
+        if kind == "kv":
+            g = mgr.kv_groups[gi]
+            i = g.index_of(entry.cache_id)
+            return LayerCacheView("kv", entry.write, k=g.k[i], v=g.v[i], block_table=self._tables[gi],
+                                  page_size=mgr.page_size)
+        g = mgr.state_groups[gi]
+        return LayerCacheView("state", entry.write, state=g.data[g.index_of(entry.cache_id)], slots=self._slots)
+
+    def gather_rows(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError("a model without a final norm needs a row-gather kernel")
+
+
+class Engine:
+    """A model, its cache and the step function."""
+
+    def __init__(self, model: Model, page_size: int = 16, max_tokens: Optional[int] = None,
+                 n_pages: Optional[int] = None, max_requests: int = 64, max_len: Optional[int] = None):
+        ops.require_cuda()
+        self.model = model
+        d = model.description
+        limit = d.max_positions
+        self.max_len = min(x for x in (max_len, limit, 1 << 20) if x is not None)
+        if n_pages is None:
+            if max_tokens is None:
+                max_tokens = max_requests * self.max_len
+            n_pages = (max_tokens + page_size - 1) // page_size
+        kernel_build.ensure_built(d.kernel_libs())
+        self.cache = CacheManager(d.cache_specs(), page_size=page_size, n_pages=n_pages, max_requests=max_requests,
+                                  max_len=self.max_len, dtype=model.dtype, device=model.device)
+        self.ws = Workspace(model.device)
+        self.status = torch.zeros(1, dtype=torch.int32, device=model.device)
+        self._host = [None, None]
+        self._host_events = [None, None]
+        self._dev: Optional[torch.Tensor] = None
+        self._flip = 0
+        self.n_steps = 0
+        self.n_kernel_launches = 0
+
+    # ------------------------------------------------------------------ requests
+    def add_request(self, rid: Hashable) -> None:
+        self.cache.add_request(rid)
+
+    def finish(self, rid: Hashable) -> None:
+        self.cache.release(rid)
+
+    def has_request(self, rid: Hashable) -> bool:
+        return rid in self.cache.requests
+
+    # ------------------------------------------------------------------ the step
+    def _int_buffers(self, n: int):
+        i = self._flip
+        self._flip ^= 1
+        if self._host[i] is None or self._host[i].numel() < n:
+            cap = max(4096, 2 * n)
+            self._host[i] = torch.empty(cap, dtype=torch.int32).pin_memory()
+            self._host_events[i] = None
+        if self._dev is None or self._dev.numel() < n:
+            self._dev = torch.empty(max(4096, 2 * n), dtype=torch.int32, device=self.model.device)
+        if self._host_events[i] is not None:
+            self._host_events[i].synchronize()
+        return i, self._host[i], self._dev
+
+    def _upload(self, i: int, n: int) -> None:
+        self._dev[:n].copy_(self._host[i][:n], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._host_events[i] = ev   # the pinned buffer may be rewritten once this has passed
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the entries' tokens as one batch.  Returns float32 logits ``[n_wanted, vocab]`` on the
+        device in the order of the entries and of their ``want`` lists (None if nothing is wanted)."""
+        if not entries:
+            return None
+        mgr = self.cache
+        vocab = self.model.vocab_size
+        seen = set()
+        for e in entries:
+            if e.rid in seen:
+                raise ValueError(f"request {e.rid!r} appears twice in one step")
+            seen.add(e.rid)
+            if e.rid not in mgr.requests:
+                raise KeyError(f"request {e.rid!r} is not live")
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.rid!r}: an entry needs at least one token")
+            if min(e.tokens) < 0 or max(e.tokens) >= vocab:
+                raise ValueError(f"request {e.rid!r}: token id outside 0..{vocab - 1}")
+            if any(not 0 <= w < n for w in e.want):
+                raise ValueError(f"request {e.rid!r}: wanted place outside its {n} tokens")
+            if mgr.length(e.rid) + n > self.max_len:
+                raise ValueError(f"request {e.rid!r}: position {mgr.length(e.rid) + n - 1} is beyond the model's "
+                                 f"{self.max_len} positions")
+        if not mgr.can_reserve([(e.rid, len(e.tokens)) for e in entries]):
+            from ..cache import OutOfPages
+            raise OutOfPages(f"this step needs more pages than are free {mgr.pages_free()}")
+
+        ctx = StepContext(self)
+        R = len(entries)
+        T = sum(len(e.tokens) for e in entries)
+        L = sum(len(e.want) for e in entries)
+        W = mgr.table_width
+        pad = lambda n: (n + 3) & ~3
+        off, sizes = {}, [("tokens", T), ("positions", T), ("token_req", T), ("logit_rows", L), ("slots", R),
+                          ("req_first_token", R + 1), ("req_first_position", R)]
+        sizes += [(f"table{g}", R * W) for g in range(len(mgr.kv_groups))]
+        total = 0
+        for name, n in sizes:
+            off[name] = total
+            total += pad(max(n, 1))
+        hi, host, dev = self._int_buffers(total)
+        h = host.numpy()
+        t0 = 0
+        rows: List[int] = []
+        for r, e in enumerate(entries):
+            n = len(e.tokens)
+            start = mgr.reserve(e.rid, n)
+            slot = mgr.requests[e.rid].slot
+            h[off["tokens"] + t0: off["tokens"] + t0 + n] = e.tokens
+            h[off["positions"] + t0: off["positions"] + t0 + n] = np.arange(start, start + n, dtype=np.int32)
+            h[off["token_req"] + t0: off["token_req"] + t0 + n] = r
+            h[off["slots"] + r] = slot
+            h[off["req_first_token"] + r] = t0
+            h[off["req_first_position"] + r] = start
+            rows.extend(t0 + w for w in e.want)
+            ctx.spans.append(RequestSpan(e.rid, slot, t0, n, start))
+            ctx.max_q_len = max(ctx.max_q_len, n)
+            t0 += n
+        h[off["req_first_token"] + R] = T
+        if L:
+            h[off["logit_rows"]: off["logit_rows"] + L] = rows
+        rids = [e.rid for e in entries]
+        for g in range(len(mgr.kv_groups)):
+            o = off[f"table{g}"]
+            mgr.block_table(g, rids, out=h[o: o + R * W].reshape(R, W))
+        self._upload(hi, total)
+
+        view = lambda name, n: dev[off[name]: off[name] + n]
+        ctx.stream = ops.current_stream()
+        ctx.n_tokens, ctx.n_requests, ctx.n_logit_rows = T, R, L
+        ctx.tokens, ctx.positions, ctx.token_req = view("tokens", T), view("positions", T), view("token_req", T)
+        ctx.logit_rows = view("logit_rows", L)
+        ctx.req_first_token, ctx.req_first_position = view("req_first_token", R + 1), view("req_first_position", R)
+        ctx._slots = view("slots", R)
+        ctx._tables = [view(f"table{g}", R * W).view(R, W) for g in range(len(mgr.kv_groups))]
+        try:
+            logits = self.model.run(ctx)
+        finally:
+            for e in entries:
+                mgr.commit(e.rid)
+        self.n_steps += 1
+        return logits
+
+    def read_status(self) -> int:
+        """Bits kernels set instead of faulting (token, position or page id out of range).
+        Reading synchronises with the device and clears the word."""
+        s = int(self.status.item())
+        if s:
+            self.status.zero_()
+        return s
+
+    def check_status(self) -> None:
+        s = self.read_status()
+        if s:
+            names = [n for b, n in ((ops.ST_TOKEN_RANGE, "token id out of range"),
+                                    (ops.ST_POSITION_RANGE, "position without a page or out of range"),
+                                    (ops.ST_PAGE_RANGE, "page id outside the pool"),
+                                    (ops.ST_WAIT_TIMEOUT, "a bounded wait in a kernel gave up")) if s & b]
+            raise ops.KernelError("a kernel reported: " + "; ".join(names))

@@ -1,0 +1,221 @@
+"""Python face of the CUDA kernels.
+
+Each function checks what the kernel cannot check for itself (device, dtype,
+contiguity, matching sizes), passes raw pointers and the CUDA stream to the
+``extern "C"`` launcher of the kernel's library and raises on a non-zero
+return code with the launcher's own message.  There is no fallback: without
+a CUDA device, or if a library cannot be built, these functions raise.
+
+Tensors are torch tensors used as typed device buffers; no torch operator
+runs in here.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_void_p
+from typing import Optional
+
+import torch
+
+from . import build
+
+F32, BF16 = 0, 1
+EPI_NONE, EPI_GELU_NEW = 0, 1
+
+_DT = {torch.float32: F32, torch.bfloat16: BF16}
+
+# status word bits set by kernels (csrc/common.cuh)
+ST_TOKEN_RANGE, ST_POSITION_RANGE, ST_PAGE_RANGE, ST_WAIT_TIMEOUT = 1, 2, 4, 8
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def require_cuda() -> None:
+    if not torch.cuda.is_available():
+        raise KernelError(
+            "mlx_lm_b200 runs on a CUDA device (NVIDIA B200, sm_100a) only: no device is visible and "
+            "there is no CPU path")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    try:
+        return _DT[dt]
+    except KeyError:
+        raise KernelError(f"unsupported dtype {dt}: the engine runs in float32 or bfloat16") from None
+
+
+def current_stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _p(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, dt, what: str) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{what}: tensor is on {t.device}, not on a CUDA device")
+    if dt is not None and t.dtype != dt:
+        raise KernelError(f"{what}: dtype {t.dtype}, expected {dt}")
+
+
+def _rows(t: torch.Tensor, what: str) -> int:
+    """Row stride of a 2-D tensor whose rows are contiguous."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{what}: expected a 2-D tensor with contiguous rows, got shape {tuple(t.shape)} "
+                          f"strides {t.stride()}")
+    return t.stride(0)
+
+
+_fn_cache = {}
+
+
+def _fn(libname: str, fname: str, argtypes):
+    key = (libname, fname)
+    hit = _fn_cache.get(key)
+    if hit is None:
+        lib = build.load(libname)
+        f = getattr(lib, fname)
+        f.argtypes = argtypes
+        f.restype = c_int
+        hit = _fn_cache[key] = (f, lib)
+    return hit
+
+
+def _call(libname: str, fname: str, argtypes, *args) -> None:
+    f, lib = _fn(libname, fname, argtypes)
+    rc = f(*args)
+    if rc != 0:
+        msg = lib.mlxb_last_error()
+        raise KernelError(f"{fname} failed ({rc}): {msg.decode() if msg else ''}")
+
+
+# --------------------------------------------------------------------------
+# embedding + position add
+
+_EMBED_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
+               c_void_p, c_void_p]
+
+
+def embed_pos(tokens, positions, wte, wpe, out, status, stream, scale: float = 1.0) -> None:
+    """``out[t] = wte[tokens[t]] * scale + wpe[positions[t]]`` (``wpe`` may be None)."""
+    _need(tokens, torch.int32, "embed_pos tokens")
+    _need(wte, out.dtype, "embed_pos wte")
+    T, D = out.shape
+    if wte.shape[1] != D or not wte.is_contiguous() or not out.is_contiguous():
+        raise KernelError(f"embed_pos: table {tuple(wte.shape)} against output {tuple(out.shape)}")
+    if wpe is not None:
+        _need(positions, torch.int32, "embed_pos positions")
+        _need(wpe, out.dtype, "embed_pos wpe")
+        if wpe.shape[1] != D or not wpe.is_contiguous():
+            raise KernelError(f"embed_pos: position table {tuple(wpe.shape)} against width {D}")
+    _call("embed", "mlxb_embed_pos", _EMBED_ARGS, dtype_code(out.dtype), _p(tokens), _p(positions), _p(wte),
+          _p(wpe), _p(out), T, D, wte.shape[0], 0 if wpe is None else wpe.shape[0], scale, _p(status), stream)
+
+
+# --------------------------------------------------------------------------
+# norms
+
+_LN_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p]
+
+
+def layernorm(x, gain, bias, out, eps: float, stream, rows=None) -> None:
+    """``out[r] = LayerNorm(x[rows[r]] if rows is given else x[r])``; statistics in float32."""
+    _need(x, out.dtype, "layernorm x")
+    _need(gain, torch.float32, "layernorm gain")
+    if bias is not None:
+        _need(bias, torch.float32, "layernorm bias")
+    R, D = out.shape
+    if x.shape[1] != D or gain.numel() != D or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError(f"layernorm: x {tuple(x.shape)}, gain {tuple(gain.shape)}, out {tuple(out.shape)}")
+    if rows is not None:
+        _need(rows, torch.int32, "layernorm rows")
+        if rows.numel() != R:
+            raise KernelError(f"layernorm: {rows.numel()} row indices for {R} output rows")
+    elif x.shape[0] != R:
+        raise KernelError(f"layernorm: {x.shape[0]} input rows for {R} output rows")
+    _call("norm", "mlxb_layernorm", _LN_ARGS, dtype_code(out.dtype), _p(x), _p(rows), _p(gain), _p(bias), _p(out),
+          R, D, eps, stream)
+
+
+# --------------------------------------------------------------------------
+# linear layers
+
+_SIMT_ARGS = [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+              c_int, c_void_p]
+
+
+def linear_generic(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=None) -> None:
+    """``out = epilogue(x @ w.T + bias) + residual`` on the CUDA cores in float32 arithmetic.
+
+    ``x [M,K]``, ``w [N,K]`` (rows are output features) and ``residual [M,N]`` share a dtype;
+    ``out [M,N]`` has that dtype or float32; ``bias`` is float32."""
+    _need(x, None, "linear x")
+    _need(w, x.dtype, "linear w")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not w.is_contiguous() or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    lda, ldc = _rows(x, "linear x"), _rows(out, "linear out")
+    out_f32 = 0
+    if out.dtype != x.dtype:
+        if out.dtype != torch.float32:
+            raise KernelError(f"linear: output dtype {out.dtype} for input dtype {x.dtype}")
+        out_f32 = 1
+    if bias is not None:
+        _need(bias, torch.float32, "linear bias")
+        if bias.numel() != N:
+            raise KernelError(f"linear: bias of {bias.numel()} for {N} outputs")
+    if residual is not None:
+        _need(residual, x.dtype, "linear residual")
+        if residual.shape != out.shape or _rows(residual, "linear residual") != ldc:
+            raise KernelError("linear: residual must have the output's shape and row stride")
+    _call("gemm_simt", "mlxb_linear_simt", _SIMT_ARGS, dtype_code(x.dtype), out_f32, _p(x), _p(w), _p(bias),
+          _p(residual), _p(out), M, N, K, lda, ldc, epilogue, stream)
+
+
+# --------------------------------------------------------------------------
+# paged key/value cache and attention
+
+_KVW_ARGS = [c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+             c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+
+
+def kv_write(k_src, v_src, positions, token_req, block_table, k_pool, v_pool, status, stream) -> None:
+    """Store this step's key and value rows into the pages of one layer.
+
+    ``k_src``/``v_src``: ``[T, Hkv*Dh]`` views (same row stride); pools ``[n_pages, Hkv, page, Dh]``."""
+    n_pages, Hkv, page, Dh = k_pool.shape
+    _need(k_src, k_pool.dtype, "kv_write k")
+    _need(v_src, k_pool.dtype, "kv_write v")
+    ld = _rows(k_src, "kv_write k")
+    if _rows(v_src, "kv_write v") != ld or k_src.shape[1] != Hkv * Dh or v_src.shape != k_src.shape:
+        raise KernelError(f"kv_write: k {tuple(k_src.shape)} v {tuple(v_src.shape)} for pool {tuple(k_pool.shape)}")
+    if not (k_pool.is_contiguous() and v_pool.is_contiguous() and block_table.is_contiguous()):
+        raise KernelError("kv_write: pools and block table must be contiguous")
+    _call("attention", "mlxb_kv_write", _KVW_ARGS, dtype_code(k_pool.dtype), _p(k_src), _p(v_src), ld,
+          _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, Hkv, Dh,
+          _p(k_pool), _p(v_pool), k_src.shape[0], _p(status), stream)
+
+
+_ATTN_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+              c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+
+
+def attention_generic(q, positions, token_req, block_table, k_pool, v_pool, out, n_heads: int, scale: float,
+                      window: int, status, stream) -> None:
+    """Causal attention of every token over its request's pages (float32 math, one warp per token and head).
+
+    ``q``: ``[T, n_heads*Dh]`` view; ``out``: ``[T, n_heads*Dh]``; ``window <= 0`` means all keys."""
+    n_pages, Hkv, page, Dh = k_pool.shape
+    _need(q, k_pool.dtype, "attention q")
+    _need(out, k_pool.dtype, "attention out")
+    T = q.shape[0]
+    if q.shape[1] != n_heads * Dh or out.shape[0] != T or out.shape[1] != n_heads * Dh:
+        raise KernelError(f"attention: q {tuple(q.shape)} out {tuple(out.shape)} for {n_heads} heads of {Dh}")
+    _call("attention", "mlxb_attention_generic", _ATTN_ARGS, dtype_code(k_pool.dtype), _p(q), _rows(q, "attention q"),
+          _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh,
+          window, scale, _p(k_pool), _p(v_pool), _p(out), _rows(out, "attention out"), T, _p(status), stream)

@@ -1,0 +1,56 @@
+"""A linear layer ``y = act(x W^T + b) (+ residual)`` as parts use it.
+
+The weight is held as ``[out, in]`` with the input dimension contiguous (the
+layout the kernels read); a file that stores ``[in, out]`` (HF's Conv1D, as
+GPT-2 checkpoints do, which mlx-lm transposes in ``Model.sanitize``,
+mlx_lm/models/gpt2.py:175-190) is transposed once at bind time.  Bias, the
+activation and the residual add run in the kernel's epilogue.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional
+
+import torch
+
+from .. import ops
+from .base import MATRIX, VECTOR, Init, ParamSpec, Part
+
+ACTIVATIONS = {None: ops.EPI_NONE, "none": ops.EPI_NONE, "gelu_new": ops.EPI_GELU_NEW}
+
+
+class Linear(Part):
+    kernel_libs = ("gemm_simt",)
+
+    def __init__(self, name: str, n_in: int, n_out: int, bias: bool = True, stored: str = "out_in",
+                 weight_suffix: str = ".weight", init: Init = Init(), bias_init: Init = Init()):
+        if stored not in ("out_in", "in_out"):
+            raise ValueError(f"stored layout {stored!r}: 'out_in' or 'in_out'")
+        self.name, self.n_in, self.n_out, self.has_bias, self.stored = name, n_in, n_out, bias, stored
+        self.weight_name = name + weight_suffix
+        self.init, self.bias_init = init, bias_init
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> List[ParamSpec]:
+        shape = (self.n_out, self.n_in) if self.stored == "out_in" else (self.n_in, self.n_out)
+        specs = [ParamSpec(self.weight_name, shape, MATRIX, self.init)]
+        if self.has_bias:
+            specs.append(ParamSpec(self.name + ".bias", (self.n_out,), VECTOR, self.bias_init))
+        return specs
+
+    def bind(self, tensors, dtype, device) -> None:
+        w = tensors[self.weight_name]
+        if self.stored == "in_out":
+            w = w.t().contiguous()
+        self.weight = w
+        self.bias = tensors[self.name + ".bias"] if self.has_bias else None
+
+    def use_weight(self, weight: torch.Tensor) -> None:
+        """Share another part's ``[out, in]`` tensor (a tied output head)."""
+        self.weight = weight
+
+    def forward(self, ctx, x, out, activation=None, residual=None) -> torch.Tensor:
+        epi = ACTIVATIONS[activation]
+        ops.linear_generic(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual)
+        return out

@@ -1,0 +1,69 @@
+"""Token mixers.  ``Attention``: multi-head (or grouped-query) causal
+attention over a paged key/value cache.
+
+One fused projection gives ``[q | k | v]`` per token (q = the first
+``n_heads*head_dim`` columns, then k, then v, head j = columns
+``[j*head_dim, (j+1)*head_dim)`` of each: mlx_lm/models/gpt2.py:52-58).  This
+step's keys and values go into the request's pages first, then every token
+attends keys ``max(0, p-window+1) .. p`` of its request through the block
+table with scale ``head_dim**-0.5`` (mlx_lm/models/gpt2.py:39, 63-65), and
+the output projection adds the residual in its epilogue.
+"""
+
+from __future__ import annotations
+
+from typing import List, Optional
+
+from .. import ops
+from .base import Init, Mixer, PagedKVSpec, PositionEncoding, register_part
+from .linear import Linear
+
+
+class Attention(Mixer):
+    kernel_libs = ("attention",)
+
+    def __init__(self, name: str, width: int, n_heads: int, head_dim: int, n_kv_heads: Optional[int] = None,
+                 window: Optional[int] = None, bias: bool = True, stored: str = "out_in",
+                 qkv_name: str = "c_attn", out_name: str = "c_proj", scale: Optional[float] = None,
+                 position: Optional[PositionEncoding] = None, init: Init = Init(), bias_init: Init = Init()):
+        n_kv_heads = n_heads if n_kv_heads is None else n_kv_heads
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{name}: {n_heads} query heads are not a multiple of {n_kv_heads} key/value heads")
+        if head_dim % 16 or not 16 <= head_dim <= 256:
+            raise ValueError(f"{name}: head size {head_dim} must be a multiple of 16 between 16 and 256")
+        self.name, self.width = name, width
+        self.n_heads, self.n_kv_heads, self.head_dim, self.window = n_heads, n_kv_heads, head_dim, window
+        self.scale = head_dim ** -0.5 if scale is None else float(scale)
+        self.position = position
+        self.q_width, self.kv_width = n_heads * head_dim, n_kv_heads * head_dim
+        self.qkv = Linear(f"{name}.{qkv_name}", width, self.q_width + 2 * self.kv_width, bias, stored,
+                          init=init, bias_init=bias_init)
+        self.out = Linear(f"{name}.{out_name}", self.q_width, width, bias, stored, init=init, bias_init=bias_init)
+
+    def children(self):
+        return (self.qkv, self.out)
+
+    def cache_spec(self):
+        return PagedKVSpec(self.n_kv_heads, self.head_dim, self.window)
+
+    def forward(self, ctx, x, residual, cache):
+        T = x.shape[0]
+        qkv = self.qkv.forward(ctx, x, ctx.ws.get("qkv", T, self.q_width + 2 * self.kv_width, x.dtype))
+        q = qkv[:, :self.q_width]
+        k = qkv[:, self.q_width:self.q_width + self.kv_width]
+        v = qkv[:, self.q_width + self.kv_width:]
+        if self.position is not None:
+            self.position.rotate(ctx, q, k)
+        if cache.write:
+            ops.kv_write(k, v, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, ctx.status,
+                         ctx.stream)
+        o = ctx.ws.get("attn_out", T, self.q_width, x.dtype)
+        self.attend(ctx, q, cache, o)
+        return self.out.forward(ctx, o, residual, residual=residual)
+
+    def attend(self, ctx, q, cache, o) -> None:
+        ops.attention_generic(q, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o,
+                              self.n_heads, self.scale, self.window or 0, ctx.status, ctx.stream)
+
+
+register_part("mixer", "attention", Attention)
