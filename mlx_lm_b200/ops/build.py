@@ -24,7 +24,7 @@ import tempfile
 import threading
 import time
 from concurrent.futures import ThreadPoolExecutor
-from typing import Dict, Iterable, List
+from typing import Dict, Iterable, List, Optional
 
 CSRC = os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "csrc")
 
@@ -36,7 +36,7 @@ NVCC_FLAGS = [
 ]
 
 _libs: Dict[str, ctypes.CDLL] = {}
-_lock = threading.Lock()
+_lock = threading.RLock()
 
 
 class KernelBuildError(RuntimeError):
@@ -68,19 +68,26 @@ def _digest(name: str) -> str:
     return h.hexdigest()[:12]
 
 
+_build_dir: Optional[str] = None
+
+
 def build_dir() -> str:
-    d = os.environ.get("MLXB_BUILD_DIR") or os.path.join(CSRC, "_build")
-    try:
-        os.makedirs(d, exist_ok=True)
-        probe = os.path.join(d, f".w{os.getpid()}")
-        with open(probe, "w"):
-            pass
-        os.unlink(probe)
-        return d
-    except OSError:
-        d = os.path.join(tempfile.gettempdir(), f"mlx_lm_b200-build-{os.getuid()}")
-        os.makedirs(d, exist_ok=True)
-        return d
+    global _build_dir
+    if _build_dir is not None:
+        return _build_dir
+    with _lock:
+        if _build_dir is None:
+            d = os.environ.get("MLXB_BUILD_DIR") or os.path.join(CSRC, "_build")
+            try:
+                os.makedirs(d, exist_ok=True)
+                fd, probe = tempfile.mkstemp(dir=d)
+                os.close(fd)
+                os.unlink(probe)
+            except OSError:
+                d = os.path.join(tempfile.gettempdir(), f"mlx_lm_b200-build-{os.getuid()}")
+                os.makedirs(d, exist_ok=True)
+            _build_dir = d
+    return _build_dir
 
 
 def lib_path(name: str) -> str:

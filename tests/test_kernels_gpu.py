@@ -1,0 +1,215 @@
+"""Each CUDA kernel alone against its plain statement in kernel_refs.py, at sizes other than the
+engine's tiny configurations: widths and vocabularies that are no power of two, head sizes in
+steps of 16, grouped heads, windows, pages of several sizes, block tables in scrambled order."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import kernel_refs as R
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def tol(dtype, f32=1e-5, bf16=1.6e-2):
+    return f32 if dtype == torch.float32 else bf16
+
+
+def rel_err(got, ref):
+    ref = ref.float().cpu()
+    return float((got.float().cpu() - ref).abs().max()) / max(1e-6, float(ref.abs().max()))
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from mlx_lm_b200 import ops as o
+    o.require_cuda()
+    return o
+
+
+def stream():
+    return torch.cuda.current_stream().cuda_stream
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("T,D,V,P", [(1, 64, 512, 128), (37, 96, 1000, 256), (300, 1600, 50257, 1024), (5, 40, 33, 7)])
+def test_embed_pos(ops, dtype, T, D, V, P):
+    g = torch.Generator().manual_seed(T)
+    wte = torch.randn(V, D, generator=g).to(dtype).cuda()
+    wpe = torch.randn(P, D, generator=g).to(dtype).cuda()
+    tok = torch.randint(0, V, (T,), generator=g, dtype=torch.int32).cuda()
+    pos = torch.randint(0, P, (T,), generator=g, dtype=torch.int32).cuda()
+    tok[0], pos[0] = V - 1, P - 1
+    out = torch.empty(T, D, dtype=dtype, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.embed_pos(tok, pos, wte, wpe, out, status, stream())
+    assert rel_err(out, R.embed_pos(tok.cpu(), pos.cpu(), wte.cpu(), wpe.cpu())) <= tol(dtype, 1e-7, 4e-3)
+    ops.embed_pos(tok, pos, wte, None, out, status, stream(), scale=3.0)
+    assert rel_err(out, R.embed_pos(tok.cpu(), pos.cpu(), wte.cpu(), None, 3.0)) <= tol(dtype, 1e-7, 4e-3)
+    assert int(status.item()) == 0
+    # ids outside the tables are reported, not read
+    tok[0] = V
+    ops.embed_pos(tok, pos, wte, wpe, out, status, stream())
+    assert int(status.item()) & ops.ST_TOKEN_RANGE
+    assert float(out[0].float().abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("R_,D,eps", [(1, 64, 1e-5), (33, 96, 1e-6), (130, 1600, 1e-5), (7, 1024, 1e-5), (3, 5000, 1e-3),
+                                      (2, 13000, 1e-5)])
+def test_layernorm(ops, dtype, R_, D, eps):
+    g = torch.Generator().manual_seed(D)
+    x = (torch.randn(R_, D, generator=g) * 3 + 1.5).to(dtype).cuda()
+    gain = (torch.randn(D, generator=g) * 0.1 + 1).cuda()
+    bias = (torch.randn(D, generator=g) * 0.1).cuda()
+    out = torch.empty_like(x)
+    ops.layernorm(x, gain, bias, out, eps, stream())
+    assert rel_err(out, R.layernorm(x.cpu(), gain.cpu(), bias.cpu(), eps)) <= tol(dtype, 2e-6, 4e-3)
+    ops.layernorm(x, gain, None, out, eps, stream())
+    assert rel_err(out, R.layernorm(x.cpu(), gain.cpu(), None, eps)) <= tol(dtype, 2e-6, 4e-3)
+    rows = torch.tensor([R_ - 1, 0, R_ // 2], dtype=torch.int32).cuda()
+    out3 = torch.empty(3, D, dtype=dtype, device="cuda")
+    ops.layernorm(x, gain, bias, out3, eps, stream(), rows=rows)
+    assert rel_err(out3, R.layernorm(x.cpu(), gain.cpu(), bias.cpu(), eps, rows.cpu())) <= tol(dtype, 2e-6, 4e-3)
+
+
+def test_layernorm_constant_row_and_large_mean(ops):
+    # a row with a large mean and tiny spread: a one-pass variance (E[x^2]-E[x]^2) would lose it
+    x = (1000.0 + torch.arange(256).float().remainder(2) * 0.5).repeat(2, 1).cuda()
+    gain, bias = torch.ones(256).cuda(), torch.zeros(256).cuda()
+    out = torch.empty_like(x)
+    ops.layernorm(x, gain, bias, out, 1e-5, stream())
+    assert rel_err(out, R.layernorm(x.cpu().double(), gain.cpu().double(), bias.cpu().double(), 1e-5)) <= 1e-4
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M,N,K", [(1, 192, 64), (7, 320, 96), (64, 1000, 96), (130, 50, 321), (257, 1600, 200),
+                                   (3, 7, 5)])
+def test_linear_generic(ops, dtype, M, N, K):
+    g = torch.Generator().manual_seed(M * N + K)
+    x = torch.randn(M, K, generator=g).to(dtype).cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(dtype).cuda()
+    b = torch.randn(N, generator=g).cuda()
+    res = torch.randn(M, N, generator=g).to(dtype).cuda()
+    out = torch.empty(M, N, dtype=dtype, device="cuda")
+    t = tol(dtype, 2e-6, 6e-3)
+    ops.linear_generic(x, w, b, out, stream())
+    assert rel_err(out, R.linear(x.cpu(), w.cpu(), b.cpu())) <= t
+    ops.linear_generic(x, w, None, out, stream(), epilogue=ops.EPI_GELU_NEW)
+    assert rel_err(out, R.linear(x.cpu(), w.cpu(), None, "gelu_new")) <= t
+    ops.linear_generic(x, w, b, out, stream(), epilogue=ops.EPI_GELU_NEW, residual=res)
+    assert rel_err(out, R.linear(x.cpu(), w.cpu(), b.cpu(), "gelu_new", res.cpu())) <= t
+    # in place on the residual, float32 output from bfloat16 inputs, strided input rows
+    r2 = res.clone()
+    ops.linear_generic(x, w, b, r2, stream(), residual=r2)
+    assert rel_err(r2, R.linear(x.cpu(), w.cpu(), b.cpu(), None, res.cpu())) <= t
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.linear_generic(x, w, None, out32, stream())
+    assert rel_err(out32, R.linear(x.cpu(), w.cpu())) <= 2e-6
+    wide = torch.randn(M, K + 24, generator=g).to(dtype).cuda()
+    ops.linear_generic(wide[:, 8:8 + K], w, b, out, stream())
+    assert rel_err(out, R.linear(wide[:, 8:8 + K].cpu(), w.cpu(), b.cpu())) <= t
+
+
+def test_linear_row_does_not_depend_on_batch(ops):
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(70, 96, generator=g).cuda()
+    w = torch.randn(320, 96, generator=g).cuda()
+    a = torch.empty(70, 320, device="cuda")
+    b = torch.empty(1, 320, device="cuda")
+    ops.linear_generic(x, w, None, a, stream())
+    ops.linear_generic(x[69:70], w, None, b, stream())
+    assert torch.equal(a[69:70], b)
+
+
+def paged_case(dtype, lens, new, Hq, Hkv, Dh, page, seed, n_pages=None):
+    """Requests with ``lens[i]`` cached tokens plus ``new[i]`` tokens in this step, pages handed out in a
+    scrambled order.  Returns everything the attention wrappers need, on the GPU, plus host copies."""
+    g = torch.Generator().manual_seed(seed)
+    Rn = len(lens)
+    total = [l + n for l, n in zip(lens, new)]
+    need = sum((t + page - 1) // page for t in total)
+    n_pages = n_pages or need + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max((t + page - 1) // page for t in total) + 1
+    bt = torch.full((Rn, width), -1, dtype=torch.int32)
+    for r, t in enumerate(total):
+        for lp in range((t + page - 1) // page):
+            bt[r, lp] = perm.pop()
+    k_pool = torch.randn(n_pages, Hkv, page, Dh, generator=g).to(dtype)
+    v_pool = torch.randn(n_pages, Hkv, page, Dh, generator=g).to(dtype)
+    T = sum(new)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * Dh, generator=g).to(dtype)
+    positions = torch.cat([torch.arange(l, l + n) for l, n in zip(lens, new)]).int()
+    token_req = torch.cat([torch.full((n,), r) for r, n in enumerate(new)]).int()
+    return dict(bt=bt, k_pool=k_pool, v_pool=v_pool, qkv=qkv, positions=positions, token_req=token_req, T=T,
+                Hq=Hq, Hkv=Hkv, Dh=Dh, page=page)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,window", [(4, 4, 16, 16, 0), (3, 3, 32, 16, 0), (6, 2, 48, 32, 0),
+                                                    (5, 1, 80, 64, 0), (2, 2, 128, 16, 40), (8, 4, 64, 16, 17)])
+def test_kv_write_and_attention(ops, dtype, Hq, Hkv, Dh, page, window):
+    c = paged_case(dtype, lens=[0, 37, 130, 64], new=[21, 1, 35, 2], Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=Dh + page)
+    dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    qw, kw = Hq * Dh, Hkv * Dh
+    q, k, v = dev["qkv"][:, :qw], dev["qkv"][:, qw:qw + kw], dev["qkv"][:, qw + kw:]
+    ops.kv_write(k, v, dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"], dev["v_pool"], status, stream())
+    rk, rv = R.kv_write(c["qkv"][:, qw:qw + kw], c["qkv"][:, qw + kw:], c["positions"], c["token_req"], c["bt"],
+                        c["k_pool"], c["v_pool"])
+    assert torch.equal(dev["k_pool"].cpu(), rk) and torch.equal(dev["v_pool"].cpu(), rv)
+    out = torch.empty(c["T"], qw, dtype=dtype, device="cuda")
+    scale = Dh ** -0.5
+    ops.attention_generic(q, dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"], dev["v_pool"], out, Hq,
+                          scale, window, status, stream())
+    ref = R.attention(c["qkv"][:, :qw], c["positions"], c["token_req"], c["bt"], rk, rv, Hq, scale, window)
+    assert int(status.item()) == 0
+    assert rel_err(out, ref) <= tol(dtype, 3e-6, 8e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key(ops, dtype):
+    """One key among hundreds matches the query strongly: the output must be that key's value row,
+    wherever its page lies.  Random inputs would hide a key that is skipped or read from the wrong page."""
+    Hq = Hkv = 2
+    Dh, page = 64, 16
+    for target in (0, 15, 16, 17, 255, 256, 300, 399):
+        c = paged_case(dtype, lens=[399], new=[1], Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=target)
+        qw = Hq * Dh
+        c["qkv"][:, :qw] = 0
+        c["qkv"][0, :Dh] = 6.0          # head 0 looks for ...
+        pg = int(c["bt"][0, target // page])
+        c["k_pool"][:, 0] *= 0.05
+        c["k_pool"][pg, 0, target % page, :] = 6.0   # ... this key
+        dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = torch.empty(1, qw, dtype=dtype, device="cuda")
+        ops.attention_generic(dev["qkv"][:, :qw], dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"],
+                              dev["v_pool"], out, Hq, Dh ** -0.5, 0, status, stream())
+        want = c["v_pool"][pg, 0, target % page, :].float()
+        assert float((out[0, :Dh].float().cpu() - want).abs().max()) <= (1e-4 if dtype == torch.float32 else 2e-2), target
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_window_edge(ops, dtype):
+    """With a window of W the key at p-W+1 counts and the key at p-W does not."""
+    Hq = Hkv = 1
+    Dh, page, W = 32, 16, 40
+    for hot, expect_hit in ((200 - W + 1, True), (200 - W, False)):
+        c = paged_case(dtype, lens=[200], new=[1], Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=5)
+        c["qkv"][0, :Dh] = 8.0
+        c["k_pool"] *= 0.02
+        pg = int(c["bt"][0, hot // page])
+        c["k_pool"][pg, 0, hot % page, :] = 8.0
+        dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+        status = torch.zeros(1, dtype=torch.int32, device="cuda")
+        out = torch.empty(1, Dh, dtype=dtype, device="cuda")
+        ops.attention_generic(dev["qkv"][:, :Dh], dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"],
+                              dev["v_pool"], out, Hq, Dh ** -0.5, W, status, stream())
+        want = c["v_pool"][pg, 0, hot % page, :].float()
+        close = float((out[0].float().cpu() - want).abs().max()) <= 3e-2
+        assert close == expect_hit

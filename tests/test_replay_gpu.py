@@ -1,0 +1,73 @@
+"""bin/trace_run against the plain implementation: each request alone and whole; most of it in
+one step and the last 32 tokens one by one; in portions of changing size down to two tokens and
+one; and mixed, up to four live requests with portions of some beside single tokens of others,
+in a pool so small that pages are used again.  In float32 and in bfloat16, for both tiny
+configurations and for a variant with sharp attention."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gpt2 as plain
+from helpers import (CONFIG_A, CONFIG_B, Trace, make_model_dir, max_live_tokens, mixed_schedule, random_tokens,
+                     run_trace)
+
+pytestmark = pytest.mark.gpu
+
+# largest |difference| allowed, as a fraction of max(1, largest |reference logit|)
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+CASES = {
+    "A": (CONFIG_A, 0, 0.0, [23, 29, 100, 128, 65]),
+    "B": (CONFIG_B, 1, 0.0, [29, 55, 88, 200, 256]),
+    "B-sharp": (CONFIG_B, 2, 12.0, [88, 256, 130]),
+}
+
+
+def build_trace(lengths, vocab, seed):
+    reqs = {f"r{i}": random_tokens(n, vocab, 100 * seed + i) for i, n in enumerate(lengths)}
+    tr = Trace()
+    for name, toks in reqs.items():
+        tr.whole(f"{name}:whole", toks)
+    for name, toks in reqs.items():
+        tr.bulk_then_single(f"{name}:tail", toks, tail=32)
+    for name, toks in reqs.items():
+        tr.portions(f"{name}:portions", toks)
+    mixed_schedule(tr, [(f"{name}:mixed", toks) for name, toks in reqs.items()], seed=seed)
+    mixed_schedule(tr, [(f"{name}:mixed2", toks) for name, toks in reversed(list(reqs.items()))], seed=seed + 7,
+                   sizes=(2, 1, 1, 1, 16, 1, 1, 48, 1, 2, 1, 1, 1, 9))
+    return reqs, tr
+
+
+@pytest.mark.parametrize("case", list(CASES))
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_matches_plain(case, dtype, tmp_path):
+    config, seed, sharp, lengths = CASES[case]
+    weights = make_model_dir(str(tmp_path / "model"), config, seed, peaky=sharp)
+    reqs, tr = build_trace(lengths, config["vocab_size"], seed)
+    # the pool holds exactly what the busiest moment needs, so freed pages are taken again
+    got = run_trace(str(tmp_path / "model"), tr, dtype, str(tmp_path / "out"), max_tokens=max_live_tokens(tr))
+    ref = {name: plain.logits(toks, weights, config).numpy() for name, toks in reqs.items()}
+    worst, worst_key = 0.0, None
+    n_rows = 0
+    for (rid, pos), row in got.items():
+        name = rid.split(":")[0]
+        r = ref[name][pos]
+        err = float(np.abs(row - r).max()) / max(1.0, float(np.abs(r).max()))
+        n_rows += 1
+        if err > worst:
+            worst, worst_key = err, (rid, pos)
+    # every position of every request in every cutting was written
+    assert n_rows == 5 * sum(lengths)  # whole, tail, portions, mixed, mixed2
+    print(f"{case} {dtype}: worst relative difference {worst:.3e} at {worst_key} over {n_rows} rows")
+    assert worst <= TOL[dtype], f"worst at {worst_key}: {worst}"
+    # the same position gives the same logits however it was cut (tighter than against the reference)
+    cut_tol = TOL[dtype] * 0.5
+    for name, toks in reqs.items():
+        for pos in range(len(toks)):
+            base = got[(f"{name}:whole", pos)]
+            scale = max(1.0, float(np.abs(base).max()))
+            for cut in ("tail", "portions", "mixed", "mixed2"):
+                d = float(np.abs(got[(f"{name}:{cut}", pos)] - base).max()) / scale
+                assert d <= cut_tol, f"{name} position {pos}: {cut} differs from whole by {d}"
