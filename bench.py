@@ -1,0 +1,287 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of the engine on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--batch 8] [--layers N] [--impl ours|reference]
+
+A step is one decode step of the whole batch.  The default run has the layer sizes of GPT-2 medium
+(n_embd 1024, n_head 16, n_inner 4096, vocab 50257, 1024 positions; 24 layers) with seeded random
+bfloat16 weights, a batch of 8 requests with 512-token prompts and a context of 1024: after the
+prompts are in the cache, W untimed and K timed decode steps follow.  One JSON line is printed:
+
+  value      decoded tokens per second, timed on the device (CUDA events around the K steps)
+  e2e        the same through the Python entry point (BatchGenerator): host token ids in, host
+             token ids out, every step's inputs copied from pinned host memory and its tokens read back
+  prefill    one step of 2 x 1024 prompt tokens: tokens/s, ms, flops / time / measured bf16 peak
+  roofline   decode step: bytes it has to read (every weight once + the live requests' cache) / time,
+             against the measured copy bandwidth
+  points     decode tokens/s at batch 1 and 64
+
+With --gpus N > 1 it prints one line and exits with 2: the engine runs on one GPU.
+"""
+import argparse
+import json
+import os
+import sys
+import tempfile
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+MEDIUM = dict(model_type="gpt2", n_layer=24, n_embd=1024, n_head=16, n_inner=4096, vocab_size=50257,
+              n_positions=1024, layer_norm_epsilon=1e-5, activation_function="gelu_new")
+PROMPT_LEN = 512
+CONTEXT = 1024
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm_gbs=p["hbm_gbs"], bf16_tflops=p["bf16_tflops"],
+                    bf16_tflops_sustained=p.get("bf16_tflops_sustained", p["bf16_tflops"]), source="measured")
+    return dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index=0, period=0.1):
+        self.period, self.samples, self._stop = period, [], threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.h = pynvml.nvmlDeviceGetHandleByIndex(index)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self._stop.is_set():
+            try:
+                mhz = nv.nvmlDeviceGetClockInfo(self.h, nv.NVML_CLOCK_SM)
+                reasons = nv.nvmlDeviceGetCurrentClocksThrottleReasons(self.h)
+                self.samples.append((mhz, reasons))
+            except Exception:
+                pass
+            self._stop.wait(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *a):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if self.nv is None or not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unavailable"]}
+        nv = self.nv
+        mhz = sorted(s[0] for s in self.samples)
+        bits = 0
+        for _, r in self.samples:
+            bits |= r
+        names = []
+        for attr, name in (("nvmlClocksThrottleReasonHwSlowdown", "hw_slowdown"),
+                           ("nvmlClocksThrottleReasonHwThermalSlowdown", "hw_thermal_slowdown"),
+                           ("nvmlClocksThrottleReasonSwThermalSlowdown", "sw_thermal_slowdown"),
+                           ("nvmlClocksThrottleReasonSwPowerCap", "sw_power_cap"),
+                           ("nvmlClocksThrottleReasonHwPowerBrakeSlowdown", "hw_power_brake")):
+            if bits & getattr(nv, attr, 0):
+                names.append(name)
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": nv.nvmlDeviceGetMaxClockInfo(self.h, nv.NVML_CLOCK_SM),
+                "reasons": names, "samples": len(mhz)}
+
+
+def model_bytes_and_flops(cfg, n_layer):
+    D, I, V = cfg["n_embd"], cfg["n_inner"] or 4 * cfg["n_embd"], cfg["vocab_size"]
+    per_layer = D * 3 * D + D * D + 2 * D * I               # matrix elements
+    vec = 3 * D + D + I + D + 4 * D                          # biases and norm vectors (float32)
+    weight_bytes = n_layer * (2 * per_layer + 4 * vec) + 2 * V * D + 4 * 2 * D
+    kv_bytes_per_token = n_layer * 2 * D * 2
+    linear_flops_per_token = 2 * n_layer * per_layer
+    return weight_bytes, kv_bytes_per_token, linear_flops_per_token
+
+
+def decode_loop(engine, sampler_cls, model, batch, prompt_len, steps, warmup, vocab, seed=0):
+    """Prefill `batch` prompts, then `warmup` + `steps` decode steps; returns (ms per step, launches per step)."""
+    import torch
+
+    from mlx_lm_b200 import ops
+    from mlx_lm_b200.engine import StepEntry
+    from mlx_lm_b200.engine.scheduler import Request
+    from mlx_lm_b200.sampling import GREEDY
+
+    g = torch.Generator().manual_seed(seed)
+    sample = sampler_cls(model.device, seed=seed)
+    reqs = []
+    for b in range(batch):
+        toks = torch.randint(0, vocab, (prompt_len,), generator=g).tolist()
+        engine.add_request(("bench", b))
+        reqs.append(Request(b, toks, prompt_len, 10 ** 9, GREEDY))
+    for i in range(0, batch, 4):    # prompts, four requests a step
+        chunk = reqs[i:i + 4]
+        logits = engine.step([StepEntry(("bench", r.uid), r.tokens, [prompt_len - 1]) for r in chunk])
+        toks, _ = sample(logits, chunk)
+        for r, t in zip(chunk, toks):
+            r.tokens.append(t)
+
+    def one_step():
+        logits = engine.step([StepEntry(("bench", r.uid), r.tokens[-1:], [0]) for r in reqs])
+        toks, _ = sample(logits, reqs)
+        for r, t in zip(reqs, toks):
+            r.tokens.append(t)
+
+    for _ in range(warmup):
+        one_step()
+    torch.cuda.synchronize()
+    ops.launch_count = 0
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(steps):
+        one_step()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / steps
+    launches = ops.launch_count / steps
+    mean_ctx = prompt_len + 1 + warmup + (steps - 1) / 2.0
+    engine.check_status()
+    for r in reqs:
+        engine.finish(("bench", r.uid))
+    return ms, launches, mean_ctx
+
+
+def run_ours(args):
+    import torch
+
+    from mlx_lm_b200 import ops
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.generate import BatchGenerator
+    from mlx_lm_b200.sampling.device import DeviceSampler
+    from mlx_lm_b200.weights import load_model, write_random_model
+
+    pk = peaks()
+    cfg = dict(MEDIUM)
+    n_layer_full = cfg["n_layer"]
+    cfg["n_layer"] = args.layers or n_layer_full
+    B, K, W = args.batch, args.steps, args.warmup
+    if PROMPT_LEN + 1 + W + K > CONTEXT:
+        raise SystemExit(f"--warmup {W} + --steps {K} decode steps after a {PROMPT_LEN}-token prompt exceed the "
+                         f"context of {CONTEXT}")
+    with tempfile.TemporaryDirectory() as d:
+        write_random_model(d, cfg, seed=0)
+        model, _ = load_model(d, dtype="bfloat16", device="cuda:0")
+    vocab = cfg["vocab_size"]
+    max_b = max(B, 64)
+    engine = Engine(model, page_size=16, max_tokens=max_b * CONTEXT, max_requests=max_b)
+    weight_bytes, kv_per_token, lin_flops = model_bytes_and_flops(cfg, cfg["n_layer"])
+
+    # ---- prefill: 2 x 1024 tokens in one step
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, vocab, (1024,), generator=g).tolist() for _ in range(2)]
+    times = []
+    for it in range(4):
+        for i in range(2):
+            engine.add_request(("pf", i))
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        engine.step([StepEntry(("pf", i), prompts[i], [1023]) for i in range(2)])
+        e.record()
+        torch.cuda.synchronize()
+        times.append(s.elapsed_time(e))
+        for i in range(2):
+            engine.finish(("pf", i))
+    pf_ms = min(times[1:])
+    D, L = cfg["n_embd"], cfg["n_layer"]
+    attn_flops = 2 * L * 4 * D * (1024 * 1025 // 2)          # QK^T and PV over the causal half, two prompts
+    pf_flops = 2048 * lin_flops + attn_flops + 2 * 2 * D * vocab
+    prefill = {"value": round(2048 / (pf_ms / 1e3), 1), "tokens": 2048, "ms": round(pf_ms, 4),
+               "frac": round(pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+
+    # ---- decode, device-timed
+    with ClockSampler() as clocks:
+        ms, launches, mean_ctx = decode_loop(engine, DeviceSampler, model, B, PROMPT_LEN, K, W, vocab)
+    value = B / (ms / 1e3)
+    step_bytes = weight_bytes + B * mean_ctx * kv_per_token
+    achieved = step_bytes / (ms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4)}
+
+    points = {}
+    for b in (1, 64):
+        pms, _, _ = decode_loop(engine, DeviceSampler, model, b, PROMPT_LEN, min(K, 64), max(3, min(W, 8)), vocab,
+                                seed=b)
+        points[f"decode_b{b}"] = round(b / (pms / 1e3), 1)
+
+    # ---- end to end through the Python entry point: host tokens in, host tokens out
+    g = torch.Generator().manual_seed(2)
+    host_prompts = [torch.randint(0, vocab, (PROMPT_LEN,), generator=g).tolist() for _ in range(B)]
+    gen = BatchGenerator(model, max_tokens=W + K + 1, engine=engine, completion_batch_size=max(B, 8),
+                         prefill_batch_size=max(B, 8), prefill_step_size=2048, max_tokens_per_step=4096)
+    gen.insert(host_prompts)
+    n_out = 0
+    while n_out < B * (1 + W):            # prompts and warm-up steps
+        n_out += len(gen.next_generated())
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    n_timed = 0
+    for _ in range(K):
+        n_timed += len(gen.next_generated())
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    gen.close()
+    W_tab = engine.cache.table_width
+    h2d = 4 * (3 * B + B + B + (B + 1) + B + B * W_tab + 3 * 4) + 64 * B     # step integers + sampler records
+    e2e = {"value": round(n_timed / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
+           "d2h_bytes_per_step": int(4 * (64 + B))}
+
+    out = {
+        "metric": "decode tokens/s, GPT-2 medium, batch 8, 512-token prompts, context 1024",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random prompt tokens",
+        "config": {"model": "gpt2-medium", "n_layer": cfg["n_layer"], "n_layer_of_configuration": n_layer_full,
+                   "n_embd": cfg["n_embd"], "n_head": cfg["n_head"], "n_inner": cfg["n_inner"],
+                   "vocab_size": vocab, "n_positions": cfg["n_positions"], "global_batch": B,
+                   "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": 16, "parallelism": "single_gpu",
+                   "l2": "inputs larger than L2 (weights %.0f MB)" % (weight_bytes / 1e6),
+                   "peaks": pk["source"], "prefill_peak": "bf16_tflops (burst)"},
+        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(round(launches * K)),
+        "prefill": prefill, "roofline": roofline, "points": points, "impl": "ours",
+    }
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 24 (0 = all)")
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    a = ap.parse_args()
+    if a.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "mlx-lm 0.32.0 installs offline only with --no-deps and fails at 'import mlx.core': "
+                          "no MLX wheel exists for this machine and there is no network"}))
+        return 0
+    if a.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
+        print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not offered")
+        return 2
+    a.warmup = max(a.warmup, 3)
+    run_ours(a)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

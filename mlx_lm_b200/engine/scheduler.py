@@ -1,0 +1,286 @@
+"""Continuous batching above the step function.
+
+mlx-lm's ``BatchGenerator`` (mlx_lm/generate.py:1565-1945) keeps a queue of
+unprocessed sequences, one rectangular prompt batch and one decode batch, and
+runs them as separate model calls.  Here every iteration is ONE step of the
+engine: each running request contributes the tokens it has not run yet — one
+for a decoding request, a portion of the prompt for a prefilling one — under
+a budget of tokens per step, decoding requests first.
+
+Decisions, all made in ``plan`` (plain Python, no device):
+
+* admit     from the front of ``waiting`` while fewer than ``max_requests`` run, fewer than
+            ``max_prefilling`` of them are still in their prompt, a state slot is free and pages for
+            the request's first portion are free;
+* portions  a prompt is cut under ``prefill_step_size`` per request and ``max_tokens_per_step`` for
+            the whole step, and further down to what the free pages can hold;
+* pages run out
+            if a decoding request cannot get the page its next token needs, or nothing at all can
+            run, the most recently admitted running request is preempted: it gives back all its
+            pages and goes to the FRONT of ``waiting`` with prompt := prompt + tokens generated so
+            far (recompute); tokens already handed out stay handed out.  A request that could never
+            fit the pool alone is refused at ``insert``;
+* finishing ``"length"`` at ``max_tokens`` generated tokens, ``"stop"`` when a stop sequence matches
+            (mlx_lm/generate.py:1504-1514); pages and slot are given back at once.
+
+The scheduler talks to an engine through five calls (``add_request``, ``finish``, ``step``,
+``cache`` for page arithmetic, ``max_len``), and to a ``sample`` callable; tests drive it with fakes.
+"""
+
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Callable, Deque, Dict, List, Optional, Sequence, Tuple
+
+from ..cache import OutOfPages
+from ..sampling import GREEDY, LogitsProcessors, Sampler
+from .step import StepEntry
+
+
+class StopSequenceMatcher:
+    """Match any of several token sequences at the end of a stream (mlx_lm/generate.py:887-956 does
+    this with an Aho-Corasick trie; the sequences here are few and short, so the tail is compared)."""
+
+    def __init__(self, stop_sequences: Optional[Sequence[Sequence[int]]] = None):
+        self.sequences = [tuple(s) for s in (stop_sequences or []) if len(s)]
+        self.longest = max((len(s) for s in self.sequences), default=0)
+
+    def matches(self, generated: Sequence[int]) -> bool:
+        n = len(generated)
+        for s in self.sequences:
+            k = len(s)
+            if k <= n and tuple(generated[n - k:]) == s:
+                return True
+        return False
+
+
+@dataclass
+class Request:
+    uid: int
+    tokens: List[int]                 # prompt, then generated tokens as they come
+    n_prompt: int
+    max_tokens: int
+    sampler: Sampler = GREEDY
+    processors: Sequence = ()
+    stop: StopSequenceMatcher = field(default_factory=StopSequenceMatcher)
+    n_cached: int = 0                 # tokens whose keys/values are in the cache
+    n_generated: int = 0
+    admitted_at: int = -1             # admission counter; -1 while waiting
+    preemptions: int = 0
+
+    @property
+    def remaining(self) -> int:
+        return len(self.tokens) - self.n_cached
+
+    @property
+    def generated(self) -> List[int]:
+        return self.tokens[self.n_prompt:]
+
+
+@dataclass
+class Response:
+    """One generated token (the shape of ``GenerationBatch.Response``, mlx_lm/generate.py:1321-1328)."""
+    uid: int
+    token: int
+    logprobs: float                   # log-probability of ``token``; a [V] tensor if full log-probs were asked for
+    finish_reason: Optional[str]
+    prompt_cache: Optional[object] = None
+    all_tokens: Optional[List[int]] = None
+
+
+@dataclass
+class PromptProgress:
+    """Progress of a prompt (``PromptProcessingBatch.Response``, mlx_lm/generate.py:1096-1101)."""
+    uid: int
+    progress: Tuple[int, int]
+    end_of_segment: bool
+    end_of_prompt: bool
+
+
+@dataclass
+class PlannedEntry:
+    request: Request
+    n_tokens: int
+    wants_logits: bool
+
+
+@dataclass
+class SchedulerStats:
+    steps: int = 0
+    tokens: int = 0
+    prompt_tokens: int = 0
+    generation_tokens: int = 0
+    preemptions: int = 0
+    most_running: int = 0
+
+
+class Scheduler:
+    def __init__(self, engine, sample: Callable, max_requests: int = 32, max_prefilling: int = 8,
+                 prefill_step_size: int = 2048, max_tokens_per_step: int = 2048):
+        self.engine, self.sample = engine, sample
+        self.max_requests = max_requests
+        self.max_prefilling = max(1, max_prefilling)
+        self.prefill_step_size = max(1, prefill_step_size)
+        self.max_tokens_per_step = max(1, max_tokens_per_step)
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []
+        self._uid = 0
+        self._admissions = 0
+        self.stats = SchedulerStats()
+        self.last_step_tokens = self.last_step_prompt_tokens = 0
+
+    # ------------------------------------------------------------------ requests in and out
+    def insert(self, prompt: Sequence[int], max_tokens: int, sampler: Optional[Sampler] = None,
+               processors: Sequence = (), stop: Optional[StopSequenceMatcher] = None) -> int:
+        prompt = [int(t) for t in prompt]
+        if not prompt:
+            raise ValueError("a prompt needs at least one token")
+        cache = self.engine.cache
+        total = len(prompt) + max_tokens
+        if total - 1 > self.engine.max_len:
+            raise ValueError(f"prompt of {len(prompt)} tokens plus {max_tokens} new tokens needs {total - 1} "
+                             f"positions; the model has {self.engine.max_len}")
+        need = (total - 1 + cache.page_size - 1) // cache.page_size
+        for g in cache.kv_groups:
+            held = need if g.spec.window is None else min(
+                need, (g.spec.window + self.prefill_step_size) // cache.page_size + 2)
+            if held > g.pool.n_pages:
+                raise ValueError(f"the request may hold {held} pages; the pool has {g.pool.n_pages} in all")
+        uid = self._uid
+        self._uid += 1
+        self.waiting.append(Request(uid, prompt, len(prompt), max_tokens, sampler or GREEDY, tuple(processors),
+                                    stop or StopSequenceMatcher()))
+        return uid
+
+    def remove(self, uids: Sequence[int]) -> None:
+        uids = set(uids)
+        for r in [r for r in self.running if r.uid in uids]:
+            self.engine.finish(r.uid)
+            self.running.remove(r)
+        self.waiting = deque(r for r in self.waiting if r.uid not in uids)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ------------------------------------------------------------------ decisions
+    def _preempt(self, victim: Request) -> None:
+        self.engine.finish(victim.uid)
+        self.running.remove(victim)
+        victim.n_cached = 0
+        victim.admitted_at = -1
+        victim.preemptions += 1
+        self.stats.preemptions += 1
+        self.waiting.appendleft(victim)
+
+    def _fits(self, planned: List[PlannedEntry], r: Request, n: int) -> bool:
+        wants = [(p.request.uid, p.n_tokens) for p in planned] + [(r.uid, n)]
+        return self.engine.cache.can_reserve(wants)
+
+    def _largest_portion(self, planned: List[PlannedEntry], r: Request, n: int) -> int:
+        """The longest portion <= n of r's tokens whose pages are free (0 if not even one token fits)."""
+        if self._fits(planned, r, n):
+            return n
+        lo, hi = 0, n - 1
+        while lo < hi:
+            mid = (lo + hi + 1) // 2
+            if self._fits(planned, r, mid):
+                lo = mid
+            else:
+                hi = mid - 1
+        return lo
+
+    def plan(self) -> List[PlannedEntry]:
+        """Decide this step's entries; admits and preempts as a side effect."""
+        while True:
+            planned: List[PlannedEntry] = []
+            budget = self.max_tokens_per_step
+            starved: Optional[Request] = None
+            # decoding requests first, oldest first
+            for r in sorted(self.running, key=lambda r: r.admitted_at):
+                if r.remaining != 1 or budget <= 0:
+                    continue
+                if self._fits(planned, r, 1):
+                    planned.append(PlannedEntry(r, 1, True))
+                    budget -= 1
+                else:
+                    starved = r
+                    break
+            if starved is not None:
+                victim = max(self.running, key=lambda r: r.admitted_at)
+                self._preempt(victim)
+                continue
+            # portions of prompts that are under way
+            for r in sorted(self.running, key=lambda r: r.admitted_at):
+                if r.remaining <= 1 or budget <= 0:
+                    continue
+                n = self._largest_portion(planned, r, min(r.remaining, self.prefill_step_size, budget))
+                if n > 0:
+                    planned.append(PlannedEntry(r, n, n == r.remaining))
+                    budget -= n
+            # admissions
+            while (self.waiting and budget > 0 and len(self.running) < self.max_requests
+                   and sum(1 for r in self.running if r.remaining > 1) < self.max_prefilling
+                   and self.engine.cache.has_free_slot()):
+                r = self.waiting[0]
+                self.engine.add_request(r.uid)
+                n = self._largest_portion(planned, r, min(r.remaining, self.prefill_step_size, budget))
+                if n == 0:
+                    self.engine.finish(r.uid)
+                    break
+                self.waiting.popleft()
+                r.admitted_at = self._admissions
+                self._admissions += 1
+                self.running.append(r)
+                planned.append(PlannedEntry(r, n, n == r.remaining))
+                budget -= n
+            if planned or not self.running:
+                if not planned and self.waiting:
+                    raise OutOfPages("a waiting request cannot start although nothing is running")
+                return planned
+            # nothing can move: free the newest request's pages and try again
+            self._preempt(max(self.running, key=lambda r: r.admitted_at))
+
+    # ------------------------------------------------------------------ one iteration
+    def next(self) -> Tuple[List[PromptProgress], List[Response]]:
+        planned = self.plan()
+        self.last_step_tokens = self.last_step_prompt_tokens = 0
+        if not planned:
+            return [], []
+        entries = [StepEntry(p.request.uid, p.request.tokens[p.request.n_cached:p.request.n_cached + p.n_tokens],
+                             [p.n_tokens - 1] if p.wants_logits else []) for p in planned]
+        logits = self.engine.step(entries)
+        self.stats.steps += 1
+        self.stats.most_running = max(self.stats.most_running, len(self.running))
+        prompts: List[PromptProgress] = []
+        sampled: List[Request] = []
+        for p in planned:
+            r = p.request
+            if r.n_cached < r.n_prompt:
+                done = min(r.n_cached + p.n_tokens, r.n_prompt)
+                self.stats.prompt_tokens += done - r.n_cached
+                self.last_step_prompt_tokens += done - r.n_cached
+                prompts.append(PromptProgress(r.uid, (done, r.n_prompt), done == r.n_prompt, done == r.n_prompt))
+            r.n_cached += p.n_tokens
+            self.stats.tokens += p.n_tokens
+            self.last_step_tokens += p.n_tokens
+            if p.wants_logits:
+                sampled.append(r)
+        responses: List[Response] = []
+        if sampled:
+            tokens, logprobs = self.sample(logits, sampled)
+            for r, tok, lp in zip(sampled, tokens, logprobs):
+                r.tokens.append(int(tok))
+                r.n_generated += 1
+                self.stats.generation_tokens += 1
+                reason = None
+                if r.stop.matches(r.generated):
+                    reason = "stop"
+                elif r.n_generated >= r.max_tokens:
+                    reason = "length"
+                if reason is not None:
+                    self.engine.finish(r.uid)
+                    self.running.remove(r)
+                responses.append(Response(r.uid, int(tok), lp, reason,
+                                          all_tokens=list(r.tokens) if reason is not None else None))
+        return prompts, responses

@@ -85,8 +85,13 @@ def _fn(libname: str, fname: str, argtypes):
     return hit
 
 
+launch_count = 0   # kernel launches issued through this module (bench.py reads and resets it)
+
+
 def _call(libname: str, fname: str, argtypes, *args) -> None:
+    global launch_count
     f, lib = _fn(libname, fname, argtypes)
+    launch_count += 1
     rc = f(*args)
     if rc != 0:
         msg = lib.mlxb_last_error()
@@ -219,3 +224,61 @@ def attention_generic(q, positions, token_req, block_table, k_pool, v_pool, out,
     _call("attention", "mlxb_attention_generic", _ATTN_ARGS, dtype_code(k_pool.dtype), _p(q), _rows(q, "attention q"),
           _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh,
           window, scale, _p(k_pool), _p(v_pool), _p(out), _rows(out, "attention out"), T, _p(status), stream)
+
+
+# --------------------------------------------------------------------------
+# sampling and logits processors
+
+SAMPLE_WORDS, PROCESS_WORDS = 16, 8
+
+_SAMPLE_ARGS = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                c_void_p]
+
+
+def sample(logits, params, out_token, out_logprob, stream, xtc_special=None, out_logprobs=None) -> None:
+    """One token per row of float32 ``logits [R, V]``.
+
+    ``params``: int32 ``[R, 16]`` holding the bit patterns of csrc/sampling.cu's ``SampleParams``;
+    ``out_token`` int32 ``[R]``, ``out_logprob`` float32 ``[R]`` (log-probability of the chosen token
+    under the unfiltered distribution); ``out_logprobs`` (optional) float32 ``[R, V]`` receives
+    ``logits - logsumexp(logits)``."""
+    _need(logits, torch.float32, "sample logits")
+    _need(params, torch.int32, "sample params")
+    _need(out_token, torch.int32, "sample out_token")
+    _need(out_logprob, torch.float32, "sample out_logprob")
+    R, V = logits.shape
+    if params.numel() < R * SAMPLE_WORDS or out_token.numel() < R or out_logprob.numel() < R:
+        raise KernelError(f"sample: {R} rows need {R * SAMPLE_WORDS} parameter words and {R} outputs")
+    ldo = 0
+    if out_logprobs is not None:
+        _need(out_logprobs, torch.float32, "sample out_logprobs")
+        if out_logprobs.shape != logits.shape:
+            raise KernelError("sample: out_logprobs must have the shape of logits")
+        ldo = _rows(out_logprobs, "sample out_logprobs")
+    n_special = 0
+    if xtc_special is not None:
+        _need(xtc_special, torch.int32, "sample xtc_special")
+        n_special = xtc_special.numel()
+    _call("sampling", "mlxb_sample", _SAMPLE_ARGS, _p(logits), _rows(logits, "sample logits"), R, V, _p(params),
+          _p(xtc_special), n_special, _p(out_token), _p(out_logprob), _p(out_logprobs), ldo, stream)
+
+
+_PROCESS_ARGS = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]
+
+
+def process_logits(logits, params, context, bias_index, bias_value, stream) -> None:
+    """In place on float32 ``logits [R, V]``: additive bias, then repetition, presence and frequency
+    penalties over each row's recent tokens.  ``params`` int32 ``[R, 8]`` (``ProcessParams`` bit
+    patterns); ``context`` int32 ``[R, C]`` left-padded with -1; ``bias_index`` int32 / ``bias_value``
+    float32 ``[R, B]``."""
+    _need(logits, torch.float32, "process_logits logits")
+    _need(params, torch.int32, "process_logits params")
+    _need(context, torch.int32, "process_logits context")
+    R, V = logits.shape
+    C = context.shape[1] if context.dim() == 2 else 0
+    B = bias_index.shape[1] if bias_index is not None and bias_index.dim() == 2 else 0
+    if B:
+        _need(bias_index, torch.int32, "process_logits bias_index")
+        _need(bias_value, torch.float32, "process_logits bias_value")
+    _call("sampling", "mlxb_process_logits", _PROCESS_ARGS, _p(logits), _rows(logits, "process_logits logits"), R, V,
+          _p(params), _p(context), C, _p(bias_index) if B else None, _p(bias_value) if B else None, B, stream)

@@ -1,0 +1,369 @@
+"""The engine in-process on the GPU: parts alone, long decoding, the first tokens of a sequence,
+generation through the entry points, and a toy mixer with state of its own that is registered,
+built and stepped from this file alone."""
+import math
+import os
+from dataclasses import dataclass
+from types import SimpleNamespace
+
+import numpy as np
+import pytest
+import torch
+
+import kernel_refs as R
+import plain_gpt2 as plain
+from helpers import CONFIG_A, CONFIG_B, make_model_dir, random_tokens
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+
+
+def rel(got, ref):
+    ref = torch.as_tensor(ref).float().cpu()
+    return float((torch.as_tensor(got).float().cpu() - ref).abs().max()) / max(1.0, float(ref.abs().max()))
+
+
+def part_ctx(T=0, positions=None, token_req=None):
+    from mlx_lm_b200 import ops
+    from mlx_lm_b200.engine import Workspace
+    return SimpleNamespace(ws=Workspace("cuda"), stream=ops.current_stream(), n_tokens=T,
+                           status=torch.zeros(1, dtype=torch.int32, device="cuda"),
+                           positions=positions, token_req=token_req, tokens=None)
+
+
+def bind(part, dtype, seed=0):
+    """Random tensors for a part's own specs, placed as the loader places them."""
+    from mlx_lm_b200.weights.loader import place
+    g = torch.Generator().manual_seed(seed)
+    host, dev = {}, {}
+    for s in part.all_param_specs():
+        t = (torch.randn(s.shape, generator=g) * 0.3 + (1.0 if s.name.endswith("ln.weight") else 0.0))
+        t = t.to(torch.bfloat16).float()       # representable in both dtypes
+        host[s.name] = t
+        dev[s.name] = place(s, t, dtype, "cuda")
+    part.bind_all(dev, dtype, "cuda")
+    return host
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_parts_alone(dtype):
+    from mlx_lm_b200.engine import LayerCacheView
+    from mlx_lm_b200.parts import MLP, Attention, LayerNorm, Linear, PreNormBlock
+    tol = 2e-5 if dtype == torch.float32 else 2e-2
+    g = torch.Generator().manual_seed(1)
+    T, D = 37, 80
+    x = torch.randn(T, D, generator=g).to(torch.bfloat16).float()
+    xd = x.to(dtype).cuda()
+    ctx = part_ctx(T)
+
+    lin = Linear("p", D, 56, bias=True, stored="in_out")
+    w = bind(lin, dtype)
+    out = torch.empty(T, 56, dtype=dtype, device="cuda")
+    lin.forward(ctx, xd, out, activation="gelu_new")
+    assert rel(out, plain.gelu_new(plain.conv1d_linear(x, w["p.weight"], w["p.bias"]))) <= tol
+
+    ln = LayerNorm("ln", D, 1e-3)
+    w = bind(ln, dtype)
+    assert rel(ln.forward(ctx, xd), plain.layer_norm(x, w["ln.weight"], w["ln.bias"], 1e-3)) <= tol
+
+    mlp = MLP("m", D, 136, stored="in_out")
+    w = bind(mlp, dtype)
+    res = xd.clone()
+    y = mlp.forward(ctx, xd, res)
+    assert rel(y, x + plain.mlp_part(x, {"c_fc.weight": w["m.c_fc.weight"], "c_fc.bias": w["m.c_fc.bias"],
+                                         "c_proj.weight": w["m.c_proj.weight"], "c_proj.bias": w["m.c_proj.bias"]},
+                                     "")) <= tol
+
+    # attention over pages: two requests, the second continuing at position 21 of a longer one
+    H, Dh, page = 5, 16, 16
+    att = Attention("a", D, H, Dh, stored="in_out")
+    w = bind(att, dtype, seed=3)
+    wd = {k[2:]: v for k, v in w.items()}
+    positions = torch.arange(T, dtype=torch.int32).cuda()
+    token_req = torch.zeros(T, dtype=torch.int32).cuda()
+    bt = torch.tensor([[3, 0, 2, 1]], dtype=torch.int32).cuda()
+    cache = LayerCacheView("kv", True, k=torch.zeros(4, H, page, Dh, dtype=dtype, device="cuda"),
+                           v=torch.zeros(4, H, page, Dh, dtype=dtype, device="cuda"), block_table=bt, page_size=page)
+    ctx = part_ctx(T, positions, token_req)
+    res = xd.clone()
+    y = att.forward(ctx, xd, res, cache)
+    assert rel(y, x + plain.attention_part(x, wd, "", H)) <= tol
+    # the same tokens in two steps give the same rows
+    cache.k.zero_(); cache.v.zero_()
+    ya = att.forward(part_ctx(21, positions[:21], token_req[:21]), xd[:21], xd[:21].clone(), cache).clone()
+    yb = att.forward(part_ctx(T - 21, positions[21:], token_req[21:]), xd[21:], xd[21:].clone(), cache)
+    assert rel(torch.cat([ya, yb]), y) <= tol
+
+    blk = PreNormBlock(LayerNorm("b.ln_1", D, 1e-5), Attention("b.attn", D, H, Dh, stored="in_out"),
+                       LayerNorm("b.ln_2", D, 1e-5), MLP("b.mlp", D, 100, stored="in_out"))
+    w = bind(blk, dtype, seed=4)
+    cache.k.zero_(); cache.v.zero_()
+    y = blk.forward(ctx, xd.clone(), cache)
+    wd = {"h.0." + k[2:]: v for k, v in w.items()}
+    assert rel(y, plain.block(x, wd, 0, {"layer_norm_epsilon": 1e-5, "n_head": H})) <= tol
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("config,seed", [(CONFIG_A, 3), (CONFIG_B, 4)])
+def test_long_decoding_and_first_tokens(dtype, config, seed, tmp_path):
+    """Every position of the longest sequence the model allows, one token per step."""
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.weights import load_model
+    weights = make_model_dir(str(tmp_path), config, seed, peaky=6.0)
+    model, _ = load_model(str(tmp_path), dtype=dtype)
+    n = config["n_positions"]
+    toks = random_tokens(n, config["vocab_size"], seed)
+    ref = plain.logits(toks, weights, config)
+    eng = Engine(model, page_size=16, n_pages=n // 16, max_requests=1)
+    eng.add_request("r")
+    worst = 0.0
+    for t in range(n):
+        lg = eng.step([StepEntry("r", toks[t:t + 1], [0])])
+        worst = max(worst, rel(lg[0], ref[t]))
+        if t < 3:
+            assert rel(lg[0], ref[t]) <= TOL[dtype], f"position {t}"
+    eng.check_status()
+    assert worst <= TOL[dtype]
+    with pytest.raises(ValueError):
+        eng.step([StepEntry("r", [0], [0])])          # position n is beyond the table
+    eng.finish("r")
+    assert eng.cache.pages_in_use() == [0]
+
+
+def test_step_refuses_bad_input(tmp_path):
+    from mlx_lm_b200.cache import OutOfPages
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.weights import load_model
+    make_model_dir(str(tmp_path), CONFIG_A, 0)
+    model, _ = load_model(str(tmp_path), dtype="float32")
+    eng = Engine(model, page_size=16, n_pages=2, max_requests=2)
+    eng.add_request(1)
+    with pytest.raises(ValueError):
+        eng.step([StepEntry(1, [512], [0])])
+    with pytest.raises(ValueError):
+        eng.step([StepEntry(1, [1, 2], [2])])
+    with pytest.raises(KeyError):
+        eng.step([StepEntry(2, [1], [0])])
+    with pytest.raises(ValueError):
+        eng.step([StepEntry(1, [1], [0]), StepEntry(1, [2], [0])])
+    with pytest.raises(OutOfPages):
+        eng.step([StepEntry(1, list(range(33)), [0])])
+    assert eng.cache.pages_in_use() == [0]
+    assert eng.step([StepEntry(1, [1, 2, 3], [])]) is None
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_entry_points(dtype, tmp_path):
+    from mlx_lm_b200 import batch_generate, generate, load, stream_generate
+    config = dict(CONFIG_A, ln_gain_std=0.3)
+    weights = make_model_dir(str(tmp_path), config, 5, peaky=10.0)
+    model, tokenizer = load(str(tmp_path), dtype=dtype)
+    prompts = [random_tokens(7, 512, 0), random_tokens(13, 512, 1)]
+    want = [plain.greedy_generate(p, 16, weights, config) for p in prompts]
+
+    def agrees(got, ref, prompt):
+        """Equal, or different first where the plain model's two best logits are closer than the dtype resolves."""
+        for i, (a, b) in enumerate(zip(got, ref)):
+            if a != b:
+                lg = plain.logits(prompt + ref[:i], weights, config)[-1]
+                top = torch.topk(lg, 2).values
+                return dtype == "bfloat16" and float(top[0] - top[1]) < 0.05 * float(lg.abs().max())
+        return len(got) == len(ref)
+
+    for p, w in zip(prompts, want):
+        text = generate(model, tokenizer, p, max_tokens=16)
+        got = [int(t) for t in text.split()]
+        assert agrees(got, w, p), (got, w)
+        streamed = list(stream_generate(model, tokenizer, " ".join(map(str, p)), max_tokens=16))
+        assert [r.token for r in streamed] == got and streamed[-1].finish_reason == "length"
+        assert streamed[-1].generation_tokens == 16 and streamed[0].prompt_tokens == len(p)
+    out = batch_generate(model, tokenizer, prompts, max_tokens=16, return_token_ids=True, return_logprobs=True)
+    for got, w, p in zip(out.token_ids, want, prompts):
+        assert agrees(got, w, p)
+    assert out.stats.generation_tokens == 32 and out.stats.prompt_tokens == 20
+    assert all(len(l) == 16 and all(x <= 0 for x in l) for l in out.logprobs)
+    # an end-of-sequence token stops a request and is not part of its output
+    tokenizer.add_eos_token(want[0][5])
+    text = generate(model, tokenizer, prompts[0], max_tokens=16)
+    first = want[0].index(want[0][5])
+    assert [int(t) for t in text.split()] == want[0][:first]
+
+
+def test_temperature_sampling_does_not_depend_on_batching(tmp_path):
+    from mlx_lm_b200 import load
+    from mlx_lm_b200.generate import BatchGenerator
+    from mlx_lm_b200.sampling import make_logits_processors, make_sampler
+    make_model_dir(str(tmp_path), CONFIG_B, 1)
+    model, _ = load(str(tmp_path), dtype="float32")
+    prompts = [random_tokens(n, 1000, n) for n in (5, 31, 64)]
+
+    def run(**kw):
+        gen = BatchGenerator(model, max_tokens=24, sampler=make_sampler(0.8, top_p=0.95), seed=1,
+                             logits_processors=make_logits_processors(repetition_penalty=1.1), **kw)
+        uids = gen.insert(prompts)
+        out = {u: [] for u in uids}
+        while gen.scheduler.has_work():
+            for r in gen.next_generated():
+                out[r.uid].append(r.token)
+        return [out[u] for u in uids]
+
+    together = run(completion_batch_size=8, prefill_batch_size=8)
+    one_by_one = run(completion_batch_size=1, prefill_batch_size=1)
+    small_steps = run(completion_batch_size=2, prefill_batch_size=1, prefill_step_size=7, max_tokens_per_step=9)
+    assert together == one_by_one == small_steps
+    assert all(len(t) == 24 for t in together) and len({tuple(t) for t in together}) == 3
+
+
+def test_scheduler_preempts_and_recomputes_on_the_gpu(tmp_path):
+    """A pool too small for all requests at once: some are preempted and recomputed, and every
+    request still gets the tokens it gets when it runs alone."""
+    from mlx_lm_b200 import load
+    from mlx_lm_b200.generate import BatchGenerator, get_engine
+    config = dict(CONFIG_A, ln_gain_std=0.3)
+    weights = make_model_dir(str(tmp_path), config, 6, peaky=10.0)
+    model, _ = load(str(tmp_path), dtype="float32")
+    prompts = [random_tokens(30, 512, 10 + i) for i in range(3)]
+    want = [plain.greedy_generate(p, 20, weights, config) for p in prompts]
+    engine = get_engine(model, page_size=16, num_pages=6, max_requests=4)
+    gen = BatchGenerator(model, max_tokens=20, engine=engine, completion_batch_size=3, prefill_batch_size=3)
+    uids = gen.insert(prompts)
+    out = {u: [] for u in uids}
+    while gen.scheduler.has_work():
+        for r in gen.next_generated():
+            out[r.uid].append(r.token)
+    assert gen.scheduler.stats.preemptions > 0
+    assert [out[u] for u in uids] == want
+    assert engine.cache.pages_in_use() == [0]
+
+
+# ----------------------------------------------------------------------------------------------
+# A mixer with state of its own, defined here: y_t = mean of x_0..x_t of the request, projected.
+
+def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(tmp_path):
+    from mlx_lm_b200.config import BaseModelArgs, register_architecture
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.parts import (MLP, Attention, Init, LayerNorm, Linear, Mixer, ModelDescription, NoPosition,
+                                   OutputHead, PreNormBlock, RunEntry, StateSpec, TokenEmbedding, register_part)
+    from mlx_lm_b200.weights import load_model, write_random_model
+    from safetensors.torch import load_file
+
+    class RunningMean(Mixer):
+        """State per request: [sum of inputs (width) | count]."""
+
+        def __init__(self, name, width):
+            self.name, self.width = name, width
+            self.proj = Linear(f"{name}.proj", width, width, bias=False, init=Init(0.0, 0.2))
+
+        def children(self):
+            return (self.proj,)
+
+        def cache_spec(self):
+            return StateSpec((self.width + 1,))
+
+        def forward(self, ctx, x, residual, cache):
+            y = torch.empty_like(x)
+            for s in ctx.spans:       # a request's tokens in order; the state carries over between steps
+                st = cache.state[s.slot]
+                xs = x[s.first_token:s.first_token + s.n_tokens].float()
+                sums = st[:self.width] + torch.cumsum(xs, 0)
+                counts = st[self.width] + torch.arange(1, s.n_tokens + 1, device=x.device)
+                y[s.first_token:s.first_token + s.n_tokens] = (sums / counts[:, None]).to(x.dtype)
+                if cache.write:
+                    st[:self.width] = sums[-1]
+                    st[self.width] = counts[-1]
+            return self.proj.forward(ctx, y, residual, residual=residual)
+
+    register_part("mixer", "running_mean", RunningMean, replace=True)
+
+    @dataclass
+    class ToyArgs(BaseModelArgs):
+        model_type: str
+        width: int
+        vocab_size: int
+        mixers: list
+
+    def build(a):
+        emb = TokenEmbedding("emb", a.vocab_size, a.width, init=Init(0.0, 0.5))
+        blocks = []
+        for i, kind in enumerate(a.mixers):       # the configuration chooses the mixer layer by layer
+            mixer = (RunningMean(f"l{i}.mix", a.width) if kind == "running_mean" else
+                     Attention(f"l{i}.mix", a.width, 2, a.width // 2, qkv_name="qkv", out_name="out",
+                               init=Init(0.0, 0.2)))
+            blocks.append(PreNormBlock(LayerNorm(f"l{i}.n1", a.width, 1e-5), mixer, LayerNorm(f"l{i}.n2", a.width, 1e-5),
+                                       MLP(f"l{i}.ff", a.width, 3 * a.width, up_name="up", down_name="down",
+                                           init=Init(0.0, 0.2))))
+        # block 0 runs twice; its second run reads and extends the same state
+        order = [RunEntry(0)] + [RunEntry(i) for i in range(1, len(blocks))] + [RunEntry(0)]
+        return ModelDescription("toy_state", a.width, a.vocab_size, emb, NoPosition(), blocks,
+                                LayerNorm("nf", a.width, 1e-5), OutputHead(a.vocab_size, a.width, tied_to=emb),
+                                order=order, args=a)
+
+    register_architecture("toy_state", ToyArgs, build, replace=True)
+    cfg = dict(model_type="toy_state", width=32, vocab_size=97, mixers=["running_mean", "attention", "running_mean"])
+    write_random_model(str(tmp_path), cfg, seed=3)
+    w = {k: v.float() for k, v in load_file(str(tmp_path / "model.safetensors")).items()}
+
+    def plain_toy(tokens):
+        def ln(x, n):
+            return plain.layer_norm(x, w[n + ".weight"], w[n + ".bias"], 1e-5)
+
+        def ff(x, n):
+            return plain.gelu_new(x @ w[n + ".up.weight"].T + w[n + ".up.bias"]) @ w[n + ".down.weight"].T \
+                + w[n + ".down.bias"]
+
+        def mean_mix(x, n, state):
+            sums = state[0] + torch.cumsum(x, 0)
+            counts = state[1] + torch.arange(1, len(x) + 1)
+            state[0], state[1] = sums[-1], counts[-1]
+            return (sums / counts[:, None]) @ w[n + ".proj.weight"].T
+
+        def attn(x, n):
+            qkv = x @ w[n + ".qkv.weight"].T + w[n + ".qkv.bias"]
+            q, k, v = plain.split_heads(qkv, 2)
+            return plain.causal_attention(q, k, v) @ w[n + ".out.weight"].T + w[n + ".out.bias"]
+
+        x = w["emb.weight"][torch.tensor(tokens)]
+        states = {0: [torch.zeros(32), torch.zeros(())], 2: [torch.zeros(32), torch.zeros(())]}
+        for i in (0, 1, 2, 0):
+            h = ln(x, f"l{i}.n1")
+            x = x + (attn(h, f"l{i}.mix") if i == 1 else mean_mix(h, f"l{i}.mix", states[i]))
+            x = x + ff(ln(x, f"l{i}.n2"), f"l{i}.ff")
+        return ln(x, "nf") @ w["emb.weight"].T
+
+    # block 0 runs twice per step on a running state, so whole-sequence and stepped runs differ by
+    # construction; the plain model is therefore run with the same cutting as the engine
+    model, _ = load_model(str(tmp_path), dtype="float32")
+    eng = Engine(model, page_size=16, n_pages=8, max_requests=3, max_len=64)
+    assert [g.cache_ids for g in eng.cache.state_groups] == [[0, 2]] and [g.cache_ids for g in eng.cache.kv_groups] == [[1]]
+    toks = random_tokens(40, 97, 0)
+    eng.add_request("a")
+    got = eng.step([StepEntry("a", toks, list(range(40)))]).clone()
+    assert rel(got, plain_toy(toks)) <= 5e-5
+    eng.finish("a")
+    # a second request re-uses the slot: its state must start from zero again
+    eng.add_request("b")
+    assert rel(eng.step([StepEntry("b", toks[:9], list(range(9)))]), plain_toy(toks[:9])) <= 5e-5
+    eng.finish("b")
+    # layers 1 and 2 alone (single runs) are cut-invariant: a model without the repeated block
+    cfg2 = dict(cfg, mixers=["attention", "running_mean"])
+
+    def build2(a):
+        d = build(a)
+        d.order = [RunEntry(i) for i in range(len(d.blocks))]
+        return d
+
+    register_architecture("toy_state2", ToyArgs, build2, replace=True)
+    d2 = tmp_path / "m2"
+    write_random_model(str(d2), dict(cfg2, model_type="toy_state2"), seed=4)
+    model2, _ = load_model(str(d2), dtype="float32")
+    eng2 = Engine(model2, page_size=16, n_pages=8, max_requests=3, max_len=64)
+    eng2.add_request("w"); eng2.add_request("c"); eng2.add_request("o")
+    whole = eng2.step([StepEntry("w", toks, list(range(40)))]).clone()
+    other = random_tokens(12, 97, 9)
+    rows = []
+    rows.append(eng2.step([StepEntry("c", toks[:7], list(range(7))), StepEntry("o", other[:5], [])]).clone())
+    rows.append(eng2.step([StepEntry("o", other[5:6], []), StepEntry("c", toks[7:9], [0, 1])]).clone())
+    rows.append(eng2.step([StepEntry("c", toks[9:40], list(range(31)))]).clone())
+    assert rel(torch.cat(rows), whole) <= 5e-5

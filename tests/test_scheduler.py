@@ -1,0 +1,179 @@
+"""The scheduler's decisions, driven without a device: a fake engine with the real cache manager
+and a fake sampler whose token is a function of (request, position) only, so that any way of
+batching, cutting and preempting must produce the same tokens."""
+import pytest
+
+from mlx_lm_b200.cache import CacheManager, OutOfPages
+from mlx_lm_b200.engine.scheduler import Scheduler, StopSequenceMatcher
+from mlx_lm_b200.parts import PagedKVSpec
+
+
+class FakeEngine:
+    def __init__(self, n_pages, page_size=16, max_requests=8, max_len=256):
+        self.cache = CacheManager({0: PagedKVSpec(2, 16, None)}, page_size=page_size, n_pages=n_pages,
+                                  max_requests=max_requests, max_len=max_len)
+        self.max_len = max_len
+        self.steps = []          # per step: list of (rid, start position, n tokens, wants)
+        self.fed = {}            # rid -> tokens fed since its last admission
+
+    def add_request(self, rid):
+        self.cache.add_request(rid)
+        self.fed[rid] = []
+
+    def finish(self, rid):
+        self.cache.release(rid)
+
+    def step(self, entries):
+        rec, rows = [], []
+        for e in entries:
+            start = self.cache.reserve(e.rid, len(e.tokens))
+            assert start == len(self.fed[e.rid]), "tokens must continue where the cache ends"
+            self.fed[e.rid].extend(e.tokens)
+            rec.append((e.rid, start, len(e.tokens), list(e.want)))
+            rows.extend((e.rid, start + w) for w in e.want)
+        for e in entries:
+            self.cache.commit(e.rid)
+        self.cache.check()
+        self.steps.append(rec)
+        return rows
+
+
+def token_fn(uid, position):
+    return (uid * 7919 + position * 104729) % 1000
+
+
+def fake_sample(rows, requests):
+    assert [r.uid for r in requests] == [rid for rid, _ in rows]
+    return [token_fn(rid, pos + 1) for rid, pos in rows], [0.0] * len(rows)
+
+
+def run(sched, limit=10000):
+    out, reasons = {}, {}
+    n = 0
+    while sched.has_work():
+        _, gens = sched.next()
+        for r in gens:
+            out.setdefault(r.uid, []).append(r.token)
+            if r.finish_reason:
+                reasons[r.uid] = r.finish_reason
+        n += 1
+        assert n < limit, "the scheduler does not finish"
+    return out, reasons
+
+
+def expected(uid, prompt_len, n):
+    return [token_fn(uid, prompt_len + i) for i in range(n)]
+
+
+def test_single_request_is_cut_under_the_budget():
+    eng = FakeEngine(n_pages=16)
+    s = Scheduler(eng, fake_sample, prefill_step_size=40, max_tokens_per_step=64)
+    uid = s.insert(list(range(100)), max_tokens=5)
+    out, reasons = run(s)
+    assert out[uid] == expected(uid, 100, 5) and reasons[uid] == "length"
+    sizes = [e[2] for step in eng.steps for e in step]
+    assert sizes == [40, 40, 20, 1, 1, 1, 1]
+    wants = [e[3] for step in eng.steps for e in step]
+    assert wants[:3] == [[], [], [19]]         # logits only where the prompt ends
+    assert eng.cache.pages_in_use() == [0]
+
+
+def test_decode_first_then_prompts_fill_the_budget():
+    eng = FakeEngine(n_pages=64)
+    s = Scheduler(eng, fake_sample, max_requests=4, max_prefilling=2, prefill_step_size=32, max_tokens_per_step=40)
+    a = s.insert(list(range(10)), max_tokens=30)
+    s.next()                                   # a is decoding from now on
+    b = s.insert(list(range(70)), max_tokens=3)
+    c = s.insert(list(range(50)), max_tokens=3)
+    s.next()
+    step = eng.steps[-1]
+    assert step[0][:3] == (a, 10, 1)           # the decoding request first, one token
+    assert step[1][:3] == (b, 0, 32)           # then a portion of the oldest prompt
+    assert step[2][:3] == (c, 0, 7)            # and what is left of the budget: 40 - 1 - 32
+    out, reasons = run(s)
+    assert out[b] == expected(b, 70, 3) and out[c] == expected(c, 50, 3)
+    assert len(out[a]) + 2 == 30 or len(out[a]) == 28
+    assert all(sum(e[2] for e in st) <= 40 for st in eng.steps)
+
+
+def test_admission_limits():
+    eng = FakeEngine(n_pages=64, max_requests=8)
+    s = Scheduler(eng, fake_sample, max_requests=3, max_prefilling=1, prefill_step_size=16, max_tokens_per_step=64)
+    uids = [s.insert(list(range(40)), max_tokens=4) for _ in range(5)]
+    s.next()
+    assert len(s.running) == 1                 # one request in its prompt at a time
+    out, reasons = run(s)
+    assert max(len(st) for st in eng.steps) <= 3
+    for u in uids:
+        assert out[u] == expected(u, 40, 4)
+
+
+def test_batch_equals_single_and_per_request_max_tokens():
+    prompts = [list(range(5 + 9 * i)) for i in range(6)]
+    max_tokens = [3, 9, 1, 12, 5, 7]
+    eng = FakeEngine(n_pages=64)
+    s = Scheduler(eng, fake_sample, max_requests=3, max_prefilling=2, prefill_step_size=8, max_tokens_per_step=20)
+    uids = [s.insert(p, m) for p, m in zip(prompts, max_tokens)]
+    out, reasons = run(s)
+    for u, p, m in zip(uids, prompts, max_tokens):
+        assert out[u] == expected(u, len(p), m) and reasons[u] == "length"
+    assert eng.cache.pages_in_use() == [0] and not eng.cache.requests
+
+
+def test_stop_sequence_and_remove():
+    eng = FakeEngine(n_pages=32)
+    s = Scheduler(eng, fake_sample)
+    want = expected(0, 6, 10)
+    stop = StopSequenceMatcher([[want[3], want[4]], [99999]])
+    a = s.insert(list(range(6)), 10, stop=stop)
+    b = s.insert(list(range(9)), 50)
+    out = {}
+    for _ in range(3):
+        for r in s.next()[1]:
+            out.setdefault(r.uid, []).append(r)
+    s.remove([b])
+    assert eng.cache.pages_in_use()[0] > 0 and b not in eng.cache.requests
+    while s.has_work():
+        for r in s.next()[1]:
+            out.setdefault(r.uid, []).append(r)
+    assert [r.token for r in out[a]] == want[:5] and out[a][-1].finish_reason == "stop"
+    assert out[a][-1].all_tokens == list(range(6)) + want[:5]
+    assert len(out[b]) == 3 and eng.cache.pages_in_use() == [0]
+
+
+def test_pages_run_out_newest_request_is_recomputed():
+    # 6 pages of 16: three requests of 30 prompt tokens take 2 pages each; decoding past 32 needs a third
+    eng = FakeEngine(n_pages=6)
+    s = Scheduler(eng, fake_sample, max_requests=3, max_prefilling=3, prefill_step_size=64, max_tokens_per_step=128)
+    uids = [s.insert(list(range(100 * i, 100 * i + 30)), max_tokens=20) for i in range(3)]
+    out, reasons = run(s)
+    assert s.stats.preemptions > 0
+    for i, u in enumerate(uids):
+        assert out[u] == expected(u, 30, 20), "a recomputed request must continue with the same tokens"
+        assert reasons[u] == "length"
+    # a preempted request came back with prompt + generated tokens in one or more portions from position 0
+    restarts = [e for st in eng.steps for e in st if e[1] == 0]
+    assert len(restarts) > 3
+    assert eng.cache.pages_in_use() == [0]
+    # the oldest request is never the victim: it starts from position 0 exactly once
+    assert sum(1 for e in restarts if e[0] == uids[0]) == 1
+
+
+def test_request_that_can_never_fit_is_refused():
+    eng = FakeEngine(n_pages=4)
+    s = Scheduler(eng, fake_sample)
+    with pytest.raises(ValueError):
+        s.insert(list(range(60)), max_tokens=10)      # 69 positions = 5 pages > 4
+    with pytest.raises(ValueError):
+        s.insert(list(range(250)), max_tokens=10)     # beyond the model's positions
+    with pytest.raises(ValueError):
+        s.insert([], max_tokens=1)
+    u = s.insert(list(range(60)), max_tokens=5)       # 64 positions = 4 pages: fits alone
+    out, _ = run(s)
+    assert out[u] == expected(u, 60, 5)
+
+
+def test_stop_matcher():
+    m = StopSequenceMatcher([[1, 2, 3], [7]])
+    assert not m.matches([1, 2]) and m.matches([0, 1, 2, 3]) and m.matches([7]) and not m.matches([7, 1])
+    assert not StopSequenceMatcher().matches([1])
