@@ -14,6 +14,18 @@
 //            float32; keys are visited in order 32 at a time, so the result
 //            for a token does not depend on what else is in the batch or on
 //            how the request's tokens were cut into steps.
+//
+// attention_decode / attention_combine  (single-token rows: decode steps)
+//            A row has one query but hundreds of keys, and a small batch has too
+//            few (row, head) pairs to fill 148 SMs, so the keys are cut into
+//            chunks of a fixed number of positions.  One CTA per (chunk, head,
+//            row) streams its keys and values once with 16-byte loads (Dh/8
+//            threads side by side on one key, so a warp reads contiguous
+//            runs), keeps a running (max, sum, weighted values) per thread
+//            group, merges the groups, and writes one partial (m, l, o[Dh]) to
+//            scratch memory.  The combine kernel folds a row's partials in
+//            chunk order.  The chunk length is a constant of the engine, not
+//            of the batch, so a row's result does not depend on its neighbours.
 #include "common.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
@@ -58,12 +70,14 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, const int* __restrict
                          const int* __restrict__ token_req, const int* __restrict__ block_table,
                          int max_pages, int n_pages, int page, int Hq, int Hkv, int Dh, int window,
                          float scale, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
-                         T* __restrict__ out, int ldo, int n_tokens, int* __restrict__ status) {
+                         T* __restrict__ out, int ldo, const int* __restrict__ rows, int n_tokens,
+                         int* __restrict__ status) {
   extern __shared__ float sq[];  // [warps][Dh]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int w = blockIdx.x * (blockDim.x >> 5) + warp;
   if (w >= n_tokens * Hq) return;
-  const int t = w / Hq, h = w - t * Hq;
+  const int ti = w / Hq, h = w - ti * Hq;
+  const int t = rows ? rows[ti] : ti;
   const int hk = h / (Hq / Hkv);
   const int p = positions[t];
   const int r = token_req[t];
@@ -151,12 +165,13 @@ MLXB_EXPORT int mlxb_kv_write(int dtype, const void* k_src, const void* v_src, i
   return mlxb_check_launch("kv_write");
 }
 
-// q: [n_tokens, >= Hq*Dh] at row stride ldq; out: [n_tokens, Hq*Dh] at row stride ldo.
-// window <= 0: all keys 0..p.
+// q: [*, >= Hq*Dh] at row stride ldq; out: [*, Hq*Dh] at row stride ldo; rows: int32[n_tokens] token indices to
+// process, or null for tokens 0..n_tokens-1.  window <= 0: all keys 0..p.
 MLXB_EXPORT int mlxb_attention_generic(int dtype, const void* q, int ldq, const int* positions, const int* token_req,
                                        const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                                        int Dh, int window, float scale, const void* k_pool, const void* v_pool,
-                                       void* out, int ldo, int n_tokens, int* status, cudaStream_t stream) {
+                                       void* out, int ldo, const int* rows, int n_tokens, int* status,
+                                       cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (int e = check_common("attention", page, Hq, Hkv, Dh)) return e;
   const int warps = 4;
@@ -166,12 +181,230 @@ MLXB_EXPORT int mlxb_attention_generic(int dtype, const void* q, int ldq, const 
   if (dtype == MLXB_F32)
     attention_generic_kernel<float><<<blocks, warps * 32, smem, stream>>>(
         (const float*)q, ldq, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, Dh, window, scale,
-        (const float*)k_pool, (const float*)v_pool, (float*)out, ldo, n_tokens, status);
+        (const float*)k_pool, (const float*)v_pool, (float*)out, ldo, rows, n_tokens, status);
   else if (dtype == MLXB_BF16)
     attention_generic_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
         (const __nv_bfloat16*)q, ldq, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, Dh, window,
-        scale, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, ldo, n_tokens, status);
+        scale, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, ldo, rows, n_tokens,
+        status);
   else
     return mlxb_fail(MLXB_BAD_DTYPE, "attention: dtype code %d", dtype);
   return mlxb_check_launch("attention (generic)");
+}
+
+
+// ---------------------------------------------------------------- single-token rows
+
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float (&v)[8]);
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[8]) {
+  const uint4 u = *reinterpret_cast<const uint4*>(p);
+  const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
+  const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+
+constexpr int DEC_THREADS = 128;
+constexpr int DEC_UNROLL = 4;
+
+// partial: float [n_rows][Hq][n_chunks_max][Dh + 2] = (m, l, o[Dh]) per chunk.
+template <typename T, int TPK>
+__global__ void __launch_bounds__(DEC_THREADS)
+attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict__ rows,
+                        const int* __restrict__ positions, const int* __restrict__ token_req,
+                        const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
+                        int Dh, int window, float scale, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
+                        float* __restrict__ partial, int n_chunks_max, int chunk, int* __restrict__ status) {
+  constexpr int GROUPS = DEC_THREADS / TPK;
+  extern __shared__ float sm[];   // m[GROUPS] | l[GROUPS] | o[GROUPS][Dh]
+  const int c = blockIdx.x, h = blockIdx.y, ri = blockIdx.z;
+  const int t = rows ? rows[ri] : ri;
+  const int r = token_req[t];
+  if (r < 0) return;
+  const int p = positions[t];
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int k_begin = max(lo, c * chunk), k_end = min(p + 1, (c + 1) * chunk);
+  if (k_begin >= k_end) return;
+  const int hk = h / (Hq / Hkv);
+  const int grp = threadIdx.x / TPK, j = threadIdx.x % TPK;
+  const int d0 = 8 * j;
+  const bool active = d0 < Dh;
+  const int* bt = block_table + (size_t)r * max_pages;
+  const int shift = __ffs(page) - 1;
+
+  float qv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) qv[i] = 0.f;
+  if (active) {
+    load8<T>(q + (size_t)t * ldq + h * Dh + d0, qv);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) qv[i] *= scale;
+  }
+  float m = -INFINITY, l = 0.f, o[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = 0.f;
+
+  const int n_keys = k_end - k_begin;
+  const int iters = (n_keys + GROUPS * DEC_UNROLL - 1) / (GROUPS * DEC_UNROLL);
+  for (int it = 0; it < iters; ++it) {
+    float kv[DEC_UNROLL][8], vv[DEC_UNROLL][8];
+    bool ok[DEC_UNROLL];
+#pragma unroll
+    for (int u = 0; u < DEC_UNROLL; ++u) {
+      const int key = k_begin + (it * DEC_UNROLL + u) * GROUPS + grp;
+      ok[u] = key < k_end;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { kv[u][i] = 0.f; vv[u][i] = 0.f; }
+      if (ok[u]) {
+        const int lp = key >> shift;
+        const int pg = lp < max_pages ? bt[lp] : -1;
+        if (pg < 0 || pg >= n_pages) {
+          if (j == 0) atomicOr(status, pg < 0 ? MLXB_ST_POSITION_RANGE : MLXB_ST_PAGE_RANGE);
+          ok[u] = false;
+        } else if (active) {
+          const size_t off = (((size_t)pg * Hkv + hk) * page + (key & (page - 1))) * Dh + d0;
+          load8<T>(k_pool + off, kv[u]);
+          load8<T>(v_pool + off, vv[u]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < DEC_UNROLL; ++u) {
+      float s = 0.f;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s = fmaf(qv[i], kv[u][i], s);
+#pragma unroll
+      for (int w = TPK / 2; w > 0; w >>= 1) s += __shfl_xor_sync(0xffffffffu, s, w);
+      if (ok[u]) {
+        const float m_new = fmaxf(m, s);
+        const float corr = expf(m - m_new);   // exp(-inf) = 0 on the first key
+        const float pw = expf(s - m_new);
+        l = l * corr + pw;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = fmaf(pw, vv[u][i], o[i] * corr);
+        m = m_new;
+      }
+    }
+  }
+
+  float* sm_m = sm;
+  float* sm_l = sm + GROUPS;
+  float* sm_o = sm + 2 * GROUPS;
+  if (j == 0) { sm_m[grp] = m; sm_l[grp] = l; }
+  if (active) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm_o[grp * Dh + d0 + i] = o[i];
+  }
+  __syncthreads();
+  float M = -INFINITY;
+  for (int g2 = 0; g2 < GROUPS; ++g2) M = fmaxf(M, sm_m[g2]);
+  float* dst = partial + (((size_t)ri * Hq + h) * n_chunks_max + c) * (Dh + 2);
+  for (int d = threadIdx.x; d < Dh; d += DEC_THREADS) {
+    float acc = 0.f;
+    for (int g2 = 0; g2 < GROUPS; ++g2) {
+      const float w = sm_m[g2] == -INFINITY ? 0.f : expf(sm_m[g2] - M);
+      acc = fmaf(w, sm_o[g2 * Dh + d], acc);
+    }
+    dst[2 + d] = acc;
+  }
+  if (threadIdx.x == 0) {
+    float L = 0.f;
+    for (int g2 = 0; g2 < GROUPS; ++g2) L += sm_m[g2] == -INFINITY ? 0.f : sm_l[g2] * expf(sm_m[g2] - M);
+    dst[0] = M;
+    dst[1] = L;
+  }
+}
+
+template <typename T>
+__global__ void attention_combine_kernel(const float* __restrict__ partial, const int* __restrict__ rows,
+                                         const int* __restrict__ positions, const int* __restrict__ token_req,
+                                         int Hq, int Dh, int window, int n_chunks_max, int chunk,
+                                         T* __restrict__ out, int ldo) {
+  const int h = blockIdx.x, ri = blockIdx.y;
+  const int t = rows ? rows[ri] : ri;
+  if (token_req[t] < 0) return;
+  const int p = positions[t];
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int c0 = lo / chunk, c1 = p / chunk;
+  const float* src = partial + ((size_t)ri * Hq + h) * n_chunks_max * (Dh + 2);
+  float M = -INFINITY;
+  for (int c = c0; c <= c1; ++c) M = fmaxf(M, src[(size_t)c * (Dh + 2)]);
+  float L = 0.f;
+  for (int c = c0; c <= c1; ++c) L += src[(size_t)c * (Dh + 2) + 1] * expf(src[(size_t)c * (Dh + 2)] - M);
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
+    float acc = 0.f;
+    for (int c = c0; c <= c1; ++c)
+      acc = fmaf(expf(src[(size_t)c * (Dh + 2)] - M), src[(size_t)c * (Dh + 2) + 2 + d], acc);
+    out[(size_t)t * ldo + h * Dh + d] = from_f<T>(acc * inv);
+  }
+}
+
+template <typename T>
+static int launch_decode(const void* q, int ldq, const int* rows, const int* positions, const int* token_req,
+                         const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv, int Dh,
+                         int window, float scale, const void* k_pool, const void* v_pool, float* partial,
+                         int n_chunks_max, int chunk, void* out, int ldo, int n_rows, int* status,
+                         cudaStream_t stream) {
+  const int chunks8 = (Dh + 7) / 8;
+  int tpk = 2;
+  while (tpk < chunks8) tpk <<= 1;
+  const dim3 grid(n_chunks_max, Hq, n_rows);
+#define DEC(TPK_)                                                                                                    \
+  {                                                                                                                  \
+    const size_t smem = (size_t)(DEC_THREADS / TPK_) * (Dh + 2) * sizeof(float);                                     \
+    attention_decode_kernel<T, TPK_><<<grid, DEC_THREADS, smem, stream>>>(                                           \
+        (const T*)q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, Dh, window,    \
+        scale, (const T*)k_pool, (const T*)v_pool, partial, n_chunks_max, chunk, status);                            \
+  }
+  if (tpk == 2) DEC(2) else if (tpk == 4) DEC(4) else if (tpk == 8) DEC(8) else if (tpk == 16) DEC(16) else DEC(32)
+#undef DEC
+  if (int e = mlxb_check_launch("attention (single-token rows)")) return e;
+  const int threads = Dh <= 32 ? 32 : (Dh <= 64 ? 64 : 128);
+  attention_combine_kernel<T><<<dim3(Hq, n_rows), threads, 0, stream>>>(partial, rows, positions, token_req, Hq, Dh,
+                                                                        window, n_chunks_max, chunk, (T*)out, ldo);
+  return mlxb_check_launch("attention combine");
+}
+
+// Floats of scratch that n_rows rows need.
+MLXB_EXPORT long long mlxb_attention_decode_scratch(int n_rows, int Hq, int Dh, int n_chunks_max) {
+  return (long long)n_rows * Hq * n_chunks_max * (Dh + 2);
+}
+
+// Rows with one query each.  rows: int32[n_rows] token indices or null (tokens 0..n_rows-1).
+// n_chunks_max * chunk must cover every position a row may have; partial: float32 scratch of
+// mlxb_attention_decode_scratch() floats, contents need not be initialised.
+// Dh must be a multiple of 8 (16 for bfloat16 alignment is implied by pages); q rows 16-byte aligned.
+MLXB_EXPORT int mlxb_attention_decode(int dtype, const void* q, int ldq, const int* rows, const int* positions,
+                                      const int* token_req, const int* block_table, int max_pages, int n_pages,
+                                      int page, int Hq, int Hkv, int Dh, int window, float scale, const void* k_pool,
+                                      const void* v_pool, float* partial, int n_chunks_max, int chunk, void* out,
+                                      int ldo, int n_rows, int* status, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (int e = check_common("attention (single-token rows)", page, Hq, Hkv, Dh)) return e;
+  if (Dh % 8) return mlxb_fail(MLXB_BAD_ARG, "attention (single-token rows): head size %d is not a multiple of 8", Dh);
+  if (chunk <= 0 || n_chunks_max <= 0 || n_chunks_max > 65535 || n_rows > 65535 || Hq > 65535)
+    return mlxb_fail(MLXB_BAD_ARG, "attention (single-token rows): chunk %d x %d, %d rows, %d heads", chunk,
+                     n_chunks_max, n_rows, Hq);
+  const int esz = dtype == MLXB_F32 ? 4 : 2;
+  if (((uintptr_t)q & 15) || ((size_t)ldq * esz) % 16 || ((size_t)Dh * esz) % 16)
+    return mlxb_fail(MLXB_BAD_ARG, "attention (single-token rows): query rows and heads must be 16-byte aligned");
+  if (dtype == MLXB_F32)
+    return launch_decode<float>(q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv,
+                                Dh, window, scale, k_pool, v_pool, partial, n_chunks_max, chunk, out, ldo, n_rows,
+                                status, stream);
+  if (dtype == MLXB_BF16)
+    return launch_decode<__nv_bfloat16>(q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page, Hq,
+                                        Hkv, Dh, window, scale, k_pool, v_pool, partial, n_chunks_max, chunk, out,
+                                        ldo, n_rows, status, stream);
+  return mlxb_fail(MLXB_BAD_DTYPE, "attention (single-token rows): dtype code %d", dtype);
 }

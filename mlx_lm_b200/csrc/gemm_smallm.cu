@@ -1,0 +1,187 @@
+// Linear layer for few rows (decode steps): M <= 64 tokens against a weight
+// that has to be streamed from HBM once.
+//   C[M,N] = epilogue(A[M,K] . W[N,K]^T + bias[N]) (+ residual[M,N])
+// A, W, residual bfloat16; float32 accumulation; C bfloat16 or float32.
+//
+// The kernel is bound by reading W, so it is organised around that stream:
+// a CTA owns 8*NW output features (rows of W) over the whole K; its 8 warps
+// take the 32-wide K blocks round robin, so the CTA reads 8 consecutive
+// blocks (512 contiguous bytes of each row) at a time, every thread with one
+// 16-byte load per row block straight into registers (no shared-memory
+// staging), several blocks in flight.  Products run on the tensor cores
+// (mma.sync m16n8k16, tokens on the 16-side, weight rows on the 8-side).
+// Both operands are loaded with the same trick: the thread that owns logical
+// k-slots (2q, 2q+1, 2q+8, 2q+9) of two consecutive MMAs loads the 8
+// physically consecutive values 8q..8q+7 of the block, and since a dot product
+// does not care about the order of its terms, activation and weight fragments
+// agree as long as both use this mapping.
+// The 8 partial sums of a CTA are added in warp order through shared memory;
+// the order of additions depends on K alone, never on M or on the batch.
+// K must be a multiple of 8 (16-byte loads); other K go to the generic kernel.
+#include "common.cuh"
+
+MLXB_DEFINE_LAST_ERROR()
+
+enum { EPI_NONE = 0, EPI_GELU_NEW = 1 };
+
+constexpr int WARPS = 8;
+
+__device__ __forceinline__ uint4 ldg_stream(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ uint4 ldg_cached(const void* p) {
+  uint4 v;
+  asm volatile("ld.global.nc.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
+                                         unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// MT: 16-row token tiles (M <= 16*MT); NW: 8-row weight tiles per CTA.
+template <int MT, int NW, typename TO, int EPI>
+__global__ void __launch_bounds__(WARPS * 32)
+gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
+                   const float* __restrict__ bias, const __nv_bfloat16* residual, TO* C, int M, int N, int K,
+                   int lda, int ldc) {
+  extern __shared__ float part[];   // [WARPS][MT*NW*4][32]
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int g = lane >> 2, q = lane & 3;
+  const int n0 = blockIdx.x * (8 * NW);
+  const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+  float acc[MT][NW][4];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < NW; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+
+  const __nv_bfloat16* wrow[NW];
+  bool wok[NW];
+#pragma unroll
+  for (int j = 0; j < NW; ++j) {
+    const int n = n0 + j * 8 + g;
+    wok[j] = n < N;
+    wrow[j] = W + (size_t)(wok[j] ? n : 0) * K + 8 * q;
+  }
+  const __nv_bfloat16* arow[MT][2];
+  bool aok[MT][2];
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+      const int m = i * 16 + h * 8 + g;
+      aok[i][h] = m < M;
+      arow[i][h] = A + (size_t)(aok[i][h] ? m : 0) * lda + 8 * q;
+    }
+
+  const int n_blocks = (K + 31) >> 5;
+  constexpr int UNROLL = (MT * NW >= 8) ? 1 : 2;   // K blocks in flight per warp
+  for (int kb = warp; kb < n_blocks; kb += WARPS * UNROLL) {
+    uint4 wv[UNROLL][NW];
+    uint4 av[UNROLL][MT][2];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = (kb + u * WARPS) * 32;
+      const bool kin = (kb + u * WARPS) < n_blocks && (k + 8 * q) < K;   // K % 8 == 0: a chunk is all in or all out
+#pragma unroll
+      for (int j = 0; j < NW; ++j) wv[u][j] = (kin && wok[j]) ? ldg_stream(wrow[j] + k) : zero;
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) av[u][i][h] = (kin && aok[i][h]) ? ldg_cached(arow[i][h] + k) : zero;
+    }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int i = 0; i < MT; ++i)
+#pragma unroll
+        for (int j = 0; j < NW; ++j) {
+          mma_bf16(acc[i][j], av[u][i][0].x, av[u][i][1].x, av[u][i][0].y, av[u][i][1].y, wv[u][j].x, wv[u][j].y);
+          mma_bf16(acc[i][j], av[u][i][0].z, av[u][i][1].z, av[u][i][0].w, av[u][i][1].w, wv[u][j].z, wv[u][j].w);
+        }
+  }
+
+  constexpr int PER = MT * NW * 4;
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int j = 0; j < NW; ++j)
+#pragma unroll
+      for (int c = 0; c < 4; ++c) part[(warp * PER + (i * NW + j) * 4 + c) * 32 + lane] = acc[i][j][c];
+  __syncthreads();
+  for (int e = threadIdx.x; e < PER * 32; e += WARPS * 32) {
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < WARPS; ++w) v += part[w * PER * 32 + e];
+    const int idx = e >> 5, ln = e & 31;
+    const int c = idx & 3, j = (idx >> 2) % NW, i = (idx >> 2) / NW;
+    const int m = i * 16 + (ln >> 2) + ((c & 2) ? 8 : 0);
+    const int n = n0 + j * 8 + 2 * (ln & 3) + (c & 1);
+    if (m < M && n < N) {
+      if (bias) v += bias[n];
+      if (EPI == EPI_GELU_NEW) v = gelu_new_f(v);
+      if (residual) v += __bfloat162float(residual[(size_t)m * ldc + n]);
+      C[(size_t)m * ldc + n] = from_f<TO>(v);
+    }
+  }
+}
+
+template <int MT, int NW, typename TO>
+static int launch_epi(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N,
+                      int K, int lda, int ldc, int epi, cudaStream_t stream) {
+  const dim3 grid((N + 8 * NW - 1) / (8 * NW));
+  const size_t smem = (size_t)WARPS * MT * NW * 4 * 32 * sizeof(float);
+  auto k0 = gemm_smallm_kernel<MT, NW, TO, EPI_NONE>;
+  auto k1 = gemm_smallm_kernel<MT, NW, TO, EPI_GELU_NEW>;
+  auto kern = epi == EPI_GELU_NEW ? k1 : k0;
+  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  kern<<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias,
+                                           (const __nv_bfloat16*)residual, (TO*)C, M, N, K, lda, ldc);
+  return mlxb_check_launch("linear (few rows)");
+}
+
+template <typename TO>
+static int launch(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N, int K,
+                  int lda, int ldc, int epi, cudaStream_t stream) {
+  // Weight tiles per CTA: as many as keep at least ~2 CTAs per SM; more tiles re-use each
+  // activation fragment for more weight rows, which matters once M is large.
+  const int tiles = (N + 7) / 8;
+  const int mt = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
+  int nw = 1;
+  if (mt == 4) nw = tiles >= 4 * 296 ? 4 : (tiles >= 2 * 148 ? 2 : 1);
+  else if (mt == 2) nw = tiles >= 2 * 296 ? 2 : 1;
+#define GO(MT_, NW_) return launch_epi<MT_, NW_, TO>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, stream)
+  if (mt == 1) GO(1, 1);
+  if (mt == 2) { if (nw == 2) GO(2, 2); GO(2, 1); }
+  if (nw == 4) GO(4, 4);
+  if (nw == 2) GO(4, 2);
+  GO(4, 1);
+#undef GO
+}
+
+// A: bfloat16 [M, K] at row stride lda (elements, multiple of 8, base 16-byte aligned);
+// W: bfloat16 [N, K] contiguous; bias float32[N] or null; residual bfloat16 [M, N] at row stride ldc or null;
+// C: bfloat16 or float32 (out_f32) [M, N] at row stride ldc.  1 <= M <= 64, K % 8 == 0.
+MLXB_EXPORT int mlxb_linear_smallm(int out_f32, const void* A, const void* W, const float* bias, const void* residual,
+                                   void* C, int M, int N, int K, int lda, int ldc, int epi, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (M > 64) return mlxb_fail(MLXB_BAD_ARG, "linear (few rows): %d rows, at most 64", M);
+  if (K <= 0 || (K & 7) || (lda & 7) || lda < K || ldc < N)
+    return mlxb_fail(MLXB_BAD_ARG, "linear (few rows): K %d and row stride %d must be multiples of 8 (ldc %d, N %d)",
+                     K, lda, ldc, N);
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15))
+    return mlxb_fail(MLXB_BAD_ARG, "linear (few rows): operands must be 16-byte aligned");
+  if (epi != EPI_NONE && epi != EPI_GELU_NEW) return mlxb_fail(MLXB_BAD_ARG, "linear: epilogue code %d", epi);
+  if (out_f32) return launch<float>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, stream);
+  return launch<__nv_bfloat16>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, stream);
+}

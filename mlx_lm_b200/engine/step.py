@@ -55,6 +55,16 @@ class Workspace:
             self._bufs[key] = buf
         return buf[:rows]
 
+    def flat(self, tag: str, n: int, dtype: torch.dtype) -> torch.Tensor:
+        """Scratch memory of at least ``n`` elements whose size varies from step to step."""
+        key = (tag, 0, dtype)
+        buf = self._bufs.get(key)
+        if buf is None or buf.numel() < n:
+            buf = torch.empty(max(n, 1024, 2 * (buf.numel() if buf is not None else 0)), dtype=dtype,
+                              device=self.device)
+            self._bufs[key] = buf
+        return buf
+
     def nbytes(self) -> int:
         return sum(b.numel() * b.element_size() for b in self._bufs.values())
 
@@ -98,6 +108,11 @@ class StepContext:
         self.req_first_token = self.req_first_position = None
         self.spans: List[RequestSpan] = []
         self.max_q_len = 0
+        self.max_len = engine.max_len
+        # tokens of requests that bring a single token (decode) and of those that bring a portion:
+        # int32 device lists of token rows, None meaning "all tokens of the step"
+        self.n_single = self.n_portion = 0
+        self.single_rows = self.portion_rows = None
         self._tables: List[torch.Tensor] = []
         self._slots: Optional[torch.Tensor] = None
 
@@ -208,8 +223,11 @@ class Engine:
         L = sum(len(e.want) for e in entries)
         W = mgr.table_width
         pad = lambda n: (n + 3) & ~3
+        n_single = sum(1 for e in entries if len(e.tokens) == 1)
+        mixed = 0 < n_single < R
         off, sizes = {}, [("tokens", T), ("positions", T), ("token_req", T), ("logit_rows", L), ("slots", R),
-                          ("req_first_token", R + 1), ("req_first_position", R)]
+                          ("req_first_token", R + 1), ("req_first_position", R),
+                          ("single_rows", n_single if mixed else 0), ("portion_rows", T - n_single if mixed else 0)]
         sizes += [(f"table{g}", R * W) for g in range(len(mgr.kv_groups))]
         total = 0
         for name, n in sizes:
@@ -219,6 +237,8 @@ class Engine:
         h = host.numpy()
         t0 = 0
         rows: List[int] = []
+        single_rows: List[int] = []
+        portion_rows: List[int] = []
         for r, e in enumerate(entries):
             n = len(e.tokens)
             start = mgr.reserve(e.rid, n)
@@ -230,12 +250,17 @@ class Engine:
             h[off["req_first_token"] + r] = t0
             h[off["req_first_position"] + r] = start
             rows.extend(t0 + w for w in e.want)
+            if mixed:
+                (single_rows if n == 1 else portion_rows).extend(range(t0, t0 + n))
             ctx.spans.append(RequestSpan(e.rid, slot, t0, n, start))
             ctx.max_q_len = max(ctx.max_q_len, n)
             t0 += n
         h[off["req_first_token"] + R] = T
         if L:
             h[off["logit_rows"]: off["logit_rows"] + L] = rows
+        if mixed:
+            h[off["single_rows"]: off["single_rows"] + n_single] = single_rows
+            h[off["portion_rows"]: off["portion_rows"] + T - n_single] = portion_rows
         rids = [e.rid for e in entries]
         for g in range(len(mgr.kv_groups)):
             o = off[f"table{g}"]
@@ -249,6 +274,9 @@ class Engine:
         ctx.logit_rows = view("logit_rows", L)
         ctx.req_first_token, ctx.req_first_position = view("req_first_token", R + 1), view("req_first_position", R)
         ctx._slots = view("slots", R)
+        ctx.n_single, ctx.n_portion = n_single, T - n_single
+        if mixed:
+            ctx.single_rows, ctx.portion_rows = view("single_rows", n_single), view("portion_rows", T - n_single)
         ctx._tables = [view(f"table{g}", R * W).view(R, W) for g in range(len(mgr.kv_groups))]
         try:
             logits = self.model.run(ctx)

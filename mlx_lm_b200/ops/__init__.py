@@ -182,6 +182,37 @@ def linear_generic(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=N
           _p(residual), _p(out), M, N, K, lda, ldc, epilogue, stream)
 
 
+_SMALLM_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                c_void_p]
+
+SMALL_M = 64
+
+
+def linear_few_rows(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=None) -> None:
+    """``linear_generic``'s contract for bfloat16 and at most 64 rows: the weight is streamed from HBM once
+    with 16-byte loads and multiplied on the tensor cores (csrc/gemm_smallm.cu).  ``K`` and the row stride of
+    ``x`` must be multiples of 8."""
+    _need(x, torch.bfloat16, "linear x")
+    _need(w, torch.bfloat16, "linear w")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not w.is_contiguous() or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    lda, ldc = _rows(x, "linear x"), _rows(out, "linear out")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"linear: output dtype {out.dtype}")
+    if bias is not None:
+        _need(bias, torch.float32, "linear bias")
+        if bias.numel() != N:
+            raise KernelError(f"linear: bias of {bias.numel()} for {N} outputs")
+    if residual is not None:
+        _need(residual, torch.bfloat16, "linear residual")
+        if residual.shape != out.shape or _rows(residual, "linear residual") != ldc:
+            raise KernelError("linear: residual must have the output's shape and row stride")
+    _call("gemm_smallm", "mlxb_linear_smallm", _SMALLM_ARGS, int(out.dtype == torch.float32), _p(x), _p(w), _p(bias),
+          _p(residual), _p(out), M, N, K, lda, ldc, epilogue, stream)
+
+
 # --------------------------------------------------------------------------
 # paged key/value cache and attention
 
@@ -207,23 +238,58 @@ def kv_write(k_src, v_src, positions, token_req, block_table, k_pool, v_pool, st
 
 
 _ATTN_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-              c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p]
+              c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]
+
+
+def _attn_shapes(q, out, k_pool, n_heads, what):
+    n_pages, Hkv, page, Dh = k_pool.shape
+    _need(q, k_pool.dtype, what + " q")
+    _need(out, k_pool.dtype, what + " out")
+    if q.shape[1] != n_heads * Dh or out.shape[0] != q.shape[0] or out.shape[1] != n_heads * Dh:
+        raise KernelError(f"{what}: q {tuple(q.shape)} out {tuple(out.shape)} for {n_heads} heads of {Dh}")
+    return n_pages, Hkv, page, Dh
 
 
 def attention_generic(q, positions, token_req, block_table, k_pool, v_pool, out, n_heads: int, scale: float,
-                      window: int, status, stream) -> None:
-    """Causal attention of every token over its request's pages (float32 math, one warp per token and head).
+                      window: int, status, stream, rows=None) -> None:
+    """Causal attention of tokens over their requests' pages (float32 math, one warp per token and head).
 
-    ``q``: ``[T, n_heads*Dh]`` view; ``out``: ``[T, n_heads*Dh]``; ``window <= 0`` means all keys."""
-    n_pages, Hkv, page, Dh = k_pool.shape
-    _need(q, k_pool.dtype, "attention q")
-    _need(out, k_pool.dtype, "attention out")
-    T = q.shape[0]
-    if q.shape[1] != n_heads * Dh or out.shape[0] != T or out.shape[1] != n_heads * Dh:
-        raise KernelError(f"attention: q {tuple(q.shape)} out {tuple(out.shape)} for {n_heads} heads of {Dh}")
+    ``q``: ``[T, n_heads*Dh]`` view; ``out``: ``[T, n_heads*Dh]``; ``rows``: int32 token indices to run
+    (default all ``T``); ``window <= 0`` means all keys."""
+    n_pages, Hkv, page, Dh = _attn_shapes(q, out, k_pool, n_heads, "attention")
+    n = q.shape[0] if rows is None else rows.numel()
     _call("attention", "mlxb_attention_generic", _ATTN_ARGS, dtype_code(k_pool.dtype), _p(q), _rows(q, "attention q"),
           _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh,
-          window, scale, _p(k_pool), _p(v_pool), _p(out), _rows(out, "attention out"), T, _p(status), stream)
+          window, scale, _p(k_pool), _p(v_pool), _p(out), _rows(out, "attention out"), _p(rows), n, _p(status),
+          stream)
+
+
+_DEC_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+             c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
+
+DECODE_CHUNK = 128   # key positions per CTA of the single-token attention kernel: a constant, never a function of the batch
+
+
+def attention_decode_scratch(n_rows: int, n_heads: int, head_dim: int, max_len: int, chunk: int = DECODE_CHUNK) -> int:
+    """Float32 elements of scratch memory ``attention_decode`` needs for ``n_rows`` rows."""
+    return n_rows * n_heads * ((max_len + chunk - 1) // chunk) * (head_dim + 2)
+
+
+def attention_decode(q, positions, token_req, block_table, k_pool, v_pool, out, n_heads: int, scale: float,
+                     window: int, scratch, max_len: int, status, stream, rows=None, chunk: int = DECODE_CHUNK) -> None:
+    """Attention for rows with a single query each (decode steps): keys are cut into chunks of ``chunk``
+    positions, one CTA per (chunk, head, row) writes a partial result to ``scratch`` (float32, at least
+    ``attention_decode_scratch(...)`` elements) and a second kernel combines them."""
+    n_pages, Hkv, page, Dh = _attn_shapes(q, out, k_pool, n_heads, "attention_decode")
+    n = q.shape[0] if rows is None else rows.numel()
+    n_chunks = (max_len + chunk - 1) // chunk
+    _need(scratch, torch.float32, "attention_decode scratch")
+    if scratch.numel() < n * n_heads * n_chunks * (Dh + 2):
+        raise KernelError(f"attention_decode: scratch of {scratch.numel()} floats for {n} rows")
+    _call("attention", "mlxb_attention_decode", _DEC_ARGS, dtype_code(k_pool.dtype), _p(q), _rows(q, "attention q"),
+          _p(rows), _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv,
+          Dh, window, scale, _p(k_pool), _p(v_pool), _p(scratch), n_chunks, chunk, _p(out),
+          _rows(out, "attention out"), n, _p(status), stream)
 
 
 # --------------------------------------------------------------------------

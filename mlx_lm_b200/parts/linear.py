@@ -20,7 +20,7 @@ ACTIVATIONS = {None: ops.EPI_NONE, "none": ops.EPI_NONE, "gelu_new": ops.EPI_GEL
 
 
 class Linear(Part):
-    kernel_libs = ("gemm_simt",)
+    kernel_libs = ("gemm_simt", "gemm_smallm")
 
     def __init__(self, name: str, n_in: int, n_out: int, bias: bool = True, stored: str = "out_in",
                  weight_suffix: str = ".weight", init: Init = Init(), bias_init: Init = Init()):
@@ -51,6 +51,12 @@ class Linear(Part):
         self.weight = weight
 
     def forward(self, ctx, x, out, activation=None, residual=None) -> torch.Tensor:
+        """float32: the generic kernel (true 32-bit arithmetic).  bfloat16: the weight-streaming kernel for up
+        to 64 rows; more rows, or an inner size that is no multiple of 8, go to the generic kernel."""
         epi = ACTIVATIONS[activation]
-        ops.linear_generic(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual)
+        if (x.dtype == torch.bfloat16 and x.shape[0] <= ops.SMALL_M and self.n_in % 8 == 0
+                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
+            ops.linear_few_rows(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual)
+        else:
+            ops.linear_generic(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual)
         return out

@@ -14,6 +14,8 @@ from __future__ import annotations
 
 from typing import List, Optional
 
+import torch
+
 from .. import ops
 from .base import Init, Mixer, PagedKVSpec, PositionEncoding, register_part
 from .linear import Linear
@@ -62,8 +64,18 @@ class Attention(Mixer):
         return self.out.forward(ctx, o, residual, residual=residual)
 
     def attend(self, ctx, q, cache, o) -> None:
-        ops.attention_generic(q, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o,
-                              self.n_heads, self.scale, self.window or 0, ctx.status, ctx.stream)
+        """Rows of requests that bring one token go to the split-key kernel, the rest to the kernel for
+        portions; both write their rows of ``o``."""
+        window = self.window or 0
+        if ctx.n_single:
+            scratch = ctx.ws.flat("attn_partial", ops.attention_decode_scratch(
+                ctx.n_single, self.n_heads, self.head_dim, ctx.max_len), torch.float32)
+            ops.attention_decode(q, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o,
+                                 self.n_heads, self.scale, window, scratch, ctx.max_len, ctx.status, ctx.stream,
+                                 rows=ctx.single_rows)
+        if ctx.n_portion:
+            ops.attention_generic(q, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o,
+                                  self.n_heads, self.scale, window, ctx.status, ctx.stream, rows=ctx.portion_rows)
 
 
 register_part("mixer", "attention", Attention)

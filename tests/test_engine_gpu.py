@@ -30,7 +30,9 @@ def part_ctx(T=0, positions=None, token_req=None):
     from mlx_lm_b200.engine import Workspace
     return SimpleNamespace(ws=Workspace("cuda"), stream=ops.current_stream(), n_tokens=T,
                            status=torch.zeros(1, dtype=torch.int32, device="cuda"),
-                           positions=positions, token_req=token_req, tokens=None)
+                           positions=positions, token_req=token_req, tokens=None, max_len=64,
+                           n_single=T if T == 1 else 0, n_portion=0 if T == 1 else T, single_rows=None,
+                           portion_rows=None)
 
 
 def bind(part, dtype, seed=0):
@@ -95,6 +97,12 @@ def test_parts_alone(dtype):
     ya = att.forward(part_ctx(21, positions[:21], token_req[:21]), xd[:21], xd[:21].clone(), cache).clone()
     yb = att.forward(part_ctx(T - 21, positions[21:], token_req[21:]), xd[21:], xd[21:].clone(), cache)
     assert rel(torch.cat([ya, yb]), y) <= tol
+    # and one more token alone takes the single-token path
+    x1 = torch.randn(1, D, generator=g).to(torch.bfloat16).float()
+    p1 = torch.tensor([T], dtype=torch.int32).cuda()
+    y1 = att.forward(part_ctx(1, p1, token_req[:1]), x1.to(dtype).cuda(), x1.to(dtype).cuda().clone(), cache)
+    xx = torch.cat([x, x1])
+    assert rel(y1, (xx + plain.attention_part(xx, wd, "", H))[T:]) <= tol
 
     blk = PreNormBlock(LayerNorm("b.ln_1", D, 1e-5), Attention("b.attn", D, H, Dh, stored="in_out"),
                        LayerNorm("b.ln_2", D, 1e-5), MLP("b.mlp", D, 100, stored="in_out"))

@@ -114,6 +114,44 @@ def test_linear_generic(ops, dtype, M, N, K):
     assert rel_err(out, R.linear(wide[:, 8:8 + K].cpu(), w.cpu(), b.cpu())) <= t
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 192, 64), (1, 1000, 96), (8, 320, 96), (16, 96, 320), (17, 3072, 1024),
+                                   (33, 50257, 64), (64, 1600, 6400), (64, 50257, 1024), (5, 7, 8), (40, 1000, 1608)])
+def test_linear_few_rows(ops, M, N, K):
+    g = torch.Generator().manual_seed(M * N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    b = torch.randn(N, generator=g).cuda()
+    res = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.linear_few_rows(x, w, b, out, stream())
+    assert rel_err(out, R.linear(x.cpu(), w.cpu(), b.cpu())) <= 6e-3
+    ops.linear_few_rows(x, w, b, out, stream(), epilogue=ops.EPI_GELU_NEW, residual=res)
+    assert rel_err(out, R.linear(x.cpu(), w.cpu(), b.cpu(), "gelu_new", res.cpu())) <= 6e-3
+    r2 = res.clone()
+    ops.linear_few_rows(x, w, None, r2, stream(), residual=r2)       # in place on the residual
+    assert rel_err(r2, R.linear(x.cpu(), w.cpu(), None, None, res.cpu())) <= 6e-3
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.linear_few_rows(x, w, None, out32, stream())
+    assert rel_err(out32, R.linear(x.cpu(), w.cpu())) <= 1e-5       # float32 accumulation of bfloat16 products
+    # a row's result does not depend on how many rows the call has
+    one = torch.empty(1, N, dtype=torch.float32, device="cuda")
+    ops.linear_few_rows(x[M - 1:M], w, None, one, stream())
+    assert torch.equal(one[0], out32[M - 1])
+    wide = torch.randn(M, K + 24, generator=g).to(torch.bfloat16).cuda()
+    ops.linear_few_rows(wide[:, 8:8 + K], w, b, out, stream())
+    assert rel_err(out, R.linear(wide[:, 8:8 + K].cpu(), w.cpu(), b.cpu())) <= 6e-3
+    with pytest.raises(ops.KernelError):
+        ops.linear_few_rows(torch.zeros(65, K, dtype=torch.bfloat16, device="cuda"), w, None,
+                            torch.empty(65, N, dtype=torch.bfloat16, device="cuda"), stream())
+
+
+def test_linear_few_rows_refuses_odd_inner_size(ops):
+    x = torch.zeros(2, 12, dtype=torch.bfloat16, device="cuda")
+    w = torch.zeros(5, 12, dtype=torch.bfloat16, device="cuda")
+    with pytest.raises(ops.KernelError):
+        ops.linear_few_rows(x, w, None, torch.empty(2, 5, dtype=torch.bfloat16, device="cuda"), stream())
+
+
 def test_linear_row_does_not_depend_on_batch(ops):
     g = torch.Generator().manual_seed(3)
     x = torch.randn(70, 96, generator=g).cuda()
@@ -172,6 +210,47 @@ def test_kv_write_and_attention(ops, dtype, Hq, Hkv, Dh, page, window):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,window,chunk", [(4, 4, 16, 16, 0, 128), (3, 3, 32, 16, 0, 128),
+                                                          (6, 2, 48, 32, 0, 64), (5, 1, 80, 64, 0, 128),
+                                                          (2, 2, 128, 16, 40, 32), (8, 4, 64, 16, 17, 128),
+                                                          (16, 16, 64, 16, 0, 128), (2, 1, 256, 16, 0, 128)])
+def test_attention_single_token_rows(ops, dtype, Hq, Hkv, Dh, page, window, chunk):
+    """The split-key kernel on the single-token requests of a mixed step, selected by row list, and on a
+    step of single tokens only (no row list), against the plain statement."""
+    lens, new = [0, 37, 130, 64, 511, 255], [1, 1, 35, 1, 1, 1]
+    c = paged_case(dtype, lens=lens, new=new, Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=Dh + page + 1)
+    dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    qw = Hq * Dh
+    q = dev["qkv"][:, :qw]
+    scale = Dh ** -0.5
+    ref = R.attention(c["qkv"][:, :qw], c["positions"], c["token_req"], c["bt"], c["k_pool"], c["v_pool"], Hq, scale,
+                      window)
+    first = np.cumsum([0] + new)
+    single = [int(first[i]) for i, n in enumerate(new) if n == 1]
+    rows = torch.tensor(single, dtype=torch.int32).cuda()
+    max_len = 640
+    scratch = torch.full((ops.attention_decode_scratch(len(single), Hq, Dh, max_len, chunk),), float("nan"),
+                         device="cuda")
+    out = torch.zeros(c["T"], qw, dtype=dtype, device="cuda")
+    ops.attention_decode(q, dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"], dev["v_pool"], out, Hq,
+                         scale, window, scratch, max_len, status, stream(), rows=rows, chunk=chunk)
+    assert int(status.item()) == 0
+    assert rel_err(out[single], ref[single]) <= tol(dtype, 3e-6, 8e-3)
+    untouched = [t for t in range(c["T"]) if t not in single]
+    assert float(out[untouched].float().abs().max()) == 0.0
+    # all rows single: tokens 0..n-1 without a row list
+    c2 = paged_case(dtype, lens=[5, 300, 129, 0], new=[1, 1, 1, 1], Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=3)
+    d2 = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c2.items()}
+    out2 = torch.zeros(4, qw, dtype=dtype, device="cuda")
+    ops.attention_decode(d2["qkv"][:, :qw], d2["positions"], d2["token_req"], d2["bt"], d2["k_pool"], d2["v_pool"],
+                         out2, Hq, scale, window, scratch, max_len, status, stream(), chunk=chunk)
+    ref2 = R.attention(c2["qkv"][:, :qw], c2["positions"], c2["token_req"], c2["bt"], c2["k_pool"], c2["v_pool"], Hq,
+                       scale, window)
+    assert int(status.item()) == 0 and rel_err(out2, ref2) <= tol(dtype, 3e-6, 8e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_finds_one_far_key(ops, dtype):
     """One key among hundreds matches the query strongly: the output must be that key's value row,
     wherever its page lies.  Random inputs would hide a key that is skipped or read from the wrong page."""
@@ -188,9 +267,14 @@ def test_attention_finds_one_far_key(ops, dtype):
         dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
         status = torch.zeros(1, dtype=torch.int32, device="cuda")
         out = torch.empty(1, qw, dtype=dtype, device="cuda")
+        want = c["v_pool"][pg, 0, target % page, :].float()
         ops.attention_generic(dev["qkv"][:, :qw], dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"],
                               dev["v_pool"], out, Hq, Dh ** -0.5, 0, status, stream())
-        want = c["v_pool"][pg, 0, target % page, :].float()
+        assert float((out[0, :Dh].float().cpu() - want).abs().max()) <= (1e-4 if dtype == torch.float32 else 2e-2), target
+        out.zero_()
+        scratch = torch.empty(ops.attention_decode_scratch(1, Hq, Dh, 512), device="cuda")
+        ops.attention_decode(dev["qkv"][:, :qw], dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"],
+                             dev["v_pool"], out, Hq, Dh ** -0.5, 0, scratch, 512, status, stream())
         assert float((out[0, :Dh].float().cpu() - want).abs().max()) <= (1e-4 if dtype == torch.float32 else 2e-2), target
 
 
@@ -211,5 +295,11 @@ def test_attention_window_edge(ops, dtype):
         ops.attention_generic(dev["qkv"][:, :Dh], dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"],
                               dev["v_pool"], out, Hq, Dh ** -0.5, W, status, stream())
         want = c["v_pool"][pg, 0, hot % page, :].float()
+        close = float((out[0].float().cpu() - want).abs().max()) <= 3e-2
+        assert close == expect_hit
+        out.zero_()
+        scratch = torch.empty(ops.attention_decode_scratch(1, Hq, Dh, 256), device="cuda")
+        ops.attention_decode(dev["qkv"][:, :Dh], dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"],
+                             dev["v_pool"], out, Hq, Dh ** -0.5, W, scratch, 256, status, stream())
         close = float((out[0].float().cpu() - want).abs().max()) <= 3e-2
         assert close == expect_hit
