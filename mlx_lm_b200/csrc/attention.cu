@@ -408,3 +408,46 @@ MLXB_EXPORT int mlxb_attention_decode(int dtype, const void* q, int ldq, const i
                                         ldo, n_rows, status, stream);
   return mlxb_fail(MLXB_BAD_DTYPE, "attention (single-token rows): dtype code %d", dtype);
 }
+
+// ---------------------------------------------------------------- no-allocation variant
+// Declared and documented in attention_noalloc.h.
+#include "attention_noalloc.h"
+
+// Scratch for the per-chunk partial results, owned by the library.  In host code this name is only
+// a handle for the runtime: the address kernels can use comes from cudaGetSymbolAddress below.
+static __device__ __align__(256) float g_noalloc_partial[MLXB_NOALLOC_SCRATCH_FLOATS];
+
+static float* g_noalloc_partial_ptr[64];   // device address of the array, per device ordinal
+
+MLXB_EXPORT int mlxb_attention_decode_noalloc(int dtype, const void* q, int ldq, const int* rows,
+                                              const int* positions, const int* token_req, const int* block_table,
+                                              int max_pages, int n_pages, int page, int n_q_heads, int n_kv_heads,
+                                              int head_dim, int window, float scale, const void* k_pool,
+                                              const void* v_pool, int n_chunks_max, int chunk, void* out, int ldo,
+                                              int n_rows, int* status, cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (n_q_heads <= 0 || head_dim <= 0 || n_chunks_max <= 0)
+    return mlxb_fail(MLXB_BAD_ARG, "attention (no allocation): %d heads of %d, %d chunks", n_q_heads, head_dim,
+                     n_chunks_max);
+  const long long need = mlxb_attention_decode_scratch(n_rows, n_q_heads, head_dim, n_chunks_max);
+  if (need > (long long)MLXB_NOALLOC_SCRATCH_FLOATS)
+    return mlxb_fail(MLXB_BAD_ARG,
+                     "attention (no allocation): %d rows x %d heads x %d chunks x (%d + 2) = %lld floats of scratch, "
+                     "the built-in array holds %d",
+                     n_rows, n_q_heads, n_chunks_max, head_dim, need, (int)MLXB_NOALLOC_SCRATCH_FLOATS);
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return mlxb_fail((int)e, "attention (no allocation): cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= 64) return mlxb_fail(MLXB_BAD_ARG, "attention (no allocation): device ordinal %d", dev);
+  if (g_noalloc_partial_ptr[dev] == nullptr) {   // first call on this device (it is current): look the address up
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_noalloc_partial);
+    if (e != cudaSuccess || p == nullptr)
+      return mlxb_fail(e != cudaSuccess ? (int)e : MLXB_BAD_ARG,
+                       "attention (no allocation): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_noalloc_partial_ptr[dev] = p;
+  }
+  return mlxb_attention_decode(dtype, q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page,
+                               n_q_heads, n_kv_heads, head_dim, window, scale, k_pool, v_pool,
+                               g_noalloc_partial_ptr[dev], n_chunks_max, chunk, out, ldo, n_rows, status, stream);
+}
