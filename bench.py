@@ -125,18 +125,17 @@ def decode_loop(engine, sampler_cls, model, batch, prompt_len, steps, warmup, vo
     reqs = []
     for b in range(batch):
         toks = torch.randint(0, vocab, (prompt_len,), generator=g).tolist()
-        engine.add_request(("bench", b))
-        reqs.append(Request(b, toks, prompt_len, 10 ** 9, GREEDY))
+        engine.add_request(1000 + b)
+        reqs.append(Request(1000 + b, toks, prompt_len, 10 ** 9, GREEDY))
     for i in range(0, batch, 4):    # prompts, four requests a step
         chunk = reqs[i:i + 4]
-        logits = engine.step([StepEntry(("bench", r.uid), r.tokens, [prompt_len - 1]) for r in chunk])
+        logits = engine.step([StepEntry(r.uid, r.tokens, [prompt_len - 1]) for r in chunk])
         toks, _ = sample(logits, chunk)
         for r, t in zip(chunk, toks):
             r.tokens.append(t)
 
-    def one_step():
-        logits = engine.step([StepEntry(("bench", r.uid), r.tokens[-1:], [0]) for r in reqs])
-        toks, _ = sample(logits, reqs)
+    def one_step():     # model and sampler as one call: a CUDA graph replay for these batch sizes
+        toks, _ = engine.decode_sampled([StepEntry(r.uid, r.tokens[-1:], [0]) for r in reqs], reqs, sample)
         for r, t in zip(reqs, toks):
             r.tokens.append(t)
 
@@ -155,7 +154,7 @@ def decode_loop(engine, sampler_cls, model, batch, prompt_len, steps, warmup, vo
     mean_ctx = prompt_len + 1 + warmup + (steps - 1) / 2.0
     engine.check_status()
     for r in reqs:
-        engine.finish(("bench", r.uid))
+        engine.finish(r.uid)
     return ms, launches, mean_ctx
 
 

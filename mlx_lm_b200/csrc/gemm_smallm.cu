@@ -144,7 +144,11 @@ static int launch_epi(const void* A, const void* W, const float* bias, const voi
   auto k0 = gemm_smallm_kernel<MT, NW, TO, EPI_NONE>;
   auto k1 = gemm_smallm_kernel<MT, NW, TO, EPI_GELU_NEW>;
   auto kern = epi == EPI_GELU_NEW ? k1 : k0;
-  if (smem > 48 * 1024) cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  static bool raised[2] = {false, false};   // once per instantiation, and never for the first time inside a stream capture
+  if (smem > 48 * 1024 && !raised[epi == EPI_GELU_NEW]) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    raised[epi == EPI_GELU_NEW] = true;
+  }
   kern<<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias,
                                            (const __nv_bfloat16*)residual, (TO*)C, M, N, K, lda, ldc);
   return mlxb_check_launch("linear (few rows)");

@@ -49,12 +49,13 @@ MLXB_EXPORT int mlxb_layernorm(int dtype, const void* x, const int* rows, const 
   const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : (D >= 128 ? 128 : 64));
   const size_t smem = (size_t)(D + 40) * sizeof(float);
   if (dtype == MLXB_F32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem > 48 * 1024)   // 227 KB is the most a CTA can have; set once to the largest width this file accepts
+      cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (49152 + 40) * 4);
     layernorm_kernel<float><<<R, threads, smem, stream>>>((const float*)x, rows, gain, bias, (float*)y, D, eps);
   } else if (dtype == MLXB_BF16) {
     if (smem > 48 * 1024)
-      cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                           (49152 + 40) * 4);
     layernorm_kernel<__nv_bfloat16><<<R, threads, smem, stream>>>((const __nv_bfloat16*)x, rows, gain, bias,
                                                                    (__nv_bfloat16*)y, D, eps);
   } else {

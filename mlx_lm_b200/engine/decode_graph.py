@@ -1,0 +1,129 @@
+"""A decode step as a CUDA graph.
+
+A step in which every request brings one token launches some two hundred small kernels; issued
+one by one from Python they cost more host time than device time.  For each batch size in
+``Engine.GRAPH_BUCKETS`` the whole step — embedding, every block, final norm, output head and
+the sampling kernel — is captured once into a CUDA graph over buffers of fixed address; a step
+then writes its integers (tokens, positions, block tables, sampler records) into one pinned
+buffer, copies it, replays the graph and reads the chosen tokens back.
+
+A batch smaller than its bucket is padded with rows whose request index is -1: the cache write
+and the attention kernels skip them, the other kernels compute rows nobody reads.  The graph has
+a workspace of its own, so that a later, larger step cannot move the buffers it was captured on.
+"""
+
+from __future__ import annotations
+
+from typing import List, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from .. import ops
+from ..sampling import LogitsProcessors
+from .step import StepContext, StepEntry, Workspace
+
+
+class DecodeGraph:
+    @staticmethod
+    def samplers_fit(requests: Sequence, sampler) -> bool:
+        """Whether the sampling kernel alone covers what these requests ask for."""
+        if getattr(sampler, "return_logprobs", False) or not hasattr(sampler, "seed"):
+            return False
+        return all(not r.processors and not r.sampler.xtc_special_tokens for r in requests)
+
+    def __init__(self, engine, bucket: int):
+        self.engine, self.B = engine, bucket
+        mgr = engine.cache
+        dev = engine.model.device
+        B, W = bucket, mgr.table_width
+        pad = lambda n: (n + 3) & ~3
+        sizes = [("tokens", B), ("positions", B), ("token_req", B), ("logit_rows", B), ("slots", B),
+                 ("req_first_token", B + 1), ("req_first_position", B), ("sample", B * ops.SAMPLE_WORDS)]
+        sizes += [(f"table{g}", B * W) for g in range(len(mgr.kv_groups))]
+        self.off, total = {}, 0
+        for name, n in sizes:
+            self.off[name] = total
+            total += pad(n)
+        self.total = total
+        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
+        self.out = torch.zeros(2 * B, dtype=torch.int32, device=dev)      # tokens | log-probability bits
+        self.out_host = torch.zeros(2 * B, dtype=torch.int32).pin_memory()
+        h = self.host.numpy()
+        h[self.off["logit_rows"]: self.off["logit_rows"] + B] = np.arange(B)
+        h[self.off["req_first_token"]: self.off["req_first_token"] + B + 1] = np.arange(B + 1)
+        h[self.off["token_req"]: self.off["token_req"] + B] = -1
+        for g in range(len(mgr.kv_groups)):
+            h[self.off[f"table{g}"]: self.off[f"table{g}"] + B * W] = -1
+
+        view = lambda name, n: self.dev[self.off[name]: self.off[name] + n]
+        ctx = StepContext(engine)
+        ctx.ws = Workspace(dev)
+        ctx.n_tokens = ctx.n_requests = ctx.n_logit_rows = B
+        ctx.tokens, ctx.positions, ctx.token_req = view("tokens", B), view("positions", B), view("token_req", B)
+        ctx.logit_rows = view("logit_rows", B)
+        ctx.req_first_token, ctx.req_first_position = view("req_first_token", B + 1), view("req_first_position", B)
+        ctx._slots = view("slots", B)
+        ctx._tables = [view(f"table{g}", B * W).view(B, W) for g in range(len(mgr.kv_groups))]
+        ctx.n_single, ctx.n_portion, ctx.max_q_len = B, 0, 1
+        self.ctx = ctx
+        self.params = view("sample", B * ops.SAMPLE_WORDS)
+        self.tok = self.out[:B]
+        self.lp = self.out[B:2 * B].view(torch.float32)
+
+        # once eagerly on a side stream (loads libraries, sizes the workspace), then capture
+        self.dev.copy_(self.host)
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            self._launch()
+        side.synchronize()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph, stream=side):
+            self._launch()
+        torch.cuda.current_stream(dev).wait_stream(side)
+        self.n_kernels = self._count
+
+    def _launch(self) -> None:
+        ctx = self.ctx
+        ctx.stream = ops.current_stream()
+        before = ops.launch_count
+        logits = self.engine.model.run(ctx)
+        ops.sample(logits, self.params, self.tok, self.lp, ctx.stream)
+        self._count = ops.launch_count - before
+
+    def run(self, entries: Sequence[StepEntry], requests: Sequence, seed: int) -> Tuple[List[int], List[float]]:
+        eng, mgr, B = self.engine, self.engine.cache, self.B
+        eng._validate(entries)
+        n = len(entries)
+        h, off, W = self.host.numpy(), self.off, mgr.table_width
+        h[off["token_req"] + n: off["token_req"] + B] = -1
+        by_rid = {r.uid: r for r in requests}
+        words = []
+        for i, e in enumerate(entries):
+            start = mgr.reserve(e.rid, 1)
+            h[off["tokens"] + i] = e.tokens[0]
+            h[off["positions"] + i] = start
+            h[off["token_req"] + i] = i
+            h[off["slots"] + i] = mgr.requests[e.rid].slot
+            h[off["req_first_position"] + i] = start
+            r = requests[i]
+            words.append(r.sampler.words(seed, r.uid, len(r.tokens)))
+        h[off["sample"]: off["sample"] + n * ops.SAMPLE_WORDS] = np.frombuffer(b"".join(words), dtype=np.int32)
+        h[off["sample"] + n * ops.SAMPLE_WORDS: off["sample"] + B * ops.SAMPLE_WORDS] = 0
+        rids = [e.rid for e in entries]
+        for g in range(len(mgr.kv_groups)):
+            o = off[f"table{g}"]
+            mgr.block_table(g, rids, out=h[o: o + n * W].reshape(n, W))
+            h[o + n * W: o + B * W] = -1
+        self.dev.copy_(self.host, non_blocking=True)
+        self.graph.replay()
+        ops.launch_count += self.n_kernels
+        self.out_host.copy_(self.out, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        for e in entries:
+            mgr.commit(e.rid)
+        eng.n_steps += 1
+        o = self.out_host.numpy()
+        return o[:n].tolist(), o[B:B + n].view(np.float32).tolist()

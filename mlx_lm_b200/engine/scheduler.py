@@ -249,11 +249,17 @@ class Scheduler:
             return [], []
         entries = [StepEntry(p.request.uid, p.request.tokens[p.request.n_cached:p.request.n_cached + p.n_tokens],
                              [p.n_tokens - 1] if p.wants_logits else []) for p in planned]
-        logits = self.engine.step(entries)
+        sampled = [p.request for p in planned if p.wants_logits]
+        fused = (len(sampled) == len(planned) and hasattr(self.engine, "decode_sampled")
+                 and all(p.n_tokens == 1 for p in planned))
+        if fused:     # a pure decode step: model and sampler in one call (a CUDA graph where it fits)
+            tokens, logprobs = self.engine.decode_sampled(entries, sampled, self.sample)
+        else:
+            logits = self.engine.step(entries)
+            tokens, logprobs = self.sample(logits, sampled) if sampled else ([], [])
         self.stats.steps += 1
         self.stats.most_running = max(self.stats.most_running, len(self.running))
         prompts: List[PromptProgress] = []
-        sampled: List[Request] = []
         for p in planned:
             r = p.request
             if r.n_cached < r.n_prompt:
@@ -264,11 +270,8 @@ class Scheduler:
             r.n_cached += p.n_tokens
             self.stats.tokens += p.n_tokens
             self.last_step_tokens += p.n_tokens
-            if p.wants_logits:
-                sampled.append(r)
         responses: List[Response] = []
         if sampled:
-            tokens, logprobs = self.sample(logits, sampled)
             for r, tok, lp in zip(sampled, tokens, logprobs):
                 r.tokens.append(int(tok))
                 r.n_generated += 1

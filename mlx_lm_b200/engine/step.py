@@ -51,7 +51,7 @@ class Workspace:
             cap = max(rows, 16)
             if buf is not None:
                 cap = max(cap, 2 * buf.shape[0])
-            buf = torch.empty((cap, cols), dtype=dtype, device=self.device)
+            buf = torch.zeros((cap, cols), dtype=dtype, device=self.device)   # rows a step never writes stay finite
             self._bufs[key] = buf
         return buf[:rows]
 
@@ -157,7 +157,8 @@ class Engine:
         self._dev: Optional[torch.Tensor] = None
         self._flip = 0
         self.n_steps = 0
-        self.n_kernel_launches = 0
+        self.use_graphs = True
+        self._graphs = {}
 
     # ------------------------------------------------------------------ requests
     def add_request(self, rid: Hashable) -> None:
@@ -189,11 +190,7 @@ class Engine:
         ev.record()
         self._host_events[i] = ev   # the pinned buffer may be rewritten once this has passed
 
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
-        """Run the entries' tokens as one batch.  Returns float32 logits ``[n_wanted, vocab]`` on the
-        device in the order of the entries and of their ``want`` lists (None if nothing is wanted)."""
-        if not entries:
-            return None
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
         mgr = self.cache
         vocab = self.model.vocab_size
         seen = set()
@@ -216,6 +213,14 @@ class Engine:
         if not mgr.can_reserve([(e.rid, len(e.tokens)) for e in entries]):
             from ..cache import OutOfPages
             raise OutOfPages(f"this step needs more pages than are free {mgr.pages_free()}")
+
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Run the entries' tokens as one batch.  Returns float32 logits ``[n_wanted, vocab]`` on the
+        device in the order of the entries and of their ``want`` lists (None if nothing is wanted)."""
+        if not entries:
+            return None
+        mgr = self.cache
+        self._validate(entries)
 
         ctx = StepContext(self)
         R = len(entries)
@@ -285,6 +290,28 @@ class Engine:
                 mgr.commit(e.rid)
         self.n_steps += 1
         return logits
+
+    # ------------------------------------------------------------------ decode steps as CUDA graphs
+    GRAPH_BUCKETS = (1, 2, 4, 8, 16, 32, 64)
+
+    def decode_sampled(self, entries: Sequence[StepEntry], requests: Sequence, sampler):
+        """One token for each of the requests, sampled on the device: ``(tokens, logprobs)`` as lists.
+
+        When every entry brings a single token and the samplers need nothing beyond the sampling
+        kernel, the whole step (model and sampler) is replayed as a CUDA graph captured for the next
+        batch size in ``GRAPH_BUCKETS``; otherwise it is ``step`` followed by ``sampler``."""
+        from .decode_graph import DecodeGraph
+
+        n = len(entries)
+        ok = (self.use_graphs and n <= self.GRAPH_BUCKETS[-1] and all(len(e.tokens) == 1 for e in entries)
+              and DecodeGraph.samplers_fit(requests, sampler))
+        if not ok:
+            return sampler(self.step(entries), requests)
+        bucket = next(b for b in self.GRAPH_BUCKETS if b >= n)
+        graph = self._graphs.get(bucket)
+        if graph is None:
+            graph = self._graphs[bucket] = DecodeGraph(self, bucket)
+        return graph.run(entries, requests, sampler.seed)
 
     def read_status(self) -> int:
         """Bits kernels set instead of faulting (token, position or page id out of range).

@@ -199,6 +199,39 @@ def test_greedy_generation_through_the_entry_points(dtype, tmp_path):
     assert [int(t) for t in text.split()] == want[0][:first]
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_decode_as_a_cuda_graph_equals_the_eager_step(dtype, tmp_path):
+    """Pure decode steps are replayed as CUDA graphs per batch-size bucket; tokens and log-probabilities
+    must be those of the eager step, also for a batch smaller than its bucket and after requests left."""
+    from mlx_lm_b200 import load
+    from mlx_lm_b200.generate import BatchGenerator, get_engine
+    from mlx_lm_b200.sampling import make_sampler
+    make_model_dir(str(tmp_path), dict(CONFIG_B, ln_gain_std=0.3), 8, peaky=8.0)
+    model, _ = load(str(tmp_path), dtype=dtype)
+    prompts = [random_tokens(n, 1000, 50 + n) for n in (3, 17, 40, 33, 9)]       # 5 requests: bucket of 8
+    max_tokens = [30, 12, 25, 5, 18]
+
+    def run(use_graphs):
+        engine = get_engine(model, page_size=16, num_pages=64, max_requests=8)
+        engine.use_graphs = use_graphs
+        gen = BatchGenerator(model, engine=engine, sampler=make_sampler(0.7, top_k=20), seed=3,
+                             completion_batch_size=8, prefill_batch_size=8)
+        uids = gen.insert(prompts, max_tokens)
+        out = {u: [] for u in uids}
+        while gen.scheduler.has_work():
+            for r in gen.next_generated():
+                out[r.uid].append((r.token, round(r.logprobs, 4 if dtype == "float32" else 1)))
+        assert engine.cache.pages_in_use() == [0]
+        return [out[u] for u in uids], engine
+
+    eager, _ = run(False)
+    graphed, engine = run(True)
+    assert set(engine._graphs) >= {8, 4, 2, 1}           # the batch shrank through the buckets
+    assert [[t for t, _ in o] for o in eager] == [[t for t, _ in o] for o in graphed]
+    assert eager == graphed
+    engine.check_status()
+
+
 def test_temperature_sampling_does_not_depend_on_batching(tmp_path):
     from mlx_lm_b200 import load
     from mlx_lm_b200.generate import BatchGenerator
