@@ -183,6 +183,11 @@ def run_ours(args):
     engine = Engine(model, page_size=16, max_tokens=max_b * CONTEXT, max_requests=max_b)
     weight_bytes, kv_per_token, lin_flops = model_bytes_and_flops(cfg, cfg["n_layer"])
 
+    if args.only == "decode":
+        ms, launches, mean_ctx = decode_loop(engine, DeviceSampler, model, B, PROMPT_LEN, K, W, vocab)
+        print(json.dumps({"only": "decode", "batch": B, "ms_per_step": round(ms, 4), "launches_per_step": launches}))
+        return
+
     # ---- prefill: 2 x 1024 tokens in one step
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, vocab, (1024,), generator=g).tolist() for _ in range(2)]
@@ -205,6 +210,9 @@ def run_ours(args):
     pf_flops = 2048 * lin_flops + attn_flops + 2 * 2 * D * vocab
     prefill = {"value": round(2048 / (pf_ms / 1e3), 1), "tokens": 2048, "ms": round(pf_ms, 4),
                "frac": round(pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", **prefill}))
+        return
 
     # ---- decode, device-timed
     with ClockSampler() as clocks:
@@ -268,6 +276,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 24 (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
+                    help="run just this part and print its figures (for profiling a short run)")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

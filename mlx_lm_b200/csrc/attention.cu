@@ -23,9 +23,11 @@
 //            threads side by side on one key, so a warp reads contiguous
 //            runs), keeps a running (max, sum, weighted values) per thread
 //            group, merges the groups, and writes one partial (m, l, o[Dh]) to
-//            scratch memory.  The combine kernel folds a row's partials in
-//            chunk order.  The chunk length is a constant of the engine, not
-//            of the batch, so a row's result does not depend on its neighbours.
+//            scratch memory.  The CTA that finishes last for a (row, head) —
+//            found with a ticket counter that it resets to zero afterwards —
+//            folds that row's partials in chunk order and writes the output.
+//            The chunk length is a constant of the engine, not of the batch,
+//            so a row's result does not depend on its neighbours.
 #include "common.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
@@ -37,6 +39,8 @@ __global__ void kv_write_kernel(const T* __restrict__ k_src, const T* __restrict
                                 const int* __restrict__ block_table, int max_pages, int n_pages, int page,
                                 int Hkv, int Dh, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                 int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int p = positions[t];
   const int r = token_req[t];
@@ -73,6 +77,8 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, const int* __restrict
                          T* __restrict__ out, int ldo, const int* __restrict__ rows, int n_tokens,
                          int* __restrict__ status) {
   extern __shared__ float sq[];  // [warps][Dh]
+  pdl_trigger();
+  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int w = blockIdx.x * (blockDim.x >> 5) + warp;
   if (w >= n_tokens * Hq) return;
@@ -153,13 +159,13 @@ MLXB_EXPORT int mlxb_kv_write(int dtype, const void* k_src, const void* v_src, i
   if (int e = check_common("kv_write", page, Hkv, Hkv, Dh)) return e;
   const int threads = Hkv * Dh >= 512 ? 256 : 128;
   if (dtype == MLXB_F32)
-    kv_write_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)k_src, (const float*)v_src, ld, positions,
-                                                            token_req, block_table, max_pages, n_pages, page, Hkv, Dh,
-                                                            (float*)k_pool, (float*)v_pool, status);
+    launch_pdl(kv_write_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)k_src,
+               (const float*)v_src, ld, positions, token_req, block_table, max_pages, n_pages, page, Hkv, Dh,
+               (float*)k_pool, (float*)v_pool, status);
   else if (dtype == MLXB_BF16)
-    kv_write_kernel<__nv_bfloat16><<<n_tokens, threads, 0, stream>>>(
-        (const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, ld, positions, token_req, block_table, max_pages,
-        n_pages, page, Hkv, Dh, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, status);
+    launch_pdl(kv_write_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream,
+               (const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src, ld, positions, token_req, block_table,
+               max_pages, n_pages, page, Hkv, Dh, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, status);
   else
     return mlxb_fail(MLXB_BAD_DTYPE, "kv_write: dtype code %d", dtype);
   return mlxb_check_launch("kv_write");
@@ -179,11 +185,11 @@ MLXB_EXPORT int mlxb_attention_generic(int dtype, const void* q, int ldq, const 
   const int blocks = (int)((total + warps - 1) / warps);
   const size_t smem = (size_t)warps * Dh * sizeof(float);
   if (dtype == MLXB_F32)
-    attention_generic_kernel<float><<<blocks, warps * 32, smem, stream>>>(
+    launch_pdl(attention_generic_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
         (const float*)q, ldq, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, Dh, window, scale,
         (const float*)k_pool, (const float*)v_pool, (float*)out, ldo, rows, n_tokens, status);
   else if (dtype == MLXB_BF16)
-    attention_generic_kernel<__nv_bfloat16><<<blocks, warps * 32, smem, stream>>>(
+    launch_pdl(attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream,
         (const __nv_bfloat16*)q, ldq, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, Dh, window,
         scale, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, ldo, rows, n_tokens,
         status);
@@ -223,9 +229,13 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
                         const int* __restrict__ positions, const int* __restrict__ token_req,
                         const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                         int Dh, int window, float scale, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
-                        float* __restrict__ partial, int n_chunks_max, int chunk, int* __restrict__ status) {
+                        float* partial, int* counters, int n_chunks_max, int chunk, T* __restrict__ out, int ldo,
+                        int* __restrict__ status) {
   constexpr int GROUPS = DEC_THREADS / TPK;
   extern __shared__ float sm[];   // m[GROUPS] | l[GROUPS] | o[GROUPS][Dh]
+  __shared__ int s_last;
+  pdl_trigger();
+  pdl_wait();
   const int c = blockIdx.x, h = blockIdx.y, ri = blockIdx.z;
   const int t = rows ? rows[ri] : ri;
   const int r = token_req[t];
@@ -322,38 +332,39 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
     dst[0] = M;
     dst[1] = L;
   }
-}
 
-template <typename T>
-__global__ void attention_combine_kernel(const float* __restrict__ partial, const int* __restrict__ rows,
-                                         const int* __restrict__ positions, const int* __restrict__ token_req,
-                                         int Hq, int Dh, int window, int n_chunks_max, int chunk,
-                                         T* __restrict__ out, int ldo) {
-  const int h = blockIdx.x, ri = blockIdx.y;
-  const int t = rows ? rows[ri] : ri;
-  if (token_req[t] < 0) return;
-  const int p = positions[t];
-  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  // The last CTA of this (row, head) to get here combines all chunks.
   const int c0 = lo / chunk, c1 = p / chunk;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const int ticket = atomicAdd(&counters[ri * Hq + h], 1);
+    s_last = (ticket == c1 - c0);
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
   const float* src = partial + ((size_t)ri * Hq + h) * n_chunks_max * (Dh + 2);
-  float M = -INFINITY;
-  for (int c = c0; c <= c1; ++c) M = fmaxf(M, src[(size_t)c * (Dh + 2)]);
-  float L = 0.f;
-  for (int c = c0; c <= c1; ++c) L += src[(size_t)c * (Dh + 2) + 1] * expf(src[(size_t)c * (Dh + 2)] - M);
-  const float inv = L > 0.f ? 1.f / L : 0.f;
-  for (int d = threadIdx.x; d < Dh; d += blockDim.x) {
+  float Mx = -INFINITY;
+  for (int cc = c0; cc <= c1; ++cc) Mx = fmaxf(Mx, __ldcg(src + (size_t)cc * (Dh + 2)));
+  float Ls = 0.f;
+  for (int cc = c0; cc <= c1; ++cc)
+    Ls += __ldcg(src + (size_t)cc * (Dh + 2) + 1) * expf(__ldcg(src + (size_t)cc * (Dh + 2)) - Mx);
+  const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
+  for (int d = threadIdx.x; d < Dh; d += DEC_THREADS) {
     float acc = 0.f;
-    for (int c = c0; c <= c1; ++c)
-      acc = fmaf(expf(src[(size_t)c * (Dh + 2)] - M), src[(size_t)c * (Dh + 2) + 2 + d], acc);
+    for (int cc = c0; cc <= c1; ++cc)
+      acc = fmaf(expf(__ldcg(src + (size_t)cc * (Dh + 2)) - Mx), __ldcg(src + (size_t)cc * (Dh + 2) + 2 + d), acc);
     out[(size_t)t * ldo + h * Dh + d] = from_f<T>(acc * inv);
   }
+  if (threadIdx.x == 0) counters[ri * Hq + h] = 0;   // ready for the next call
 }
 
 template <typename T>
 static int launch_decode(const void* q, int ldq, const int* rows, const int* positions, const int* token_req,
                          const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv, int Dh,
                          int window, float scale, const void* k_pool, const void* v_pool, float* partial,
-                         int n_chunks_max, int chunk, void* out, int ldo, int n_rows, int* status,
+                         int* counters, int n_chunks_max, int chunk, void* out, int ldo, int n_rows, int* status,
                          cudaStream_t stream) {
   const int chunks8 = (Dh + 7) / 8;
   int tpk = 2;
@@ -362,17 +373,13 @@ static int launch_decode(const void* q, int ldq, const int* rows, const int* pos
 #define DEC(TPK_)                                                                                                    \
   {                                                                                                                  \
     const size_t smem = (size_t)(DEC_THREADS / TPK_) * (Dh + 2) * sizeof(float);                                     \
-    attention_decode_kernel<T, TPK_><<<grid, DEC_THREADS, smem, stream>>>(                                           \
-        (const T*)q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, Dh, window,    \
-        scale, (const T*)k_pool, (const T*)v_pool, partial, n_chunks_max, chunk, status);                            \
+    launch_pdl(attention_decode_kernel<T, TPK_>, grid, dim3(DEC_THREADS), smem, stream, (const T*)q, ldq, rows,      \
+               positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, Dh, window, scale,              \
+               (const T*)k_pool, (const T*)v_pool, partial, counters, n_chunks_max, chunk, (T*)out, ldo, status);    \
   }
   if (tpk == 2) DEC(2) else if (tpk == 4) DEC(4) else if (tpk == 8) DEC(8) else if (tpk == 16) DEC(16) else DEC(32)
 #undef DEC
-  if (int e = mlxb_check_launch("attention (single-token rows)")) return e;
-  const int threads = Dh <= 32 ? 32 : (Dh <= 64 ? 64 : 128);
-  attention_combine_kernel<T><<<dim3(Hq, n_rows), threads, 0, stream>>>(partial, rows, positions, token_req, Hq, Dh,
-                                                                        window, n_chunks_max, chunk, (T*)out, ldo);
-  return mlxb_check_launch("attention combine");
+  return mlxb_check_launch("attention (single-token rows)");
 }
 
 // Floats of scratch that n_rows rows need.
@@ -382,13 +389,14 @@ MLXB_EXPORT long long mlxb_attention_decode_scratch(int n_rows, int Hq, int Dh, 
 
 // Rows with one query each.  rows: int32[n_rows] token indices or null (tokens 0..n_rows-1).
 // n_chunks_max * chunk must cover every position a row may have; partial: float32 scratch of
-// mlxb_attention_decode_scratch() floats, contents need not be initialised.
+// mlxb_attention_decode_scratch() floats, contents need not be initialised; counters: int32[n_rows * Hq]
+// that must be ZERO before the first call and are left zero by every call.
 // Dh must be a multiple of 8 (16 for bfloat16 alignment is implied by pages); q rows 16-byte aligned.
 MLXB_EXPORT int mlxb_attention_decode(int dtype, const void* q, int ldq, const int* rows, const int* positions,
                                       const int* token_req, const int* block_table, int max_pages, int n_pages,
                                       int page, int Hq, int Hkv, int Dh, int window, float scale, const void* k_pool,
-                                      const void* v_pool, float* partial, int n_chunks_max, int chunk, void* out,
-                                      int ldo, int n_rows, int* status, cudaStream_t stream) {
+                                      const void* v_pool, float* partial, int* counters, int n_chunks_max, int chunk,
+                                      void* out, int ldo, int n_rows, int* status, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (int e = check_common("attention (single-token rows)", page, Hq, Hkv, Dh)) return e;
   if (Dh % 8) return mlxb_fail(MLXB_BAD_ARG, "attention (single-token rows): head size %d is not a multiple of 8", Dh);
@@ -400,12 +408,12 @@ MLXB_EXPORT int mlxb_attention_decode(int dtype, const void* q, int ldq, const i
     return mlxb_fail(MLXB_BAD_ARG, "attention (single-token rows): query rows and heads must be 16-byte aligned");
   if (dtype == MLXB_F32)
     return launch_decode<float>(q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv,
-                                Dh, window, scale, k_pool, v_pool, partial, n_chunks_max, chunk, out, ldo, n_rows,
-                                status, stream);
+                                Dh, window, scale, k_pool, v_pool, partial, counters, n_chunks_max, chunk, out, ldo,
+                                n_rows, status, stream);
   if (dtype == MLXB_BF16)
     return launch_decode<__nv_bfloat16>(q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page, Hq,
-                                        Hkv, Dh, window, scale, k_pool, v_pool, partial, n_chunks_max, chunk, out,
-                                        ldo, n_rows, status, stream);
+                                        Hkv, Dh, window, scale, k_pool, v_pool, partial, counters, n_chunks_max, chunk,
+                                        out, ldo, n_rows, status, stream);
   return mlxb_fail(MLXB_BAD_DTYPE, "attention (single-token rows): dtype code %d", dtype);
 }
 
@@ -417,7 +425,11 @@ MLXB_EXPORT int mlxb_attention_decode(int dtype, const void* q, int ldq, const i
 // a handle for the runtime: the address kernels can use comes from cudaGetSymbolAddress below.
 static __device__ __align__(256) float g_noalloc_partial[MLXB_NOALLOC_SCRATCH_FLOATS];
 
-static float* g_noalloc_partial_ptr[64];   // device address of the array, per device ordinal
+// Ticket counters of the kernel, one per (row, head); zero when the library is loaded and left zero by every call.
+static __device__ __align__(256) int g_noalloc_counters[MLXB_NOALLOC_COUNTERS];
+
+static float* g_noalloc_partial_ptr[64];   // device addresses of the arrays, per device ordinal
+static int* g_noalloc_counters_ptr[64];
 
 MLXB_EXPORT int mlxb_attention_decode_noalloc(int dtype, const void* q, int ldq, const int* rows,
                                               const int* positions, const int* token_req, const int* block_table,
@@ -435,6 +447,9 @@ MLXB_EXPORT int mlxb_attention_decode_noalloc(int dtype, const void* q, int ldq,
                      "attention (no allocation): %d rows x %d heads x %d chunks x (%d + 2) = %lld floats of scratch, "
                      "the built-in array holds %d",
                      n_rows, n_q_heads, n_chunks_max, head_dim, need, (int)MLXB_NOALLOC_SCRATCH_FLOATS);
+  if ((long long)n_rows * n_q_heads > (long long)MLXB_NOALLOC_COUNTERS)
+    return mlxb_fail(MLXB_BAD_ARG, "attention (no allocation): %d rows x %d heads, the built-in counters hold %d",
+                     n_rows, n_q_heads, (int)MLXB_NOALLOC_COUNTERS);
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return mlxb_fail((int)e, "attention (no allocation): cudaGetDevice: %s", cudaGetErrorString(e));
@@ -445,9 +460,16 @@ MLXB_EXPORT int mlxb_attention_decode_noalloc(int dtype, const void* q, int ldq,
     if (e != cudaSuccess || p == nullptr)
       return mlxb_fail(e != cudaSuccess ? (int)e : MLXB_BAD_ARG,
                        "attention (no allocation): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    int* cnt = nullptr;
+    e = cudaGetSymbolAddress((void**)&cnt, g_noalloc_counters);
+    if (e != cudaSuccess || cnt == nullptr)
+      return mlxb_fail(e != cudaSuccess ? (int)e : MLXB_BAD_ARG,
+                       "attention (no allocation): cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+    g_noalloc_counters_ptr[dev] = cnt;
     g_noalloc_partial_ptr[dev] = p;
   }
   return mlxb_attention_decode(dtype, q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page,
                                n_q_heads, n_kv_heads, head_dim, window, scale, k_pool, v_pool,
-                               g_noalloc_partial_ptr[dev], n_chunks_max, chunk, out, ldo, n_rows, status, stream);
+                               g_noalloc_partial_ptr[dev], g_noalloc_counters_ptr[dev], n_chunks_max, chunk, out, ldo,
+                               n_rows, status, stream);
 }

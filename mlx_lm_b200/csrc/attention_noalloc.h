@@ -12,7 +12,8 @@
 // has no allocator of its own to ask.  For them this variant keeps the scratch
 // in a fixed array inside the library.
 //
-// What it costs.  The array is MLXB_NOALLOC_SCRATCH_FLOATS float32 (4 MiB).
+// What it costs.  The array is MLXB_NOALLOC_SCRATCH_FLOATS float32 (4 MiB), plus
+// MLXB_NOALLOC_COUNTERS int32 ticket counters (256 KiB) for n_rows * n_q_heads.
 // Every GPU on which the library is loaded holds it from load until the process
 // exits, whether or not this function is ever called.
 //
@@ -28,9 +29,12 @@
 // stream capture, so make the first call on a device outside any capture.
 //
 // Sharing.  All calls on a device use the same array, and it keeps whatever the
-// previous call left there.  Nothing in it has to start at zero: every partial
-// result the second kernel reads has been written by the first kernel of the
-// same call.  Two calls that overlap on the GPU (different streams, or graphs
+// previous call left there.  No partial result has to start at zero: each one
+// that is read has been written earlier in the same call.  The ticket counters
+// do have to be zero at the start of a call; they are zero when the library is
+// loaded and the kernel puts each one back to zero itself, so a caller has
+// nothing to clear (a call that was aborted by a device fault would leave them
+// undefined, as it leaves the whole context).  Two calls that overlap on the GPU (different streams, or graphs
 // replayed concurrently) would overwrite each other's partial results: run calls
 // on one device one after the other, i.e. on one stream.
 //
@@ -42,6 +46,7 @@
 #include <cuda_runtime.h>
 
 #define MLXB_NOALLOC_SCRATCH_FLOATS (1 << 20)
+#define MLXB_NOALLOC_COUNTERS (1 << 16)
 
 #ifdef __cplusplus
 extern "C" {

@@ -9,6 +9,7 @@
 #include <stdarg.h>
 #include <stdint.h>
 #include <stdio.h>
+#include <stdlib.h>
 #include <string.h>
 
 #define MLXB_EXPORT extern "C" __attribute__((visibility("default")))
@@ -48,6 +49,42 @@ static inline int mlxb_check_launch(const char* what) {
     return (int)e;
   }
   return 0;
+}
+
+// ---- programmatic dependent launch
+// Kernels of a step run one after the other on one stream, each a few microseconds long, so the
+// gap between them matters.  A kernel launched with launch_pdl() may start while its predecessor
+// is still running: it must call pdl_wait() before it reads anything the predecessor wrote or
+// writes anything the predecessor may still read; what it does before that (index arithmetic,
+// prefetching weights, which no kernel writes) overlaps the predecessor's tail.  pdl_trigger()
+// lets the successor start early in the same way.  MLXB_PDL=0 in the environment turns the
+// attribute off (every kernel then starts after its predecessor has finished, as usual).
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+static inline bool mlxb_pdl_enabled() {
+  static int on = -1;
+  if (on < 0) {
+    const char* e = getenv("MLXB_PDL");
+    on = (e && e[0] == '0') ? 0 : 1;
+  }
+  return on == 1;
+}
+
+template <typename... KArgs, typename... Args>
+static inline cudaError_t launch_pdl(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     cudaStream_t stream, Args... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = mlxb_pdl_enabled() ? 1 : 0;
+  return cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
 #define MLXB_DEFINE_LAST_ERROR()                                   \

@@ -13,6 +13,8 @@ __global__ void embed_pos_kernel(const int* __restrict__ tok, const int* __restr
                                  const T* __restrict__ wte, const T* __restrict__ wpe,
                                  T* __restrict__ out, int D, int V, int P, float scale,
                                  int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
   const int t = blockIdx.x;
   const int id = tok[t];
   const int p = wpe ? pos[t] : 0;

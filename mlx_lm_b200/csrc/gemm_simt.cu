@@ -23,6 +23,8 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, const float* 
                  int lda, int ldc) {
   __shared__ float sA[BK][BM + 4];
   __shared__ float sW[BK][BN + 4];
+  pdl_trigger();
+  pdl_wait();
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads; thread owns rows ty*4.., cols tx*4..
@@ -80,11 +82,11 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
                   int K, int lda, int ldc, int epi, cudaStream_t stream) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   if (epi == EPI_NONE)
-    gemm_simt_kernel<T, TO, EPI_NONE><<<grid, 256, 0, stream>>>((const T*)A, (const T*)W, bias, (const T*)residual,
-                                                                 (TO*)C, M, N, K, lda, ldc);
+    launch_pdl(gemm_simt_kernel<T, TO, EPI_NONE>, grid, dim3(256), 0, stream, (const T*)A, (const T*)W, bias,
+               (const T*)residual, (TO*)C, M, N, K, lda, ldc);
   else if (epi == EPI_GELU_NEW)
-    gemm_simt_kernel<T, TO, EPI_GELU_NEW><<<grid, 256, 0, stream>>>((const T*)A, (const T*)W, bias,
-                                                                     (const T*)residual, (TO*)C, M, N, K, lda, ldc);
+    launch_pdl(gemm_simt_kernel<T, TO, EPI_GELU_NEW>, grid, dim3(256), 0, stream, (const T*)A, (const T*)W, bias,
+               (const T*)residual, (TO*)C, M, N, K, lda, ldc);
   else
     return mlxb_fail(MLXB_BAD_ARG, "linear: epilogue code %d", epi);
   return mlxb_check_launch("linear (generic)");

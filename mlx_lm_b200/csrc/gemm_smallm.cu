@@ -18,6 +18,15 @@
 // The 8 partial sums of a CTA are added in warp order through shared memory;
 // the order of additions depends on K alone, never on M or on the batch.
 // K must be a multiple of 8 (16-byte loads); other K go to the generic kernel.
+//
+// Launch gaps: the kernel is launched as a programmatic dependent (common.cuh).  Before it
+// waits for its predecessor it asks L2 for its whole slab of W and loads its first weight
+// fragments, so the weight stream of one layer overlaps the tail of the kernel before it.
+//
+// Fused cache write: with a KvScatter argument the output is the fused [q | k | v] projection of an
+// attention layer; q columns go to C as usual, k and v columns go straight into the request's
+// pages (the element for token m, head h, dim d lands in page block_table[req][pos / page], row
+// pos % page), which saves the separate cache-write kernel of a decode step.
 #include "common.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
@@ -45,12 +54,22 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
+struct KvScatter {
+  const int* positions;     // [M]
+  const int* token_req;     // [M] row of the block table, < 0 for padding rows
+  const int* block_table;   // [*, max_pages]
+  __nv_bfloat16* k_pool;    // [n_pages, Hkv, page, Dh]
+  __nv_bfloat16* v_pool;
+  int* status;
+  int max_pages, n_pages, page, Hkv, Dh, q_width;
+};
+
 // MT: 16-row token tiles (M <= 16*MT); NW: 8-row weight tiles per CTA.
-template <int MT, int NW, typename TO, int EPI>
+template <int MT, int NW, typename TO, int EPI, bool SCATTER>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                    const float* __restrict__ bias, const __nv_bfloat16* residual, TO* C, int M, int N, int K,
-                   int lda, int ldc) {
+                   int lda, int ldc, KvScatter kv) {
   extern __shared__ float part[];   // [WARPS][MT*NW*4][32]
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int g = lane >> 2, q = lane & 3;
@@ -85,21 +104,48 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     }
 
   const int n_blocks = (K + 31) >> 5;
-  constexpr int UNROLL = (MT * NW >= 8) ? 1 : 2;   // K blocks in flight per warp
-  for (int kb = warp; kb < n_blocks; kb += WARPS * UNROLL) {
-    uint4 wv[UNROLL][NW];
-    uint4 av[UNROLL][MT][2];
+  constexpr int UNROLL = (MT * NW >= 8) ? 1 : 2;   // K blocks per warp and iteration
+  constexpr int STEP = WARPS * UNROLL;
+
+  auto load_w = [&](int kb, uint4 (&dst)[UNROLL][NW]) {
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (kb + u * WARPS) * 32;
       const bool kin = (kb + u * WARPS) < n_blocks && (k + 8 * q) < K;   // K % 8 == 0: a chunk is all in or all out
 #pragma unroll
-      for (int j = 0; j < NW; ++j) wv[u][j] = (kin && wok[j]) ? ldg_stream(wrow[j] + k) : zero;
+      for (int j = 0; j < NW; ++j) dst[u][j] = (kin && wok[j]) ? ldg_stream(wrow[j] + k) : zero;
+    }
+  };
+
+  // Before waiting for the previous kernel: everything that touches only W.
+  pdl_trigger();
+  {
+    const int lines_per_row = (K * 2 + 127) >> 7;
+    for (int i = threadIdx.x; i < 8 * NW * lines_per_row; i += WARPS * 32) {
+      const int rrow = i / lines_per_row, n = n0 + rrow;
+      if (n < N) {
+        const char* p = reinterpret_cast<const char*>(W + (size_t)n * K) + (size_t)(i - rrow * lines_per_row) * 128;
+        asm volatile("prefetch.global.L2 [%0];" ::"l"(p));
+      }
+    }
+  }
+  uint4 wv[UNROLL][NW];
+  load_w(warp, wv);
+  pdl_wait();
+
+  for (int kb = warp; kb < n_blocks; kb += STEP) {
+    uint4 av[UNROLL][MT][2];
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u) {
+      const int k = (kb + u * WARPS) * 32;
+      const bool kin = (kb + u * WARPS) < n_blocks && (k + 8 * q) < K;
 #pragma unroll
       for (int i = 0; i < MT; ++i)
 #pragma unroll
         for (int h = 0; h < 2; ++h) av[u][i][h] = (kin && aok[i][h]) ? ldg_cached(arow[i][h] + k) : zero;
     }
+    uint4 wn[UNROLL][NW];
+    load_w(kb + STEP, wn);          // next iteration's weights are in flight while this one multiplies
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)
 #pragma unroll
@@ -109,6 +155,10 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
           mma_bf16(acc[i][j], av[u][i][0].x, av[u][i][1].x, av[u][i][0].y, av[u][i][1].y, wv[u][j].x, wv[u][j].y);
           mma_bf16(acc[i][j], av[u][i][0].z, av[u][i][1].z, av[u][i][0].w, av[u][i][1].w, wv[u][j].z, wv[u][j].w);
         }
+#pragma unroll
+    for (int u = 0; u < UNROLL; ++u)
+#pragma unroll
+      for (int j = 0; j < NW; ++j) wv[u][j] = wn[u][j];
   }
 
   constexpr int PER = MT * NW * 4;
@@ -131,32 +181,53 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
       if (bias) v += bias[n];
       if (EPI == EPI_GELU_NEW) v = gelu_new_f(v);
       if (residual) v += __bfloat162float(residual[(size_t)m * ldc + n]);
-      C[(size_t)m * ldc + n] = from_f<TO>(v);
+      if (SCATTER && n >= kv.q_width) {
+        const int r = kv.token_req[m];
+        if (r >= 0) {
+          const int pos = kv.positions[m];
+          const int lp = pos / kv.page;
+          const int pg = (pos >= 0 && lp < kv.max_pages) ? kv.block_table[(size_t)r * kv.max_pages + lp] : -2;
+          if (pg == -2) {
+            atomicOr(kv.status, MLXB_ST_POSITION_RANGE);
+          } else if (pg >= kv.n_pages) {
+            atomicOr(kv.status, MLXB_ST_PAGE_RANGE);
+          } else if (pg >= 0) {
+            const int kvw = kv.Hkv * kv.Dh;
+            int c2 = n - kv.q_width;
+            __nv_bfloat16* pool = kv.k_pool;
+            if (c2 >= kvw) { c2 -= kvw; pool = kv.v_pool; }
+            const int hh = c2 / kv.Dh, d = c2 - hh * kv.Dh;
+            pool[(((size_t)pg * kv.Hkv + hh) * kv.page + (pos % kv.page)) * kv.Dh + d] = __float2bfloat16_rn(v);
+          }
+        }
+      } else {
+        C[(size_t)m * ldc + n] = from_f<TO>(v);
+      }
     }
   }
 }
 
-template <int MT, int NW, typename TO>
+template <int MT, int NW, typename TO, bool SCATTER>
 static int launch_epi(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N,
-                      int K, int lda, int ldc, int epi, cudaStream_t stream) {
+                      int K, int lda, int ldc, int epi, const KvScatter& kv, cudaStream_t stream) {
   const dim3 grid((N + 8 * NW - 1) / (8 * NW));
   const size_t smem = (size_t)WARPS * MT * NW * 4 * 32 * sizeof(float);
-  auto k0 = gemm_smallm_kernel<MT, NW, TO, EPI_NONE>;
-  auto k1 = gemm_smallm_kernel<MT, NW, TO, EPI_GELU_NEW>;
+  auto k0 = gemm_smallm_kernel<MT, NW, TO, EPI_NONE, SCATTER>;
+  auto k1 = gemm_smallm_kernel<MT, NW, TO, EPI_GELU_NEW, SCATTER>;
   auto kern = epi == EPI_GELU_NEW ? k1 : k0;
   static bool raised[2] = {false, false};   // once per instantiation, and never for the first time inside a stream capture
   if (smem > 48 * 1024 && !raised[epi == EPI_GELU_NEW]) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     raised[epi == EPI_GELU_NEW] = true;
   }
-  kern<<<grid, WARPS * 32, smem, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias,
-                                           (const __nv_bfloat16*)residual, (TO*)C, M, N, K, lda, ldc);
+  launch_pdl(kern, grid, dim3(WARPS * 32), smem, stream, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias,
+             (const __nv_bfloat16*)residual, (TO*)C, M, N, K, lda, ldc, kv);
   return mlxb_check_launch("linear (few rows)");
 }
 
-template <typename TO>
+template <typename TO, bool SCATTER>
 static int launch(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N, int K,
-                  int lda, int ldc, int epi, cudaStream_t stream) {
+                  int lda, int ldc, int epi, const KvScatter& kv, cudaStream_t stream) {
   // Weight tiles per CTA: as many as keep at least ~2 CTAs per SM; more tiles re-use each
   // activation fragment for more weight rows, which matters once M is large.
   const int tiles = (N + 7) / 8;
@@ -164,7 +235,8 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
   int nw = 1;
   if (mt == 4) nw = tiles >= 4 * 296 ? 4 : (tiles >= 2 * 148 ? 2 : 1);
   else if (mt == 2) nw = tiles >= 2 * 296 ? 2 : 1;
-#define GO(MT_, NW_) return launch_epi<MT_, NW_, TO>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, stream)
+#define GO(MT_, NW_) \
+  return launch_epi<MT_, NW_, TO, SCATTER>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, kv, stream)
   if (mt == 1) GO(1, 1);
   if (mt == 2) { if (nw == 2) GO(2, 2); GO(2, 1); }
   if (nw == 4) GO(4, 4);
@@ -173,12 +245,7 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
 #undef GO
 }
 
-// A: bfloat16 [M, K] at row stride lda (elements, multiple of 8, base 16-byte aligned);
-// W: bfloat16 [N, K] contiguous; bias float32[N] or null; residual bfloat16 [M, N] at row stride ldc or null;
-// C: bfloat16 or float32 (out_f32) [M, N] at row stride ldc.  1 <= M <= 64, K % 8 == 0.
-MLXB_EXPORT int mlxb_linear_smallm(int out_f32, const void* A, const void* W, const float* bias, const void* residual,
-                                   void* C, int M, int N, int K, int lda, int ldc, int epi, cudaStream_t stream) {
-  if (M <= 0 || N <= 0) return 0;
+static int check_args(int M, int N, int K, int lda, int ldc, int epi, const void* A, const void* W) {
   if (M > 64) return mlxb_fail(MLXB_BAD_ARG, "linear (few rows): %d rows, at most 64", M);
   if (K <= 0 || (K & 7) || (lda & 7) || lda < K || ldc < N)
     return mlxb_fail(MLXB_BAD_ARG, "linear (few rows): K %d and row stride %d must be multiples of 8 (ldc %d, N %d)",
@@ -186,6 +253,34 @@ MLXB_EXPORT int mlxb_linear_smallm(int out_f32, const void* A, const void* W, co
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15))
     return mlxb_fail(MLXB_BAD_ARG, "linear (few rows): operands must be 16-byte aligned");
   if (epi != EPI_NONE && epi != EPI_GELU_NEW) return mlxb_fail(MLXB_BAD_ARG, "linear: epilogue code %d", epi);
-  if (out_f32) return launch<float>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, stream);
-  return launch<__nv_bfloat16>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, stream);
+  return 0;
+}
+
+// A: bfloat16 [M, K] at row stride lda (elements, multiple of 8, base 16-byte aligned);
+// W: bfloat16 [N, K] contiguous; bias float32[N] or null; residual bfloat16 [M, N] at row stride ldc or null;
+// C: bfloat16 or float32 (out_f32) [M, N] at row stride ldc.  1 <= M <= 64, K % 8 == 0.
+MLXB_EXPORT int mlxb_linear_smallm(int out_f32, const void* A, const void* W, const float* bias, const void* residual,
+                                   void* C, int M, int N, int K, int lda, int ldc, int epi, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (int e = check_args(M, N, K, lda, ldc, epi, A, W)) return e;
+  const KvScatter none = {};
+  if (out_f32) return launch<float, false>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, stream);
+  return launch<__nv_bfloat16, false>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, stream);
+}
+
+// The fused [q | k | v] projection of an attention layer with the cache write in its epilogue:
+// columns [0, q_width) go to C (bfloat16, row stride ldc); the Hkv*Dh key columns and the Hkv*Dh value
+// columns after them go into k_pool / v_pool [n_pages, Hkv, page, Dh] at each token's page and row.
+// N must equal q_width + 2*Hkv*Dh.  Rows with token_req < 0 (padding) write no keys or values.
+MLXB_EXPORT int mlxb_linear_smallm_qkv(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
+                                       int lda, int ldc, const int* positions, const int* token_req,
+                                       const int* block_table, int max_pages, int n_pages, int page, int Hkv, int Dh,
+                                       int q_width, void* k_pool, void* v_pool, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (int e = check_args(M, N, K, lda, ldc, EPI_NONE, A, W)) return e;
+  if (Hkv <= 0 || Dh <= 0 || page <= 0 || q_width < 0 || N != q_width + 2 * Hkv * Dh)
+    return mlxb_fail(MLXB_BAD_ARG, "linear (q|k|v): %d outputs for %d query columns and 2 x %d x %d", N, q_width, Hkv, Dh);
+  KvScatter kv = {positions, token_req, block_table, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, status,
+                  max_pages, n_pages, page, Hkv, Dh, q_width};
+  return launch<__nv_bfloat16, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, kv, stream);
 }

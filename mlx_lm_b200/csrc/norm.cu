@@ -16,6 +16,8 @@ __global__ void layernorm_kernel(const T* __restrict__ x, const int* __restrict_
                                  T* __restrict__ y, int D, float eps) {
   extern __shared__ float srow[];  // D floats + 33 for the reductions
   float* red = srow + D;
+  pdl_trigger();
+  pdl_wait();
   const int r = blockIdx.x;
   const T* xi = x + (size_t)(rows ? rows[r] : r) * D;
   float s = 0.f;
@@ -51,13 +53,14 @@ MLXB_EXPORT int mlxb_layernorm(int dtype, const void* x, const int* rows, const 
   if (dtype == MLXB_F32) {
     if (smem > 48 * 1024)   // 227 KB is the most a CTA can have; set once to the largest width this file accepts
       cudaFuncSetAttribute(layernorm_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (49152 + 40) * 4);
-    layernorm_kernel<float><<<R, threads, smem, stream>>>((const float*)x, rows, gain, bias, (float*)y, D, eps);
+    launch_pdl(layernorm_kernel<float>, dim3(R), dim3(threads), smem, stream, (const float*)x, rows, gain, bias,
+               (float*)y, D, eps);
   } else if (dtype == MLXB_BF16) {
     if (smem > 48 * 1024)
       cudaFuncSetAttribute(layernorm_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                            (49152 + 40) * 4);
-    layernorm_kernel<__nv_bfloat16><<<R, threads, smem, stream>>>((const __nv_bfloat16*)x, rows, gain, bias,
-                                                                   (__nv_bfloat16*)y, D, eps);
+    launch_pdl(layernorm_kernel<__nv_bfloat16>, dim3(R), dim3(threads), smem, stream, (const __nv_bfloat16*)x, rows,
+               gain, bias, (__nv_bfloat16*)y, D, eps);
   } else {
     return mlxb_fail(MLXB_BAD_DTYPE, "layernorm: dtype code %d", dtype);
   }

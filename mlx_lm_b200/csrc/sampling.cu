@@ -126,6 +126,8 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleParam
               float* __restrict__ out_logprob, float* __restrict__ out_logprobs, int ldo) {
   __shared__ float redf[40];
   __shared__ int redi[40];
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   const float* lg = logits + (size_t)row * ld;
   const SampleParams P = params[row];
@@ -253,8 +255,8 @@ MLXB_EXPORT int mlxb_sample(const float* logits, int ld, int R, int V, const voi
   if (V <= 0 || ld < V) return mlxb_fail(MLXB_BAD_ARG, "sample: vocabulary %d, row stride %d", V, ld);
   if (n_special < 0 || n_special > 64) return mlxb_fail(MLXB_BAD_ARG, "sample: %d special tokens (at most 64)", n_special);
   const int threads = V >= 16384 ? 1024 : (V >= 2048 ? 512 : 256);
-  sample_kernel<<<R, threads, 0, stream>>>(logits, ld, V, (const SampleParams*)params, xtc_special, n_special,
-                                           out_token, out_logprob, out_logprobs, ldo);
+  launch_pdl(sample_kernel, dim3(R), dim3(threads), 0, stream, logits, ld, V, (const SampleParams*)params,
+             xtc_special, n_special, out_token, out_logprob, out_logprobs, ldo);
   return mlxb_check_launch("sample");
 }
 
@@ -269,6 +271,8 @@ struct ProcessParams {   // 8 x 32-bit words per row
 __global__ void process_kernel(float* __restrict__ logits, int ld, int V, const ProcessParams* __restrict__ params,
                                const int* __restrict__ context, int C, const int* __restrict__ bias_index,
                                const float* __restrict__ bias_value, int B) {
+  pdl_trigger();
+  pdl_wait();
   const int row = blockIdx.x;
   float* lg = logits + (size_t)row * ld;
   const ProcessParams P = params[row];

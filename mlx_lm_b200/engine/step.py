@@ -60,8 +60,8 @@ class Workspace:
         key = (tag, 0, dtype)
         buf = self._bufs.get(key)
         if buf is None or buf.numel() < n:
-            buf = torch.empty(max(n, 1024, 2 * (buf.numel() if buf is not None else 0)), dtype=dtype,
-                              device=self.device)
+            buf = torch.zeros(max(n, 1024, 2 * (buf.numel() if buf is not None else 0)), dtype=dtype,
+                              device=self.device)   # zero: ticket counters of kernels start from zero
             self._bufs[key] = buf
         return buf
 

@@ -213,6 +213,33 @@ def linear_few_rows(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=
           _p(residual), _p(out), M, N, K, lda, ldc, epilogue, stream)
 
 
+_QKV_ARGS = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+             c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
+
+
+def linear_qkv_to_cache(x, w, bias, out, positions, token_req, block_table, k_pool, v_pool, q_width: int, status,
+                        stream) -> None:
+    """The fused ``[q | k | v]`` projection of at most 64 bfloat16 rows with the cache write in its epilogue:
+    query columns go to ``out[:, :q_width]``, key and value columns straight into the pages
+    ``[n_pages, Hkv, page, Dh]`` (the other columns of ``out`` are not written)."""
+    _need(x, torch.bfloat16, "linear x")
+    _need(w, torch.bfloat16, "linear w")
+    _need(out, torch.bfloat16, "linear out")
+    _need(k_pool, torch.bfloat16, "linear k_pool")
+    M, K = x.shape
+    N = w.shape[0]
+    n_pages, Hkv, page, Dh = k_pool.shape
+    if w.shape[1] != K or not w.is_contiguous() or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    if N != q_width + 2 * Hkv * Dh or not (k_pool.is_contiguous() and v_pool.is_contiguous()):
+        raise KernelError(f"linear (q|k|v): {N} outputs for {q_width} query columns and pools {tuple(k_pool.shape)}")
+    if bias is not None:
+        _need(bias, torch.float32, "linear bias")
+    _call("gemm_smallm", "mlxb_linear_smallm_qkv", _QKV_ARGS, _p(x), _p(w), _p(bias), _p(out), M, N, K,
+          _rows(x, "linear x"), _rows(out, "linear out"), _p(positions), _p(token_req), _p(block_table),
+          block_table.shape[1], n_pages, page, Hkv, Dh, q_width, _p(k_pool), _p(v_pool), _p(status), stream)
+
+
 # --------------------------------------------------------------------------
 # paged key/value cache and attention
 
@@ -265,7 +292,8 @@ def attention_generic(q, positions, token_req, block_table, k_pool, v_pool, out,
 
 
 _DEC_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-             c_int, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p]
+             c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
+             c_void_p]
 
 DECODE_CHUNK = 128   # key positions per CTA of the single-token attention kernel: a constant, never a function of the batch
 
@@ -276,19 +304,23 @@ def attention_decode_scratch(n_rows: int, n_heads: int, head_dim: int, max_len: 
 
 
 def attention_decode(q, positions, token_req, block_table, k_pool, v_pool, out, n_heads: int, scale: float,
-                     window: int, scratch, max_len: int, status, stream, rows=None, chunk: int = DECODE_CHUNK) -> None:
+                     window: int, scratch, counters, max_len: int, status, stream, rows=None,
+                     chunk: int = DECODE_CHUNK) -> None:
     """Attention for rows with a single query each (decode steps): keys are cut into chunks of ``chunk``
     positions, one CTA per (chunk, head, row) writes a partial result to ``scratch`` (float32, at least
-    ``attention_decode_scratch(...)`` elements) and a second kernel combines them."""
+    ``attention_decode_scratch(...)`` elements) and the CTA that finishes last for a (row, head) combines
+    them.  ``counters``: int32, at least rows x heads, zero before the first call (every call leaves it zero)."""
     n_pages, Hkv, page, Dh = _attn_shapes(q, out, k_pool, n_heads, "attention_decode")
     n = q.shape[0] if rows is None else rows.numel()
     n_chunks = (max_len + chunk - 1) // chunk
     _need(scratch, torch.float32, "attention_decode scratch")
-    if scratch.numel() < n * n_heads * n_chunks * (Dh + 2):
-        raise KernelError(f"attention_decode: scratch of {scratch.numel()} floats for {n} rows")
+    _need(counters, torch.int32, "attention_decode counters")
+    if scratch.numel() < n * n_heads * n_chunks * (Dh + 2) or counters.numel() < n * n_heads:
+        raise KernelError(f"attention_decode: scratch of {scratch.numel()} floats, {counters.numel()} counters "
+                          f"for {n} rows")
     _call("attention", "mlxb_attention_decode", _DEC_ARGS, dtype_code(k_pool.dtype), _p(q), _rows(q, "attention q"),
           _p(rows), _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv,
-          Dh, window, scale, _p(k_pool), _p(v_pool), _p(scratch), n_chunks, chunk, _p(out),
+          Dh, window, scale, _p(k_pool), _p(v_pool), _p(scratch), _p(counters), n_chunks, chunk, _p(out),
           _rows(out, "attention out"), n, _p(status), stream)
 
 

@@ -50,15 +50,22 @@ class Attention(Mixer):
 
     def forward(self, ctx, x, residual, cache):
         T = x.shape[0]
-        qkv = self.qkv.forward(ctx, x, ctx.ws.get("qkv", T, self.q_width + 2 * self.kv_width, x.dtype))
+        qkv = ctx.ws.get("qkv", T, self.q_width + 2 * self.kv_width, x.dtype)
         q = qkv[:, :self.q_width]
-        k = qkv[:, self.q_width:self.q_width + self.kv_width]
-        v = qkv[:, self.q_width + self.kv_width:]
-        if self.position is not None:
-            self.position.rotate(ctx, q, k)
-        if cache.write:
-            ops.kv_write(k, v, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, ctx.status,
-                         ctx.stream)
+        if (cache.write and self.position is None and x.dtype == torch.bfloat16 and T <= ops.SMALL_M
+                and self.width % 8 == 0):
+            # few rows: the projection's epilogue puts keys and values into the pages itself
+            ops.linear_qkv_to_cache(x, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, ctx.token_req,
+                                    cache.block_table, cache.k, cache.v, self.q_width, ctx.status, ctx.stream)
+        else:
+            self.qkv.forward(ctx, x, qkv)
+            k = qkv[:, self.q_width:self.q_width + self.kv_width]
+            v = qkv[:, self.q_width + self.kv_width:]
+            if self.position is not None:
+                self.position.rotate(ctx, q, k)
+            if cache.write:
+                ops.kv_write(k, v, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, ctx.status,
+                             ctx.stream)
         o = ctx.ws.get("attn_out", T, self.q_width, x.dtype)
         self.attend(ctx, q, cache, o)
         return self.out.forward(ctx, o, residual, residual=residual)
@@ -70,9 +77,10 @@ class Attention(Mixer):
         if ctx.n_single:
             scratch = ctx.ws.flat("attn_partial", ops.attention_decode_scratch(
                 ctx.n_single, self.n_heads, self.head_dim, ctx.max_len), torch.float32)
+            counters = ctx.ws.flat("attn_tickets", ctx.n_single * self.n_heads, torch.int32)
             ops.attention_decode(q, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o,
-                                 self.n_heads, self.scale, window, scratch, ctx.max_len, ctx.status, ctx.stream,
-                                 rows=ctx.single_rows)
+                                 self.n_heads, self.scale, window, scratch, counters, ctx.max_len, ctx.status,
+                                 ctx.stream, rows=ctx.single_rows)
         if ctx.n_portion:
             ops.attention_generic(q, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o,
                                   self.n_heads, self.scale, window, ctx.status, ctx.stream, rows=ctx.portion_rows)

@@ -145,6 +145,34 @@ def test_linear_few_rows(ops, M, N, K):
                             torch.empty(65, N, dtype=torch.bfloat16, device="cuda"), stream())
 
 
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,K", [(4, 4, 16, 16, 64), (3, 3, 32, 16, 96), (6, 2, 48, 32, 288), (16, 16, 64, 16, 1024)])
+def test_linear_qkv_to_cache(ops, Hq, Hkv, Dh, page, K):
+    """The fused projection writes queries to its output and keys/values into the right page rows, as the
+    plain projection followed by kv_write does; padding rows (request -1) write nothing."""
+    lens, new = [0, 37, 130, 64, 15], [1, 1, 1, 1, 1]
+    c = paged_case(torch.bfloat16, lens=lens, new=new, Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=K)
+    g = torch.Generator().manual_seed(K)
+    M, N = 6, (Hq + 2 * Hkv) * Dh                                  # 5 live rows and one padding row
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    positions = torch.cat([c["positions"], torch.tensor([0], dtype=torch.int32)])
+    token_req = torch.cat([c["token_req"], torch.tensor([-1], dtype=torch.int32)])
+    ref = R.linear(x, w, b).to(torch.bfloat16)
+    qw, kw = Hq * Dh, Hkv * Dh
+    rk, rv = R.kv_write(ref[:, qw:qw + kw], ref[:, qw + kw:], positions, token_req, c["bt"], c["k_pool"], c["v_pool"])
+    kp, vp = c["k_pool"].cuda(), c["v_pool"].cuda()
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.linear_qkv_to_cache(x.cuda(), w.cuda(), b.cuda(), out, positions.cuda(), token_req.cuda(), c["bt"].cuda(), kp, vp,
+                            qw, status, stream())
+    assert int(status.item()) == 0
+    assert rel_err(out[:, :qw], ref[:, :qw].float()) <= 8e-3
+    assert rel_err(kp, rk.float()) <= 8e-3 and rel_err(vp, rv.float()) <= 8e-3
+    changed = (kp.cpu() != c["k_pool"]).any(dim=-1)               # [page, head, row]: only the five written rows
+    assert int(changed.sum()) <= 5 * Hkv
+
+
 def test_linear_few_rows_refuses_odd_inner_size(ops):
     x = torch.zeros(2, 12, dtype=torch.bfloat16, device="cuda")
     w = torch.zeros(5, 12, dtype=torch.bfloat16, device="cuda")
@@ -232,9 +260,10 @@ def test_attention_single_token_rows(ops, dtype, Hq, Hkv, Dh, page, window, chun
     max_len = 640
     scratch = torch.full((ops.attention_decode_scratch(len(single), Hq, Dh, max_len, chunk),), float("nan"),
                          device="cuda")
+    counters = torch.zeros(8 * Hq, dtype=torch.int32, device="cuda")
     out = torch.zeros(c["T"], qw, dtype=dtype, device="cuda")
     ops.attention_decode(q, dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"], dev["v_pool"], out, Hq,
-                         scale, window, scratch, max_len, status, stream(), rows=rows, chunk=chunk)
+                         scale, window, scratch, counters, max_len, status, stream(), rows=rows, chunk=chunk)
     assert int(status.item()) == 0
     assert rel_err(out[single], ref[single]) <= tol(dtype, 3e-6, 8e-3)
     untouched = [t for t in range(c["T"]) if t not in single]
@@ -244,10 +273,11 @@ def test_attention_single_token_rows(ops, dtype, Hq, Hkv, Dh, page, window, chun
     d2 = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c2.items()}
     out2 = torch.zeros(4, qw, dtype=dtype, device="cuda")
     ops.attention_decode(d2["qkv"][:, :qw], d2["positions"], d2["token_req"], d2["bt"], d2["k_pool"], d2["v_pool"],
-                         out2, Hq, scale, window, scratch, max_len, status, stream(), chunk=chunk)
+                         out2, Hq, scale, window, scratch, counters, max_len, status, stream(), chunk=chunk)
     ref2 = R.attention(c2["qkv"][:, :qw], c2["positions"], c2["token_req"], c2["bt"], c2["k_pool"], c2["v_pool"], Hq,
                        scale, window)
     assert int(status.item()) == 0 and rel_err(out2, ref2) <= tol(dtype, 3e-6, 8e-3)
+    assert int(counters.abs().max().item()) == 0        # the ticket counters are left at zero
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -273,8 +303,9 @@ def test_attention_finds_one_far_key(ops, dtype):
         assert float((out[0, :Dh].float().cpu() - want).abs().max()) <= (1e-4 if dtype == torch.float32 else 2e-2), target
         out.zero_()
         scratch = torch.empty(ops.attention_decode_scratch(1, Hq, Dh, 512), device="cuda")
+        counters = torch.zeros(Hq, dtype=torch.int32, device="cuda")
         ops.attention_decode(dev["qkv"][:, :qw], dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"],
-                             dev["v_pool"], out, Hq, Dh ** -0.5, 0, scratch, 512, status, stream())
+                             dev["v_pool"], out, Hq, Dh ** -0.5, 0, scratch, counters, 512, status, stream())
         assert float((out[0, :Dh].float().cpu() - want).abs().max()) <= (1e-4 if dtype == torch.float32 else 2e-2), target
 
 
@@ -299,7 +330,8 @@ def test_attention_window_edge(ops, dtype):
         assert close == expect_hit
         out.zero_()
         scratch = torch.empty(ops.attention_decode_scratch(1, Hq, Dh, 256), device="cuda")
+        counters = torch.zeros(Hq, dtype=torch.int32, device="cuda")
         ops.attention_decode(dev["qkv"][:, :Dh], dev["positions"], dev["token_req"], dev["bt"], dev["k_pool"],
-                             dev["v_pool"], out, Hq, Dh ** -0.5, W, scratch, 256, status, stream())
+                             dev["v_pool"], out, Hq, Dh ** -0.5, W, scratch, counters, 256, status, stream())
         close = float((out[0].float().cpu() - want).abs().max()) <= 3e-2
         assert close == expect_hit

@@ -58,8 +58,9 @@ def test_no_alloc_entry_point_matches_the_ordinary_one(dtype):
         n = len(lens)
         want = torch.zeros(n, Hq * Dh, dtype=dtype, device="cuda")
         scratch = torch.empty(ops.attention_decode_scratch(n, Hq, Dh, max_len, chunk), device="cuda")
+        counters = torch.zeros(n * Hq, dtype=torch.int32, device="cuda")
         ops.attention_decode(c["q"], c["positions"], c["token_req"], c["bt"], c["k"], c["v"], want, Hq, Dh ** -0.5, 0,
-                             scratch, max_len, status, stream, chunk=chunk)
+                             scratch, counters, max_len, status, stream, chunk=chunk)
         got = torch.zeros_like(want)
         rc = fn(ops.dtype_code(dtype), c["q"].data_ptr(), Hq * Dh, None, c["positions"].data_ptr(),
                 c["token_req"].data_ptr(), c["bt"].data_ptr(), c["width"], c["n_pages"], page, Hq, Hkv, Dh, 0,
