@@ -213,6 +213,35 @@ def linear_few_rows(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=
           _p(residual), _p(out), M, N, K, lda, ldc, epilogue, stream)
 
 
+_TC_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+            c_void_p, c_void_p]
+
+
+def linear_tensor_cores(x, w, bias, out, status, stream, epilogue: int = EPI_NONE, residual=None) -> None:
+    """``linear_generic``'s contract for bfloat16 and many rows, on tcgen05 tensor cores with TMA-fed
+    shared-memory stages and the accumulator in tensor memory (csrc/gemm_tcgen05.cu).  ``K`` and the row
+    stride of ``x`` must be multiples of 8.  ``status`` receives ``ST_WAIT_TIMEOUT`` if a bounded wait gives up."""
+    _need(x, torch.bfloat16, "linear x")
+    _need(w, torch.bfloat16, "linear w")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not w.is_contiguous() or out.shape[0] != M or out.shape[1] != N:
+        raise KernelError(f"linear: x {tuple(x.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)}")
+    lda, ldc = _rows(x, "linear x"), _rows(out, "linear out")
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise KernelError(f"linear: output dtype {out.dtype}")
+    if bias is not None:
+        _need(bias, torch.float32, "linear bias")
+        if bias.numel() != N:
+            raise KernelError(f"linear: bias of {bias.numel()} for {N} outputs")
+    if residual is not None:
+        _need(residual, torch.bfloat16, "linear residual")
+        if residual.shape != out.shape or _rows(residual, "linear residual") != ldc:
+            raise KernelError("linear: residual must have the output's shape and row stride")
+    _call("gemm_tcgen05", "mlxb_linear_tcgen05", _TC_ARGS, int(out.dtype == torch.float32), _p(x), _p(w), _p(bias),
+          _p(residual), _p(out), M, N, K, lda, ldc, epilogue, _p(status), stream)
+
+
 _QKV_ARGS = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
 

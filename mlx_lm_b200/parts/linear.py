@@ -20,7 +20,7 @@ ACTIVATIONS = {None: ops.EPI_NONE, "none": ops.EPI_NONE, "gelu_new": ops.EPI_GEL
 
 
 class Linear(Part):
-    kernel_libs = ("gemm_simt", "gemm_smallm")
+    kernel_libs = ("gemm_simt", "gemm_smallm", "gemm_tcgen05")
 
     def __init__(self, name: str, n_in: int, n_out: int, bias: bool = True, stored: str = "out_in",
                  weight_suffix: str = ".weight", init: Init = Init(), bias_init: Init = Init()):
@@ -52,11 +52,16 @@ class Linear(Part):
 
     def forward(self, ctx, x, out, activation=None, residual=None) -> torch.Tensor:
         """float32: the generic kernel (true 32-bit arithmetic).  bfloat16: the weight-streaming kernel for up
-        to 64 rows; more rows, or an inner size that is no multiple of 8, go to the generic kernel."""
+        to 64 rows, the tcgen05 kernel for more; an inner size that is no multiple of 8 (no 16-byte rows)
+        goes to the generic kernel."""
         epi = ACTIVATIONS[activation]
-        if (x.dtype == torch.bfloat16 and x.shape[0] <= ops.SMALL_M and self.n_in % 8 == 0
-                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
+        fast = (x.dtype == torch.bfloat16 and self.n_in % 8 == 0 and x.stride(0) % 8 == 0
+                and x.data_ptr() % 16 == 0)
+        if fast and x.shape[0] <= ops.SMALL_M:
             ops.linear_few_rows(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual)
+        elif fast:
+            ops.linear_tensor_cores(x, self.weight, self.bias, out, ctx.status, ctx.stream, epilogue=epi,
+                                    residual=residual)
         else:
             ops.linear_generic(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual)
         return out

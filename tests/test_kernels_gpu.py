@@ -145,6 +145,57 @@ def test_linear_few_rows(ops, M, N, K):
                             torch.empty(65, N, dtype=torch.bfloat16, device="cuda"), stream())
 
 
+@pytest.mark.parametrize("M,N,K", [(128, 128, 64), (65, 192, 64), (200, 320, 96), (130, 1000, 96), (257, 96, 320),
+                                   (2048, 3072, 1024), (300, 1600, 6400), (1000, 50257, 64), (129, 7, 8),
+                                   (512, 1024, 4096)])
+def test_linear_tensor_cores(ops, M, N, K):
+    """The tcgen05 kernel against the plain statement: tiles with ragged edges in M, N and K, many K stages,
+    both output dtypes, every epilogue, in place on the residual."""
+    g = torch.Generator().manual_seed(M + N + K)
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    b = torch.randn(N, generator=g).cuda()
+    res = torch.randn(M, N, generator=g).to(torch.bfloat16).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ref = R.linear(x.cpu(), w.cpu(), b.cpu()) if M * N * K < 2e9 else (x.float() @ w.float().t() + b).cpu()
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    ops.linear_tensor_cores(x, w, b, out, status, stream())
+    assert int(status.item()) == 0
+    assert rel_err(out, ref) <= 6e-3
+    out32 = torch.empty(M, N, dtype=torch.float32, device="cuda")
+    ops.linear_tensor_cores(x, w, b, out32, status, stream())
+    assert rel_err(out32, ref) <= 2e-5          # float32 accumulation of exact bfloat16 products
+    ops.linear_tensor_cores(x, w, b, out, status, stream(), epilogue=ops.EPI_GELU_NEW, residual=res)
+    assert rel_err(out, R.gelu_new(ref) + res.float().cpu()) <= 6e-3
+    r2 = res.clone()
+    ops.linear_tensor_cores(x, w, None, r2, status, stream(), residual=r2)
+    assert rel_err(r2, ref - b.cpu() + res.float().cpu()) <= 6e-3
+    # a row's result does not depend on the other rows of the call
+    n_sub = min(70, M - 1)
+    sub = torch.empty(n_sub, N, dtype=torch.float32, device="cuda")
+    ops.linear_tensor_cores(x[M - n_sub:], w, b, sub, status, stream())
+    assert torch.equal(sub, out32[M - n_sub:])
+    assert int(status.item()) == 0
+
+
+def test_linear_tensor_cores_finds_one_hot_entries(ops):
+    """One-hot rows and columns: the output must be exactly the picked weight entry, which pins down the
+    operand layouts (swizzle, K steps inside a stage, tile edges) far better than random data."""
+    M, N, K = 256, 256, 256
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    w = torch.arange(N * K, dtype=torch.float32).reshape(N, K).remainder(251).to(torch.bfloat16).cuda()
+    for k_hot in (0, 7, 8, 15, 16, 63, 64, 65, 127, 128, 255):
+        x = torch.zeros(M, K, dtype=torch.bfloat16, device="cuda")
+        x[:, k_hot] = 1.0
+        x[5, k_hot] = 2.0
+        out = torch.empty(M, N, dtype=torch.float32, device="cuda")
+        ops.linear_tensor_cores(x, w, None, out, status, stream())
+        want = w[:, k_hot].float().unsqueeze(0).repeat(M, 1)
+        want[5] *= 2
+        assert torch.equal(out, want), k_hot
+    assert int(status.item()) == 0
+
+
 @pytest.mark.parametrize("Hq,Hkv,Dh,page,K", [(4, 4, 16, 16, 64), (3, 3, 32, 16, 96), (6, 2, 48, 32, 288), (16, 16, 64, 16, 1024)])
 def test_linear_qkv_to_cache(ops, Hq, Hkv, Dh, page, K):
     """The fused projection writes queries to its output and keys/values into the right page rows, as the
