@@ -1,0 +1,278 @@
+// Causal attention of prompt portions over the paged key/value cache, on tensor cores.
+//
+// A portion (the next n > 1 tokens of one request) is cut into tiles of 64 queries; one CTA of four
+// warps handles (tile, query head), 16 queries a warp.  It walks the request's keys in blocks of 64
+// positions, from the first block the tile may see (0, or the window's lower edge) to the block of
+// the tile's last query; the keys of this very step are already in the pages.  K and V blocks are
+// gathered through the block table with 16-byte cp.async into double-buffered shared memory (rows
+// padded by 16 bytes, which makes every ldmatrix conflict-free for any head size that is a multiple
+// of 16), so the next block loads while the current one is multiplied.
+//   S = Q K^T        mma.sync m16n8k16, bf16 inputs, float32 accumulators; Q stays in registers
+//   softmax          float32, online (running maximum and sum per query row), exp2 of scores
+//                    pre-multiplied by scale*log2(e); masked: key > query position, key below the
+//                    window, rows beyond the tile
+//   O += P V         P rounded to bf16 as the A operand (the accumulator layout of S is the A layout
+//                    of the next product), V through ldmatrix.trans
+// The order in which a query's keys are added depends only on its position: blocks of 64 positions
+// from block 0 (or the window's first block) upward.
+//
+// (tcgen05 has no place here yet: with 64-wide heads the softmax, not the products, is the long pole
+// of this kernel; the linear layers, which carry 92 % of a prompt's flops, use tcgen05.)
+#include "common.cuh"
+
+MLXB_DEFINE_LAST_ERROR()
+
+constexpr int BKV = 64, WARPS = 4;   // 16 queries a warp: 64 queries a CTA
+
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+  const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
+  const int n = valid ? 16 : 0;   // 0 source bytes: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned (&r)[4], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned (&r)[4], const void* p) {
+  const unsigned a = (unsigned)__cvta_generic_to_shared(p);
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
+  const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const unsigned*>(&v);
+}
+
+// tiles: int32 [n_tiles][4] = (row of the tile's first token among the step's tokens, queries in the tile
+// (1..64), block-table row of the request, position of the tile's first query).
+template <int DH>
+__global__ void __launch_bounds__(WARPS * 32)
+attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int4* __restrict__ tiles,
+                         const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
+                         int window, float scale_log2e, const __nv_bfloat16* __restrict__ k_pool,
+                         const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, int ldo,
+                         int* __restrict__ status) {
+  constexpr int STRIDE = DH + 8;              // elements per shared-memory row (16 bytes of padding)
+  constexpr int KS = DH / 16;                 // k steps of Q K^T
+  constexpr int NT = DH / 8;                  // n tiles of the output
+  constexpr int CHUNKS = DH / 8;              // 16-byte chunks per key row
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* sk = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [2][BKV][STRIDE]
+  __nv_bfloat16* sv = sk + 2 * BKV * STRIDE;                             // [2][BKV][STRIDE]
+
+  pdl_trigger();
+  pdl_wait();
+  const int4 tile = tiles[blockIdx.x];
+  const int row0 = tile.x, n_rows = tile.y, req = tile.z, pos0 = tile.w;
+  const int h = blockIdx.y, hk = h / (Hq / Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, qd = lane & 3;
+  const int* bt = block_table + (size_t)req * max_pages;
+  const int shift = __ffs(page) - 1;
+
+  const int last_pos = pos0 + n_rows - 1;
+  const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
+  const int kb_lo = first_key / BKV, kb_hi = last_pos / BKV;
+
+  // gather one block of keys and values into stage `st`
+  auto load_block = [&](int kb, int st) {
+    __nv_bfloat16* dk = sk + st * BKV * STRIDE;
+    __nv_bfloat16* dv = sv + st * BKV * STRIDE;
+    for (int i = threadIdx.x; i < BKV * CHUNKS; i += WARPS * 32) {
+      const int kr = i / CHUNKS, ch = i - kr * CHUNKS;
+      const int key = kb * BKV + kr;
+      bool ok = key <= last_pos && key >= first_key;
+      size_t off = 0;
+      if (ok) {
+        const int lp = key >> shift;
+        const int pg = lp < max_pages ? bt[lp] : -1;
+        if (pg < 0 || pg >= n_pages) {
+          atomicOr(status, pg < 0 ? MLXB_ST_POSITION_RANGE : MLXB_ST_PAGE_RANGE);
+          ok = false;
+        } else {
+          off = (((size_t)pg * Hkv + hk) * page + (key & (page - 1))) * DH + ch * 8;
+        }
+      }
+      cp_async16(dk + kr * STRIDE + ch * 8, k_pool + off, ok);
+      cp_async16(dv + kr * STRIDE + ch * 8, v_pool + off, ok);
+    }
+    cp_async_commit();
+  };
+
+  load_block(kb_lo, 0);
+
+  // this warp's 16 queries: rows r_lo = 16*warp + g and r_hi = r_lo + 8 of the tile
+  const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
+  const bool v_lo = r_lo < n_rows, v_hi = r_hi < n_rows;
+  const int p_lo = v_lo ? pos0 + r_lo : -1, p_hi = v_hi ? pos0 + r_hi : -1;   // -1: nothing is visible
+  const int lo_lo = (window > 0 && p_lo - window + 1 > 0) ? p_lo - window + 1 : 0;
+  const int lo_hi = (window > 0 && p_hi - window + 1 > 0) ? p_hi - window + 1 : 0;
+  unsigned qa[KS][4];
+  {
+    const __nv_bfloat16* q_lo = q + (size_t)(row0 + (v_lo ? r_lo : 0)) * ldq + h * DH;
+    const __nv_bfloat16* q_hi = q + (size_t)(row0 + (v_hi ? r_hi : 0)) * ldq + h * DH;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int d = ks * 16 + 2 * qd;
+      qa[ks][0] = v_lo ? *reinterpret_cast<const unsigned*>(q_lo + d) : 0u;
+      qa[ks][1] = v_hi ? *reinterpret_cast<const unsigned*>(q_hi + d) : 0u;
+      qa[ks][2] = v_lo ? *reinterpret_cast<const unsigned*>(q_lo + d + 8) : 0u;
+      qa[ks][3] = v_hi ? *reinterpret_cast<const unsigned*>(q_hi + d + 8) : 0u;
+    }
+  }
+  const int warp_last_pos = min(last_pos, pos0 + warp * 16 + 15);
+
+  float o[NT][4];
+#pragma unroll
+  for (int i = 0; i < NT; ++i)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
+  float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
+
+  const int mi = lane >> 3, mr = lane & 7;   // ldmatrix: which 8x8 matrix this lane addresses, and its row
+
+  for (int kb = kb_lo; kb <= kb_hi; ++kb) {
+    const int st = (kb - kb_lo) & 1;
+    if (kb < kb_hi) load_block(kb + 1, st ^ 1);
+    if (kb < kb_hi) cp_async_wait<1>(); else cp_async_wait<0>();
+    __syncthreads();
+
+    if (kb * BKV <= warp_last_pos) {     // otherwise every key of the block lies after this warp's queries
+      const __nv_bfloat16* bk = sk + st * BKV * STRIDE;
+      const __nv_bfloat16* bv = sv + st * BKV * STRIDE;
+      float s[BKV / 8][4];
+#pragma unroll
+      for (int i = 0; i < BKV / 8; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[i][c] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int np = 0; np < BKV / 16; ++np) {   // pairs of key tiles
+          unsigned b[4];
+          ldmatrix_x4(b, bk + (np * 16 + (mi >> 1) * 8 + mr) * STRIDE + ks * 16 + (mi & 1) * 8);
+          mma_bf16(s[2 * np], qa[ks], b[0], b[1]);
+          mma_bf16(s[2 * np + 1], qa[ks], b[2], b[3]);
+        }
+      }
+      // mask, scale (to base-2 exponents) and running maximum
+      const int key0 = kb * BKV + 2 * qd;
+      float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+      for (int i = 0; i < BKV / 8; ++i) {
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int key = key0 + i * 8 + c;
+          const float a = (key <= p_lo && key >= lo_lo) ? s[i][c] * scale_log2e : -INFINITY;
+          const float b2 = (key <= p_hi && key >= lo_hi) ? s[i][2 + c] * scale_log2e : -INFINITY;
+          s[i][c] = a;
+          s[i][2 + c] = b2;
+          mx_lo = fmaxf(mx_lo, a);
+          mx_hi = fmaxf(mx_hi, b2);
+        }
+      }
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
+      mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
+      mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo, base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+      const float corr_lo = exp2f(m_lo - base_lo), corr_hi = exp2f(m_hi - base_hi);   // exp2(-inf) = 0
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+      float sum_lo = 0.f, sum_hi = 0.f;
+      unsigned pa[BKV / 16][4];
+#pragma unroll
+      for (int i = 0; i < BKV / 8; ++i) {
+        const float e0 = exp2f(s[i][0] - base_lo), e1 = exp2f(s[i][1] - base_lo);
+        const float e2 = exp2f(s[i][2] - base_hi), e3 = exp2f(s[i][3] - base_hi);
+        sum_lo += e0 + e1;
+        sum_hi += e2 + e3;
+        // accumulator tiles 2j and 2j+1 are the A fragment of the j-th 16-key step of P V
+        pa[i >> 1][(i & 1) * 2] = pack_bf16(e0, e1);
+        pa[i >> 1][(i & 1) * 2 + 1] = pack_bf16(e2, e3);
+      }
+      l_lo = l_lo * corr_lo + sum_lo;   // per-lane partial sums; the four lanes of a row are added at the end
+      l_hi = l_hi * corr_hi + sum_hi;
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        o[i][0] *= corr_lo; o[i][1] *= corr_lo;
+        o[i][2] *= corr_hi; o[i][3] *= corr_hi;
+      }
+#pragma unroll
+      for (int kk = 0; kk < BKV / 16; ++kk) {
+#pragma unroll
+        for (int dp = 0; dp < NT / 2; ++dp) {   // pairs of output-dim tiles
+          unsigned b[4];
+          ldmatrix_x4_trans(b, bv + (kk * 16 + (mi & 1) * 8 + mr) * STRIDE + dp * 16 + (mi >> 1) * 8);
+          mma_bf16(o[2 * dp], pa[kk], b[0], b[1]);
+          mma_bf16(o[2 * dp + 1], pa[kk], b[2], b[3]);
+        }
+      }
+    }
+    __syncthreads();   // everyone is done with stage st before it is loaded again
+  }
+
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
+  l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
+  l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
+  __nv_bfloat16* o_lo = out + (size_t)(row0 + r_lo) * ldo + h * DH + 2 * qd;
+  __nv_bfloat16* o_hi = out + (size_t)(row0 + r_hi) * ldo + h * DH + 2 * qd;
+#pragma unroll
+  for (int i = 0; i < NT; ++i) {
+    if (v_lo) *reinterpret_cast<unsigned*>(o_lo + i * 8) = pack_bf16(o[i][0] * inv_lo, o[i][1] * inv_lo);
+    if (v_hi) *reinterpret_cast<unsigned*>(o_hi + i * 8) = pack_bf16(o[i][2] * inv_hi, o[i][3] * inv_hi);
+  }
+}
+
+template <int DH>
+static int launch(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table, int max_pages,
+                  int n_pages, int page, int Hq, int Hkv, int window, float scale, const void* k_pool,
+                  const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream) {
+  const size_t smem = (size_t)2 * 2 * BKV * (DH + 8) * sizeof(__nv_bfloat16);
+  auto kern = attention_prefill_kernel<DH>;
+  static bool raised = false;
+  if (smem > 48 * 1024 && !raised) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    raised = true;
+  }
+  launch_pdl(kern, dim3(n_tiles, Hq), dim3(WARPS * 32), smem, stream, (const __nv_bfloat16*)q, ldq,
+             (const int4*)tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window,
+             scale * 1.4426950408889634f, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
+             (__nv_bfloat16*)out, ldo, status);
+  return mlxb_check_launch("attention (portions)");
+}
+
+// bfloat16 only.  q: [*, >= Hq*Dh] at row stride ldq; out: [*, Hq*Dh] at row stride ldo (both strides even,
+// bases 4-byte aligned); tiles: int32 [n_tiles][4], see the kernel; pools [n_pages, Hkv, page, Dh].
+// Dh: a multiple of 16 up to 128; other sizes are refused (the generic kernel takes them).
+MLXB_EXPORT int mlxb_attention_prefill(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table,
+                                       int max_pages, int n_pages, int page, int Hq, int Hkv, int Dh, int window,
+                                       float scale, const void* k_pool, const void* v_pool, void* out, int ldo,
+                                       int* status, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (page <= 0 || (page & (page - 1))) return mlxb_fail(MLXB_BAD_ARG, "attention (portions): page size %d", page);
+  if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || Hq > 65535)
+    return mlxb_fail(MLXB_BAD_ARG, "attention (portions): %d query heads over %d key/value heads", Hq, Hkv);
+  if ((ldq & 1) || (ldo & 1) || ((uintptr_t)q & 3) || ((uintptr_t)out & 3) || ((uintptr_t)tiles & 15))
+    return mlxb_fail(MLXB_BAD_ARG, "attention (portions): rows must be 4-byte aligned, the tile list 16-byte aligned");
+#define GO(D) case D: return launch<D>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, \
+                                       scale, k_pool, v_pool, out, ldo, status, stream)
+  switch (Dh) {
+    GO(16); GO(32); GO(48); GO(64); GO(80); GO(96); GO(112); GO(128);
+    default:
+      return mlxb_fail(MLXB_BAD_ARG, "attention (portions): head size %d is not a multiple of 16 up to 128", Dh);
+  }
+#undef GO
+}

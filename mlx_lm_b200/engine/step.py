@@ -113,6 +113,10 @@ class StepContext:
         # int32 device lists of token rows, None meaning "all tokens of the step"
         self.n_single = self.n_portion = 0
         self.single_rows = self.portion_rows = None
+        # portions cut into tiles of ops.PREFILL_TILE queries: int32 [n, 4] = (first token row, queries,
+        # block-table row, first position), longest context first
+        self.portion_tiles = None
+        self.n_portion_tiles = 0
         self._tables: List[torch.Tensor] = []
         self._slots: Optional[torch.Tensor] = None
 
@@ -230,9 +234,12 @@ class Engine:
         pad = lambda n: (n + 3) & ~3
         n_single = sum(1 for e in entries if len(e.tokens) == 1)
         mixed = 0 < n_single < R
+        TQ = ops.PREFILL_TILE
+        n_tiles = sum((len(e.tokens) + TQ - 1) // TQ for e in entries if len(e.tokens) > 1)
         off, sizes = {}, [("tokens", T), ("positions", T), ("token_req", T), ("logit_rows", L), ("slots", R),
                           ("req_first_token", R + 1), ("req_first_position", R),
-                          ("single_rows", n_single if mixed else 0), ("portion_rows", T - n_single if mixed else 0)]
+                          ("single_rows", n_single if mixed else 0), ("portion_rows", T - n_single if mixed else 0),
+                          ("tiles", 4 * n_tiles)]
         sizes += [(f"table{g}", R * W) for g in range(len(mgr.kv_groups))]
         total = 0
         for name, n in sizes:
@@ -244,6 +251,7 @@ class Engine:
         rows: List[int] = []
         single_rows: List[int] = []
         portion_rows: List[int] = []
+        tiles: List[tuple] = []
         for r, e in enumerate(entries):
             n = len(e.tokens)
             start = mgr.reserve(e.rid, n)
@@ -257,6 +265,8 @@ class Engine:
             rows.extend(t0 + w for w in e.want)
             if mixed:
                 (single_rows if n == 1 else portion_rows).extend(range(t0, t0 + n))
+            if n > 1:
+                tiles.extend((t0 + a, min(TQ, n - a), r, start + a) for a in range(0, n, TQ))
             ctx.spans.append(RequestSpan(e.rid, slot, t0, n, start))
             ctx.max_q_len = max(ctx.max_q_len, n)
             t0 += n
@@ -266,6 +276,9 @@ class Engine:
         if mixed:
             h[off["single_rows"]: off["single_rows"] + n_single] = single_rows
             h[off["portion_rows"]: off["portion_rows"] + T - n_single] = portion_rows
+        if n_tiles:
+            tiles.sort(key=lambda t: -(t[3] + t[1]))     # tiles with the most keys start first
+            h[off["tiles"]: off["tiles"] + 4 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
         rids = [e.rid for e in entries]
         for g in range(len(mgr.kv_groups)):
             o = off[f"table{g}"]
@@ -282,6 +295,8 @@ class Engine:
         ctx.n_single, ctx.n_portion = n_single, T - n_single
         if mixed:
             ctx.single_rows, ctx.portion_rows = view("single_rows", n_single), view("portion_rows", T - n_single)
+        if n_tiles:
+            ctx.portion_tiles, ctx.n_portion_tiles = view("tiles", 4 * n_tiles), n_tiles
         ctx._tables = [view(f"table{g}", R * W).view(R, W) for g in range(len(mgr.kv_groups))]
         try:
             logits = self.model.run(ctx)

@@ -320,6 +320,31 @@ def attention_generic(q, positions, token_req, block_table, k_pool, v_pool, out,
           stream)
 
 
+_PRE_ARGS = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+
+PREFILL_TILE = 64   # queries per CTA of the tensor-core attention kernel for portions
+
+
+def attention_portions_supported(dtype, head_dim: int) -> bool:
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+
+
+def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out, n_heads: int, scale: float,
+                       window: int, status, stream) -> None:
+    """Causal attention of prompt portions on tensor cores (bfloat16, csrc/attention_prefill.cu).
+
+    ``tiles``: int32 device tensor ``[n_tiles, 4]``: first token row of the tile, queries in it (1..64),
+    block-table row of its request, position of its first query."""
+    n_pages, Hkv, page, Dh = _attn_shapes(q, out, k_pool, n_heads, "attention_portions")
+    _need(tiles, torch.int32, "attention_portions tiles")
+    if tiles.numel() < 4 * n_tiles:
+        raise KernelError(f"attention_portions: {tiles.numel()} integers for {n_tiles} tiles")
+    _call("attention_prefill", "mlxb_attention_prefill", _PRE_ARGS, _p(q), _rows(q, "attention q"), _p(tiles), n_tiles,
+          _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
+          _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream)
+
+
 _DEC_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
              c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
              c_void_p]

@@ -22,7 +22,7 @@ from .linear import Linear
 
 
 class Attention(Mixer):
-    kernel_libs = ("attention",)
+    kernel_libs = ("attention", "attention_prefill")
 
     def __init__(self, name: str, width: int, n_heads: int, head_dim: int, n_kv_heads: Optional[int] = None,
                  window: Optional[int] = None, bias: bool = True, stored: str = "out_in",
@@ -82,8 +82,13 @@ class Attention(Mixer):
                                  self.n_heads, self.scale, window, scratch, counters, ctx.max_len, ctx.status,
                                  ctx.stream, rows=ctx.single_rows)
         if ctx.n_portion:
-            ops.attention_generic(q, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o,
-                                  self.n_heads, self.scale, window, ctx.status, ctx.stream, rows=ctx.portion_rows)
+            if ops.attention_portions_supported(q.dtype, self.head_dim) and ctx.portion_tiles is not None:
+                ops.attention_portions(q, ctx.portion_tiles, ctx.n_portion_tiles, cache.block_table, cache.k,
+                                       cache.v, o, self.n_heads, self.scale, window, ctx.status, ctx.stream)
+            else:
+                ops.attention_generic(q, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o,
+                                      self.n_heads, self.scale, window, ctx.status, ctx.stream,
+                                      rows=ctx.portion_rows)
 
 
 register_part("mixer", "attention", Attention)

@@ -32,7 +32,7 @@ def part_ctx(T=0, positions=None, token_req=None):
                            status=torch.zeros(1, dtype=torch.int32, device="cuda"),
                            positions=positions, token_req=token_req, tokens=None, max_len=64,
                            n_single=T if T == 1 else 0, n_portion=0 if T == 1 else T, single_rows=None,
-                           portion_rows=None)
+                           portion_rows=None, portion_tiles=None, n_portion_tiles=0)
 
 
 def bind(part, dtype, seed=0):

@@ -331,6 +331,68 @@ def test_attention_single_token_rows(ops, dtype, Hq, Hkv, Dh, page, window, chun
     assert int(counters.abs().max().item()) == 0        # the ticket counters are left at zero
 
 
+def make_tiles(lens, new, tile=64):
+    tiles, t0 = [], 0
+    for r, (l, n) in enumerate(zip(lens, new)):
+        if n > 1:
+            tiles.extend((t0 + a, min(tile, n - a), r, l + a) for a in range(0, n, tile))
+        t0 += n
+    return torch.tensor(tiles, dtype=torch.int32).reshape(-1)
+
+
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,window", [(4, 4, 16, 16, 0), (3, 3, 32, 16, 0), (6, 2, 48, 32, 0),
+                                                    (5, 1, 80, 64, 0), (2, 2, 128, 16, 40), (8, 4, 64, 16, 17),
+                                                    (16, 16, 64, 16, 0), (2, 1, 96, 16, 100), (1, 1, 112, 32, 0)])
+def test_attention_portions(ops, Hq, Hkv, Dh, page, window):
+    """The tensor-core kernel on the portions of a mixed step (single-token requests are left to the other
+    kernel): portions that start at position 0, that continue long contexts, that end inside a tile, of two tokens."""
+    lens, new = [0, 37, 130, 64, 3, 200, 0], [21, 1, 135, 2, 64, 65, 300]
+    c = paged_case(torch.bfloat16, lens=lens, new=new, Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=Dh + page + 2)
+    dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    qw = Hq * Dh
+    scale = Dh ** -0.5
+    tiles = make_tiles(lens, new).cuda()
+    out = torch.zeros(c["T"], qw, dtype=torch.bfloat16, device="cuda")
+    ops.attention_portions(dev["qkv"][:, :qw], tiles, tiles.numel() // 4, dev["bt"], dev["k_pool"], dev["v_pool"], out,
+                           Hq, scale, window, status, stream())
+    ref = R.attention(c["qkv"][:, :qw], c["positions"], c["token_req"], c["bt"], c["k_pool"], c["v_pool"], Hq, scale,
+                      window)
+    assert int(status.item()) == 0
+    first = np.cumsum([0] + new)
+    portion = [t for i, n in enumerate(new) if n > 1 for t in range(first[i], first[i + 1])]
+    single = [int(first[i]) for i, n in enumerate(new) if n == 1]
+    assert rel_err(out[portion], ref[portion]) <= 8e-3
+    assert float(out[single].float().abs().max()) == 0.0
+
+
+def test_attention_portions_sees_each_key_once(ops):
+    """Values that encode their own position and sharp queries: query i picks key (i * 7) % (i + 1) exactly, at
+    every offset inside tiles, blocks and pages; a key counted twice, skipped or taken from the wrong page shows."""
+    Hq = Hkv = 1
+    Dh, page, n = 64, 16, 333
+    c = paged_case(torch.bfloat16, lens=[0], new=[n], Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=0)
+    code = torch.randn(n, Dh, generator=torch.Generator().manual_seed(9)).sign()      # +-1 codes, one per position
+    for j in range(n):
+        pg = int(c["bt"][0, j // page])
+        c["k_pool"][pg, 0, j % page] = (code[j] * 2.0).to(torch.bfloat16)
+        c["v_pool"][pg, 0, j % page] = 0
+        c["v_pool"][pg, 0, j % page, j % Dh] = 1.0 + j // Dh          # says which key it is
+    target = [(i * 7) % (i + 1) for i in range(n)]
+    c["qkv"][:, :Dh] = (code[target] * 2.0).to(torch.bfloat16)        # score 4*64*scale=32 on the target, ~0 elsewhere
+    dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    tiles = make_tiles([0], [n]).cuda()
+    out = torch.zeros(n, Dh, dtype=torch.bfloat16, device="cuda")
+    ops.attention_portions(dev["qkv"][:, :Dh], tiles, tiles.numel() // 4, dev["bt"], dev["k_pool"], dev["v_pool"], out,
+                           Hq, Dh ** -0.5, 0, status, stream())
+    got = out.float().cpu()
+    for i in range(n):
+        j = target[i]
+        assert abs(float(got[i, j % Dh]) - (1.0 + j // Dh)) < 0.05, (i, j)
+        assert float(got[i].abs().sum()) < (1.0 + j // Dh) + 0.1, (i, j)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_attention_finds_one_far_key(ops, dtype):
     """One key among hundreds matches the query strongly: the output must be that key's value row,
