@@ -219,11 +219,39 @@ __device__ __forceinline__ void load8<float>(const float* p, float (&v)[8]) {
   v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
 }
 
-constexpr int DEC_THREADS = 128;
-constexpr int DEC_UNROLL = 4;
+
+// Raw 8-element rows as they come from memory; converted to float only when used, so that many
+// keys can be in flight per thread.
+template <typename T> struct Raw8;
+template <> struct Raw8<__nv_bfloat16> {
+  uint4 u;
+  __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = *reinterpret_cast<const uint4*>(p); }
+  __device__ __forceinline__ void zero() { u = make_uint4(0u, 0u, 0u, 0u); }
+  __device__ __forceinline__ void get(float (&v)[8]) const {
+    const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+    }
+  }
+};
+template <> struct Raw8<float> {
+  float4 a, b;
+  __device__ __forceinline__ void load(const float* p) {
+    a = *reinterpret_cast<const float4*>(p);
+    b = *reinterpret_cast<const float4*>(p + 4);
+  }
+  __device__ __forceinline__ void zero() { a = make_float4(0.f, 0.f, 0.f, 0.f); b = a; }
+  __device__ __forceinline__ void get(float (&v)[8]) const {
+    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+  }
+};
 
 // partial: float [n_rows][Hq][n_chunks_max][Dh + 2] = (m, l, o[Dh]) per chunk.
-template <typename T, int TPK>
+// DEC_THREADS: 512 when there are few (row, head) pairs (one CTA streams a whole row's keys with many loads in
+// flight), 256 when there are many (two CTAs per SM, so that one CTA's merge overlaps the other's loads).
+template <typename T, int TPK, int DEC_THREADS>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict__ rows,
                         const int* __restrict__ positions, const int* __restrict__ token_req,
@@ -232,109 +260,172 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
                         float* partial, int* counters, int n_chunks_max, int chunk, T* __restrict__ out, int ldo,
                         int* __restrict__ status) {
   constexpr int GROUPS = DEC_THREADS / TPK;
-  extern __shared__ float sm[];   // m[GROUPS] | l[GROUPS] | o[GROUPS][Dh]
+  constexpr int U = sizeof(T) == 2 ? 8 : 4;   // keys in flight per thread
+  extern __shared__ float sm[];               // per warp: m | l | o[Dh]
   __shared__ int s_last;
   pdl_trigger();
   pdl_wait();
   const int c = blockIdx.x, h = blockIdx.y, ri = blockIdx.z;
   const int t = rows ? rows[ri] : ri;
-  const int r = token_req[t];
-  if (r < 0) return;
-  const int p = positions[t];
-  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
-  const int k_begin = max(lo, c * chunk), k_end = min(p + 1, (c + 1) * chunk);
-  if (k_begin >= k_end) return;
-  const int hk = h / (Hq / Hkv);
   const int grp = threadIdx.x / TPK, j = threadIdx.x % TPK;
   const int d0 = 8 * j;
   const bool active = d0 < Dh;
-  const int* bt = block_table + (size_t)r * max_pages;
-  const int shift = __ffs(page) - 1;
-
+  // the query does not depend on the request's bookkeeping: its load goes out with theirs
   float qv[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) qv[i] = 0.f;
-  if (active) {
-    load8<T>(q + (size_t)t * ldq + h * Dh + d0, qv);
+  if (active) load8<T>(q + (size_t)t * ldq + h * Dh + d0, qv);
+  const int r = token_req[t];
+  const int p = positions[t];
+  if (r < 0) return;
+  const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+  const int k_begin = max(lo, c * chunk), k_end = min(p + 1, (c + 1) * chunk);
+  if (k_begin >= k_end) return;
+  const int c0 = lo / chunk, c1 = p / chunk;   // the chunks of this row that hold keys
+  const int hk = h / (Hq / Hkv);
+  const int* bt = block_table + (size_t)r * max_pages;
+  const int shift = __ffs(page) - 1;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) qv[i] *= scale;
-  }
+  for (int i = 0; i < 8; ++i) qv[i] *= scale;
+
   float m = -INFINITY, l = 0.f, o[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) o[i] = 0.f;
 
   const int n_keys = k_end - k_begin;
-  const int iters = (n_keys + GROUPS * DEC_UNROLL - 1) / (GROUPS * DEC_UNROLL);
+  const int iters = (n_keys + GROUPS * U - 1) / (GROUPS * U);
+  int pg_next[U];
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    const int key = k_begin + u * GROUPS + grp;
+    const int lp = key >> shift;
+    pg_next[u] = (key < k_end && lp < max_pages) ? bt[lp] : -1;
+  }
   for (int it = 0; it < iters; ++it) {
-    float kv[DEC_UNROLL][8], vv[DEC_UNROLL][8];
-    bool ok[DEC_UNROLL];
+    // page ids were fetched one batch ahead; now all key and value rows of the batch, then the arithmetic
+    int pg[U];
+    bool ok[U];
 #pragma unroll
-    for (int u = 0; u < DEC_UNROLL; ++u) {
-      const int key = k_begin + (it * DEC_UNROLL + u) * GROUPS + grp;
+    for (int u = 0; u < U; ++u) {
+      const int key = k_begin + (it * U + u) * GROUPS + grp;
       ok[u] = key < k_end;
+      pg[u] = pg_next[u];
+      const int nkey = key + U * GROUPS, nlp = nkey >> shift;
+      pg_next[u] = (nkey < k_end && nlp < max_pages) ? bt[nlp] : -1;
+    }
+    Raw8<T> kr[U], vr[U];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) { kv[u][i] = 0.f; vv[u][i] = 0.f; }
-      if (ok[u]) {
-        const int lp = key >> shift;
-        const int pg = lp < max_pages ? bt[lp] : -1;
-        if (pg < 0 || pg >= n_pages) {
-          if (j == 0) atomicOr(status, pg < 0 ? MLXB_ST_POSITION_RANGE : MLXB_ST_PAGE_RANGE);
-          ok[u] = false;
-        } else if (active) {
-          const size_t off = (((size_t)pg * Hkv + hk) * page + (key & (page - 1))) * Dh + d0;
-          load8<T>(k_pool + off, kv[u]);
-          load8<T>(v_pool + off, vv[u]);
-        }
+    for (int u = 0; u < U; ++u) {
+      const int key = k_begin + (it * U + u) * GROUPS + grp;
+      if (ok[u] && (pg[u] < 0 || pg[u] >= n_pages)) {
+        if (j == 0) atomicOr(status, pg[u] < 0 ? MLXB_ST_POSITION_RANGE : MLXB_ST_PAGE_RANGE);
+        ok[u] = false;
+      }
+      if (ok[u] && active) {
+        const size_t off = (((size_t)pg[u] * Hkv + hk) * page + (key & (page - 1))) * Dh + d0;
+        kr[u].load(k_pool + off);
+        vr[u].load(v_pool + off);
+      } else {
+        kr[u].zero();
+        vr[u].zero();
       }
     }
+    float sc[U];
 #pragma unroll
-    for (int u = 0; u < DEC_UNROLL; ++u) {
+    for (int u = 0; u < U; ++u) {
+      float kf[8];
+      kr[u].get(kf);
       float s = 0.f;
 #pragma unroll
-      for (int i = 0; i < 8; ++i) s = fmaf(qv[i], kv[u][i], s);
+      for (int i = 0; i < 8; ++i) s = fmaf(qv[i], kf[i], s);
 #pragma unroll
       for (int w = TPK / 2; w > 0; w >>= 1) s += __shfl_xor_sync(0xffffffffu, s, w);
-      if (ok[u]) {
-        const float m_new = fmaxf(m, s);
-        const float corr = expf(m - m_new);   // exp(-inf) = 0 on the first key
-        const float pw = expf(s - m_new);
-        l = l * corr + pw;
+      sc[u] = ok[u] ? s : -INFINITY;
+    }
+    float m_new = m;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = fmaf(pw, vv[u][i], o[i] * corr);
-        m = m_new;
+    for (int u = 0; u < U; ++u) m_new = fmaxf(m_new, sc[u]);
+    if (m_new != -INFINITY) {               // one rescale per batch instead of one per key
+      const float corr = expf(m - m_new);   // exp(-inf) = 0 for the first batch
+      l *= corr;
+#pragma unroll
+      for (int i = 0; i < 8; ++i) o[i] *= corr;
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        const float pw = expf(sc[u] - m_new);   // 0 for keys that are not there
+        float vf[8];
+        vr[u].get(vf);
+        l += pw;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = fmaf(pw, vf[i], o[i]);
       }
+      m = m_new;
     }
   }
 
-  float* sm_m = sm;
-  float* sm_l = sm + GROUPS;
-  float* sm_o = sm + 2 * GROUPS;
-  if (j == 0) { sm_m[grp] = m; sm_l[grp] = l; }
-  if (active) {
+  // Merge the thread groups: first the groups of a warp with shuffles (lanes that hold the same
+  // dims of different groups are TPK apart), then the warps through shared memory.
 #pragma unroll
-    for (int i = 0; i < 8; ++i) sm_o[grp * Dh + d0 + i] = o[i];
+  for (int w = TPK; w < 32; w <<= 1) {
+    const float m_o = __shfl_xor_sync(0xffffffffu, m, w);
+    const float l_o = __shfl_xor_sync(0xffffffffu, l, w);
+    const float m_n = fmaxf(m, m_o);
+    const float wa = m == -INFINITY ? 0.f : expf(m - m_n), wb = m_o == -INFINITY ? 0.f : expf(m_o - m_n);
+    l = l * wa + l_o * wb;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float o_o = __shfl_xor_sync(0xffffffffu, o[i], w);
+      o[i] = o[i] * wa + o_o * wb;
+    }
+    m = m_n;
+  }
+  constexpr int NWARP = DEC_THREADS / 32;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  float* sm_m = sm;                 // [NWARP]
+  float* sm_l = sm + NWARP;         // [NWARP]
+  float* sm_o = sm + 2 * NWARP;     // [NWARP][Dh]
+  if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+  if (lane < TPK && active) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) sm_o[warp * Dh + d0 + i] = o[i];
   }
   __syncthreads();
+  if (c0 == c1 && threadIdx.x >= Dh) return;   // single chunk: only Dh threads have work left
   float M = -INFINITY;
-  for (int g2 = 0; g2 < GROUPS; ++g2) M = fmaxf(M, sm_m[g2]);
+#pragma unroll
+  for (int w2 = 0; w2 < NWARP; ++w2) M = fmaxf(M, sm_m[w2]);
+  float wgt[NWARP];
+  float L = 0.f;
+#pragma unroll
+  for (int w2 = 0; w2 < NWARP; ++w2) {
+    wgt[w2] = sm_m[w2] == -INFINITY ? 0.f : expf(sm_m[w2] - M);
+    L = fmaf(sm_l[w2], wgt[w2], L);
+  }
+
+  if (c0 == c1) {   // the only chunk of this row: no partial results, no ticket
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+    for (int d = threadIdx.x; d < Dh; d += DEC_THREADS) {
+      float acc = 0.f;
+#pragma unroll
+      for (int w2 = 0; w2 < NWARP; ++w2) acc = fmaf(wgt[w2], sm_o[w2 * Dh + d], acc);
+      out[(size_t)t * ldo + h * Dh + d] = from_f<T>(acc * inv);
+    }
+    return;
+  }
+
   float* dst = partial + (((size_t)ri * Hq + h) * n_chunks_max + c) * (Dh + 2);
   for (int d = threadIdx.x; d < Dh; d += DEC_THREADS) {
     float acc = 0.f;
-    for (int g2 = 0; g2 < GROUPS; ++g2) {
-      const float w = sm_m[g2] == -INFINITY ? 0.f : expf(sm_m[g2] - M);
-      acc = fmaf(w, sm_o[g2 * Dh + d], acc);
-    }
+#pragma unroll
+    for (int w2 = 0; w2 < NWARP; ++w2) acc = fmaf(wgt[w2], sm_o[w2 * Dh + d], acc);
     dst[2 + d] = acc;
   }
   if (threadIdx.x == 0) {
-    float L = 0.f;
-    for (int g2 = 0; g2 < GROUPS; ++g2) L += sm_m[g2] == -INFINITY ? 0.f : sm_l[g2] * expf(sm_m[g2] - M);
     dst[0] = M;
     dst[1] = L;
   }
 
-  // The last CTA of this (row, head) to get here combines all chunks.
-  const int c0 = lo / chunk, c1 = p / chunk;
+  // The last CTA of this (row, head) to get here combines all chunks, in chunk order.
   __threadfence();
   __syncthreads();
   if (threadIdx.x == 0) {
@@ -346,7 +437,7 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
   __threadfence();
   const float* src = partial + ((size_t)ri * Hq + h) * n_chunks_max * (Dh + 2);
   float Mx = -INFINITY;
-  for (int cc = c0; cc <= c1; ++cc) Mx = fmaxf(Mx, __ldcg(src + (size_t)cc * (Dh + 2)));
+  for (int cc = c0; cc <= c1; ++cc) Mx = fmaxf(Mx, __ldcg(src + (size_t)cc * (Dh + 2)));   // independent loads
   float Ls = 0.f;
   for (int cc = c0; cc <= c1; ++cc)
     Ls += __ldcg(src + (size_t)cc * (Dh + 2) + 1) * expf(__ldcg(src + (size_t)cc * (Dh + 2)) - Mx);
@@ -370,15 +461,18 @@ static int launch_decode(const void* q, int ldq, const int* rows, const int* pos
   int tpk = 2;
   while (tpk < chunks8) tpk <<= 1;
   const dim3 grid(n_chunks_max, Hq, n_rows);
-#define DEC(TPK_)                                                                                                    \
+  const bool many = (long long)n_rows * Hq >= 592;
+#define DEC2(TPK_, TH_)                                                                                              \
   {                                                                                                                  \
-    const size_t smem = (size_t)(DEC_THREADS / TPK_) * (Dh + 2) * sizeof(float);                                     \
-    launch_pdl(attention_decode_kernel<T, TPK_>, grid, dim3(DEC_THREADS), smem, stream, (const T*)q, ldq, rows,      \
+    const size_t smem = (size_t)(TH_ / 32) * (Dh + 2) * sizeof(float);                                               \
+    launch_pdl(attention_decode_kernel<T, TPK_, TH_>, grid, dim3(TH_), smem, stream, (const T*)q, ldq, rows,         \
                positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, Dh, window, scale,              \
                (const T*)k_pool, (const T*)v_pool, partial, counters, n_chunks_max, chunk, (T*)out, ldo, status);    \
   }
+#define DEC(TPK_) { if (many) DEC2(TPK_, 256) else DEC2(TPK_, 512) }
   if (tpk == 2) DEC(2) else if (tpk == 4) DEC(4) else if (tpk == 8) DEC(8) else if (tpk == 16) DEC(16) else DEC(32)
 #undef DEC
+#undef DEC2
   return mlxb_check_launch("attention (single-token rows)");
 }
 

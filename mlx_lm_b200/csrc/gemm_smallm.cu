@@ -4,7 +4,7 @@
 // A, W, residual bfloat16; float32 accumulation; C bfloat16 or float32.
 //
 // The kernel is bound by reading W, so it is organised around that stream:
-// a CTA owns 8*NW output features (rows of W) over the whole K; its 8 warps
+// a CTA owns 8*NW output features (rows of W) over the whole K; its 8 (or 16) warps
 // take the 32-wide K blocks round robin, so the CTA reads 8 consecutive
 // blocks (512 contiguous bytes of each row) at a time, every thread with one
 // 16-byte load per row block straight into registers (no shared-memory
@@ -15,8 +15,9 @@
 // physically consecutive values 8q..8q+7 of the block, and since a dot product
 // does not care about the order of its terms, activation and weight fragments
 // agree as long as both use this mapping.
-// The 8 partial sums of a CTA are added in warp order through shared memory;
-// the order of additions depends on K alone, never on M or on the batch.
+// The partial sums of a CTA's warps are added in warp order through shared memory;
+// the order of additions depends on K and on the size class of M (up to 16, 32, 64
+// rows), never on which rows share the call.
 // K must be a multiple of 8 (16-byte loads); other K go to the generic kernel.
 //
 // Launch gaps: the kernel is launched as a programmatic dependent (common.cuh).  Before it
@@ -33,7 +34,6 @@ MLXB_DEFINE_LAST_ERROR()
 
 enum { EPI_NONE = 0, EPI_GELU_NEW = 1 };
 
-constexpr int WARPS = 8;
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;
@@ -64,8 +64,8 @@ struct KvScatter {
   int max_pages, n_pages, page, Hkv, Dh, q_width;
 };
 
-// MT: 16-row token tiles (M <= 16*MT); NW: 8-row weight tiles per CTA.
-template <int MT, int NW, typename TO, int EPI, bool SCATTER>
+// MT: 16-row token tiles (M <= 16*MT); NW: 8-row weight tiles per CTA; WARPS: warps that share the K blocks.
+template <int MT, int NW, int WARPS, typename TO, int EPI, bool SCATTER>
 __global__ void __launch_bounds__(WARPS * 32)
 gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                    const float* __restrict__ bias, const __nv_bfloat16* residual, TO* C, int M, int N, int K,
@@ -104,7 +104,7 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     }
 
   const int n_blocks = (K + 31) >> 5;
-  constexpr int UNROLL = (MT * NW >= 8) ? 1 : 2;   // K blocks per warp and iteration
+  constexpr int UNROLL = (MT * NW >= 8) ? 1 : (MT * NW >= 2 ? 2 : 4);   // K blocks per warp and iteration
   constexpr int STEP = WARPS * UNROLL;
 
   auto load_w = [&](int kb, uint4 (&dst)[UNROLL][NW]) {
@@ -207,13 +207,13 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
   }
 }
 
-template <int MT, int NW, typename TO, bool SCATTER>
+template <int MT, int NW, int WARPS, typename TO, bool SCATTER>
 static int launch_epi(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N,
                       int K, int lda, int ldc, int epi, const KvScatter& kv, cudaStream_t stream) {
   const dim3 grid((N + 8 * NW - 1) / (8 * NW));
   const size_t smem = (size_t)WARPS * MT * NW * 4 * 32 * sizeof(float);
-  auto k0 = gemm_smallm_kernel<MT, NW, TO, EPI_NONE, SCATTER>;
-  auto k1 = gemm_smallm_kernel<MT, NW, TO, EPI_GELU_NEW, SCATTER>;
+  auto k0 = gemm_smallm_kernel<MT, NW, WARPS, TO, EPI_NONE, SCATTER>;
+  auto k1 = gemm_smallm_kernel<MT, NW, WARPS, TO, EPI_GELU_NEW, SCATTER>;
   auto kern = epi == EPI_GELU_NEW ? k1 : k0;
   static bool raised[2] = {false, false};   // once per instantiation, and never for the first time inside a stream capture
   if (smem > 48 * 1024 && !raised[epi == EPI_GELU_NEW]) {
@@ -235,8 +235,14 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
   int nw = 1;
   if (mt == 4) nw = tiles >= 4 * 296 ? 4 : (tiles >= 2 * 148 ? 2 : 1);
   else if (mt == 2) nw = tiles >= 2 * 296 ? 2 : 1;
-#define GO(MT_, NW_) \
-  return launch_epi<MT_, NW_, TO, SCATTER>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, kv, stream)
+  // K blocks are shared by 8 warps; a long K with few output tiles gets 16 so that a warp's chain of
+  // dependent loads stays short.
+#define GO(MT_, NW_)                                                                                              \
+  {                                                                                                               \
+    if (K >= 2048 && MT_ * NW_ == 1)                                                                              \
+      return launch_epi<MT_, NW_, 16, TO, SCATTER>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, kv, stream);  \
+    return launch_epi<MT_, NW_, 8, TO, SCATTER>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, kv, stream);     \
+  }
   if (mt == 1) GO(1, 1);
   if (mt == 2) { if (nw == 2) GO(2, 2); GO(2, 1); }
   if (nw == 4) GO(4, 4);

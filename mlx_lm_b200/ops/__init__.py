@@ -349,7 +349,7 @@ _DEC_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_i
              c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
              c_void_p]
 
-DECODE_CHUNK = 128   # key positions per CTA of the single-token attention kernel: a constant, never a function of the batch
+DECODE_CHUNK = 1024   # key positions per CTA of the single-token attention kernel: a constant, never a function of the batch
 
 
 def attention_decode_scratch(n_rows: int, n_heads: int, head_dim: int, max_len: int, chunk: int = DECODE_CHUNK) -> int:
