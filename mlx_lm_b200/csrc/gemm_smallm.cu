@@ -179,7 +179,7 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     const int n = n0 + j * 8 + 2 * (ln & 3) + (c & 1);
     if (m < M && n < N) {
       if (bias) v += bias[n];
-      if (EPI == EPI_GELU_NEW) v = gelu_new_f(v);
+      if (EPI == EPI_GELU_NEW) v = gelu_new_fast(v);
       if (residual) v += __bfloat162float(residual[(size_t)m * ldc + n]);
       if (SCATTER && n >= kv.q_width) {
         const int r = kv.token_req[m];

@@ -2,14 +2,17 @@
 //   C[M,N] = epilogue(A[M,K] . W[N,K]^T + bias[N]) (+ residual[M,N])
 // A, W, residual bfloat16 (both operands K-major: the K index is contiguous), C bfloat16 or float32.
 //
-// One CTA computes a 128 x BN tile.  Warp 0 is the TMA producer: it fills a ring of shared-memory
-// stages with 128x64 tiles of A and BNx64 tiles of W (cp.async.bulk.tensor, 128-byte swizzle,
-// completion counted on an mbarrier per stage; rows and columns outside the matrices arrive as
-// zeros).  Warp 1 allocates tensor memory and issues tcgen05.mma (kind::f16, bf16 inputs, float32
-// accumulator of 128 lanes x BN columns in TMEM), four K=16 steps per stage, and releases each
-// stage with tcgen05.commit.  Warps 2-5 are the epilogue: when the accumulator is complete they
-// read it with tcgen05.ld (each warp its 32 lanes), add the bias, apply gelu_new, add the
-// residual and store.  No multicast anywhere: every CTA fetches its own tiles.
+// The kernel is persistent: one CTA per SM walks over the 128 x BN output tiles (BN = 128, 192 or 256,
+// chosen so that the last wave of tiles is as full as possible).  Warp 0 is the TMA producer: it fills a
+// ring of shared-memory stages with 128x64 tiles of A and BNx64 tiles of W (cp.async.bulk.tensor,
+// 128-byte swizzle, completion counted on an mbarrier per stage; rows and columns outside the
+// matrices arrive as zeros).  Warp 1 allocates tensor memory and issues tcgen05.mma (kind::f16, bf16
+// inputs, float32 accumulator of 128 lanes x BN columns in TMEM), four K=16 steps per stage, and
+// releases each stage with tcgen05.commit.  There are two accumulators in TMEM: while warps 2-9 (the
+// epilogue, two warps per quadrant of 32 TMEM lanes, each half of the columns) read a finished one
+// with tcgen05.ld, add the bias, apply gelu_new, add the residual and store, the MMA warp already
+// fills the other with the next tile.
+// No multicast anywhere: every CTA fetches its own tiles.
 //
 // Every wait on an mbarrier is bounded: after a limit of polls the waiter raises an abort flag in
 // shared memory and a bit in the caller's status word; all roles then fall through to the common
@@ -27,7 +30,8 @@ MLXB_DEFINE_LAST_ERROR()
 enum { EPI_NONE = 0, EPI_GELU_NEW = 1 };
 
 constexpr int BM = 128, BK = 64;
-constexpr int THREADS = 192;
+constexpr int EPI_WARPS = 8;                      // two per quadrant of TMEM lanes, each half of the columns
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -104,10 +108,82 @@ struct Smem {
   alignas(1024) __nv_bfloat16 b[STAGES][BN * BK];
   alignas(8) uint64_t full[STAGES];
   uint64_t empty[STAGES];
-  uint64_t acc_full;
+  uint64_t acc_full[2];
+  uint64_t acc_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+// One 8-column group of an output row: bias, activation, residual, store.
+template <typename TO, int EPI>
+__device__ __forceinline__ void store8(const uint32_t* r, int n8, int N, size_t row, const float* __restrict__ bias,
+                                       bool bias_vec, const __nv_bfloat16* residual, TO* C) {
+  float v[8];
+  const bool whole = n8 + 8 <= N;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+  if (bias) {
+    if (whole && bias_vec) {   // the same 32 bytes for every lane of the warp: two broadcast loads
+      const float4 b0 = *reinterpret_cast<const float4*>(bias + n8), b1 = *reinterpret_cast<const float4*>(bias + n8 + 4);
+      v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+      v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (n8 + i < N) v[i] += bias[n8 + i];
+    }
+  }
+  if (EPI == EPI_GELU_NEW) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = gelu_new_fast(v[i]);
+  }
+  if (residual) {
+    if (whole && ((row + n8) & 7) == 0) {
+      const uint4 u = *reinterpret_cast<const uint4*>(residual + row + n8);
+      const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        v[2 * i] += __uint_as_float(w[i] << 16);
+        v[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
+      }
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (n8 + i < N) v[i] += __bfloat162float(residual[row + n8 + i]);
+    }
+  }
+  if (sizeof(TO) == 2) {
+    __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + row + n8;
+    if (whole && ((row + n8) & 7) == 0) {
+      uint4 u;
+      uint32_t* w = reinterpret_cast<uint32_t*>(&u);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const __nv_bfloat162 pr = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        w[i] = *reinterpret_cast<const uint32_t*>(&pr);
+      }
+      *reinterpret_cast<uint4*>(out) = u;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (n8 + i < N) out[i] = __float2bfloat16_rn(v[i]);
+    }
+  } else {
+    float* out = reinterpret_cast<float*>(C) + row + n8;
+    if (whole && ((row + n8) & 3) == 0) {
+      *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
+      *reinterpret_cast<float4*>(out + 4) = make_float4(v[4], v[5], v[6], v[7]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        if (n8 + i < N) out[i] = v[i];
+    }
+  }
+}
 
 template <int BN, int STAGES, typename TO, int EPI>
 __global__ void __launch_bounds__(THREADS)
@@ -118,14 +194,15 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   Smem<BN, STAGES>& sm = *reinterpret_cast<Smem<BN, STAGES>*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int k_tiles = (K + BK - 1) / BK;
+  const int tiles_m = (M + BM - 1) / BM, tiles_n = (N + BN - 1) / BN;
+  const int n_tiles = tiles_m * tiles_n;
   constexpr uint32_t STAGE_BYTES = (BM + BN) * BK * sizeof(__nv_bfloat16);
-  constexpr uint32_t TMEM_COLS = BN < 32 ? 32 : BN;   // a power of two >= 32
+  constexpr uint32_t TMEM_COLS = BN <= 128 ? 256 : 512;   // two accumulators; a power of two
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
-    mbar_init(&sm.acc_full, 1);
+    for (int b = 0; b < 2; ++b) { mbar_init(&sm.acc_full[b], 1); mbar_init(&sm.acc_empty[b], 32 * EPI_WARPS); }
     sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -139,30 +216,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-  const uint32_t tmem_acc = sm.tmem_base;
+  const uint32_t tmem_base = sm.tmem_base;
   volatile int* abort_flag = &sm.abort_flag;
   pdl_trigger();
   pdl_wait();   // A (and the residual) come from the previous kernel
 
   if (warp == 0) {
     if (lane == 0) {
-      int issued = 0;
-      for (int kt = 0; kt < k_tiles; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t ph = (kt / STAGES) & 1;
-        if (!mbar_wait(&sm.empty[s], ph ^ 1, abort_flag)) break;
-        mbar_expect_tx(&sm.full[s], STAGE_BYTES);
-        tma_load_2d(sm.a[s], &map_a, kt * BK, m0, &sm.full[s]);
-        tma_load_2d(sm.b[s], &map_w, kt * BK, n0, &sm.full[s]);
-        issued = kt + 1;
+      int issued = 0;   // stages filled so far, over all tiles
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+        for (int kt = 0; kt < k_tiles; ++kt, ++issued) {
+          const int s = issued % STAGES;
+          const uint32_t ph = (issued / STAGES) & 1;
+          if (!mbar_wait(&sm.empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+          tma_load_2d(sm.a[s], &map_a, kt * BK, m0, &sm.full[s]);
+          tma_load_2d(sm.b[s], &map_w, kt * BK, n0, &sm.full[s]);
+        }
       }
       if (*abort_flag) {   // gave up: let the copies already issued land before the CTA exits
-        for (int kt = issued > STAGES ? issued - STAGES : 0; kt < issued; ++kt) {
-          const uint32_t addr = smem_u32(&sm.full[kt % STAGES]);
-          for (uint32_t i = 0; i < (1u << 20); ++i) {
+        for (int i = issued > STAGES ? issued - STAGES : 0; i < issued; ++i) {
+          const uint32_t addr = smem_u32(&sm.full[i % STAGES]);
+          for (uint32_t p = 0; p < (1u << 20); ++p) {
             uint32_t done;
             asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-                         "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(done) : "r"(addr), "r"((uint32_t)((kt / STAGES) & 1))
+                         "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(done) : "r"(addr), "r"((uint32_t)((i / STAGES) & 1))
                          : "memory");
             if (done) break;
           }
@@ -172,94 +252,60 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   } else if (warp == 1) {
     if (lane == 0) {
       constexpr uint32_t idesc = umma_idesc(BM, BN);
+      int consumed = 0, it = 0;
       bool ok = true;
-      for (int kt = 0; kt < k_tiles && ok; ++kt) {
-        const int s = kt % STAGES;
-        const uint32_t ph = (kt / STAGES) & 1;
-        ok = mbar_wait(&sm.full[s], ph, abort_flag);
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++it) {
+        const int b = it & 1;
+        // the epilogue must have drained this accumulator (its previous use was tile it-2)
+        ok = mbar_wait(&sm.acc_empty[b], ((it >> 1) & 1) ^ 1, abort_flag);
         if (!ok) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint64_t da = umma_desc(smem_u32(sm.a[s])), db = umma_desc(smem_u32(sm.b[s]));
+        const uint32_t tmem_acc = tmem_base + (uint32_t)(b * BN);
+        for (int kt = 0; kt < k_tiles; ++kt, ++consumed) {
+          const int s = consumed % STAGES;
+          const uint32_t ph = (consumed / STAGES) & 1;
+          ok = mbar_wait(&sm.full[s], ph, abort_flag);
+          if (!ok) break;
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint64_t da = umma_desc(smem_u32(sm.a[s])), db = umma_desc(smem_u32(sm.b[s]));
 #pragma unroll
-        for (int k = 0; k < BK / 16; ++k)   // 16 bf16 = 32 bytes = 2 units of the descriptor's start address
-          umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
-        umma_commit(&sm.empty[s]);   // the stage is free once these MMAs have read it
+          for (int k = 0; k < BK / 16; ++k)   // 16 bf16 = 32 bytes = 2 units of the descriptor's start address
+            umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
+          umma_commit(&sm.empty[s]);   // the stage is free once these MMAs have read it
+        }
+        if (ok) umma_commit(&sm.acc_full[b]);   // arrives when every MMA of this tile has completed
       }
-      umma_commit(&sm.acc_full);     // arrives when every MMA issued above has completed
     }
   } else {
-    // epilogue: warps 2..5; warp w may touch TMEM lanes 32*(w%4) .. +31, i.e. rows m0 + 32*(w%4) + lane
+    // epilogue: warps 2..9; warp w may touch TMEM lanes 32*(w%4) .. +31; the two warps of a quadrant
+    // split the tile's columns
     const int q = warp & 3;
-    const bool ready = mbar_wait(&sm.acc_full, 0, abort_flag);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const int m = m0 + q * 32 + lane;
-    if (ready) {
+    const int half = (warp - 2) >> 2;
+    constexpr int HALF_COLS = BN / 2;          // 64, 96 or 128: multiples of 32
+    const bool bias_vec = bias && (((uintptr_t)bias & 15) == 0);
+    int it = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
+      const int b = it & 1;
+      if (!mbar_wait(&sm.acc_full[b], (it >> 1) & 1, abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
+      const int m = m0 + q * 32 + lane;
+      const size_t row = (size_t)m * ldc;
+      const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + half * HALF_COLS);
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
         uint32_t r[32];
-        tmem_ld32(tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);   // every lane takes part
+        tmem_ld32(taddr + (uint32_t)c0, r);   // every lane takes part
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (c0 + 32 >= HALF_COLS) {   // this warp's part of the accumulator is in registers: hand it back
+          asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+          mbar_arrive(&sm.acc_empty[b]);
+        }
         if (m < M) {
-          const int n_base = n0 + c0;
-          const size_t row = (size_t)m * ldc;
 #pragma unroll
           for (int g8 = 0; g8 < 4; ++g8) {
-            const int n8 = n_base + g8 * 8;
-            if (n8 >= N) break;
-            float v[8];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int n = n8 + i;
-              float x = __uint_as_float(r[g8 * 8 + i]);
-              if (n < N) {
-                if (bias) x += bias[n];
-                if (EPI == EPI_GELU_NEW) x = gelu_new_f(x);
-              }
-              v[i] = x;
-            }
-            const bool whole = n8 + 8 <= N;
-            if (residual) {
-              if (whole && ((row + n8) & 7) == 0) {
-                const uint4 u = *reinterpret_cast<const uint4*>(residual + row + n8);
-                const uint32_t w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  v[2 * i] += __uint_as_float(w[i] << 16);
-                  v[2 * i + 1] += __uint_as_float(w[i] & 0xffff0000u);
-                }
-              } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  if (n8 + i < N) v[i] += __bfloat162float(residual[row + n8 + i]);
-              }
-            }
-            if (sizeof(TO) == 2) {
-              __nv_bfloat16* out = reinterpret_cast<__nv_bfloat16*>(C) + row + n8;
-              if (whole && ((row + n8) & 7) == 0) {
-                uint4 u;
-                uint32_t* w = reinterpret_cast<uint32_t*>(&u);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                  const __nv_bfloat162 pr = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                  w[i] = *reinterpret_cast<const uint32_t*>(&pr);
-                }
-                *reinterpret_cast<uint4*>(out) = u;
-              } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  if (n8 + i < N) out[i] = __float2bfloat16_rn(v[i]);
-              }
-            } else {
-              float* out = reinterpret_cast<float*>(C) + row + n8;
-              if (whole && ((row + n8) & 3) == 0) {
-                *reinterpret_cast<float4*>(out) = make_float4(v[0], v[1], v[2], v[3]);
-                *reinterpret_cast<float4*>(out + 4) = make_float4(v[4], v[5], v[6], v[7]);
-              } else {
-#pragma unroll
-                for (int i = 0; i < 8; ++i)
-                  if (n8 + i < N) out[i] = v[i];
-              }
-            }
+            const int n8 = n0 + half * HALF_COLS + c0 + g8 * 8;
+            if (n8 < N) store8<TO, EPI>(r + g8 * 8, n8, N, row, bias, bias_vec, residual, C);
           }
         }
       }
@@ -271,7 +317,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (threadIdx.x == 0 && sm.abort_flag) atomicOr(status, MLXB_ST_WAIT_TIMEOUT);
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"(TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
@@ -295,9 +341,22 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int 
   return 0;
 }
 
+static int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 template <int BN, int STAGES, typename TO>
-static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, const void* residual, void* C,
-                  int M, int N, int K, int ldc, int epi, int* status, cudaStream_t stream) {
+static int launch(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N, int K,
+                  int lda, int ldc, int epi, int* status, cudaStream_t stream) {
+  CUtensorMap ma, mw;
+  if (int e = make_map(&ma, A, M, K, lda, BM)) return e;
+  if (int e = make_map(&mw, W, N, K, K, BN)) return e;
   const size_t smem = sizeof(Smem<BN, STAGES>) + 1024;
   auto k0 = gemm_tcgen05_kernel<BN, STAGES, TO, EPI_NONE>;
   auto k1 = gemm_tcgen05_kernel<BN, STAGES, TO, EPI_GELU_NEW>;
@@ -309,7 +368,8 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mw, const float* bia
                                            cudaGetErrorString(e));
     raised[epi == EPI_GELU_NEW] = true;
   }
-  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  const int n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
+  const dim3 grid(n_tiles < sm_count() ? n_tiles : sm_count());
   launch_pdl(kern, grid, dim3(THREADS), smem, stream, ma, mw, bias, (const __nv_bfloat16*)residual, (TO*)C, M, N, K,
              ldc, status);
   return mlxb_check_launch("linear (tensor cores)");
@@ -329,11 +389,23 @@ MLXB_EXPORT int mlxb_linear_tcgen05(int out_f32, const void* A, const void* W, c
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15))
     return mlxb_fail(MLXB_BAD_ARG, "linear (tensor cores): operands must be 16-byte aligned");
   if (epi != EPI_NONE && epi != EPI_GELU_NEW) return mlxb_fail(MLXB_BAD_ARG, "linear: epilogue code %d", epi);
-  if ((M + BM - 1) / BM > 65535) return mlxb_fail(MLXB_BAD_ARG, "linear (tensor cores): %d rows are too many", M);
-  constexpr int BN = 128, STAGES = 4;
-  CUtensorMap ma, mw;
-  if (int e = make_map(&ma, A, M, K, lda, BM)) return e;
-  if (int e = make_map(&mw, W, N, K, K, BN)) return e;
-  if (out_f32) return launch<BN, STAGES, float>(ma, mw, bias, residual, C, M, N, K, ldc, epi, status, stream);
-  return launch<BN, STAGES, __nv_bfloat16>(ma, mw, bias, residual, C, M, N, K, ldc, epi, status, stream);
+  // Tile width: the one whose waves of tiles over the SMs cost least, a tile's cost being the bytes it streams
+  // from L2 per K step (128 rows of A plus BN rows of W).
+  const int tiles_m = (M + BM - 1) / BM, sms = sm_count();
+  int best = 128;
+  long long best_cost = -1;
+  for (int bn : {256, 192, 128}) {
+    const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn);
+    const long long cost = ((tiles + sms - 1) / sms) * (BM + bn);
+    if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
+  }
+#define GO(BN_, ST_)                                                                                              \
+  {                                                                                                               \
+    if (out_f32) return launch<BN_, ST_, float>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, status, stream);  \
+    return launch<BN_, ST_, __nv_bfloat16>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, status, stream);       \
+  }
+  if (best == 256) GO(256, 4)
+  if (best == 192) GO(192, 5)
+  GO(128, 6)
+#undef GO
 }

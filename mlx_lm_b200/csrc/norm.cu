@@ -1,5 +1,6 @@
 // LayerNorm with gain and optional bias.  Statistics are computed in 32-bit
-// in two passes over a copy of the row held in shared memory:
+// in two passes over a copy of the row held in registers (one warp per row, widths up to 2048
+// that are multiples of 8) or in shared memory (one block per row, any other width):
 //   mean = sum(x)/D;  var = sum((x-mean)^2)/D  (biased);
 //   y = (x-mean) * rsqrt(var+eps) * gain + bias.
 // `rows` (optional) gathers input rows: output row r is the norm of input row
@@ -42,12 +43,114 @@ __global__ void layernorm_kernel(const T* __restrict__ x, const int* __restrict_
   }
 }
 
+// Rows up to 2048 wide whose width is a multiple of 8: one warp per row, the row in registers (8-element
+// chunks, 16-byte loads), warp shuffles for both sums; no shared memory and no block barrier.  The
+// reduction order is fixed by D alone.
+template <typename T, int NCH>
+__global__ void __launch_bounds__(256)
+layernorm_warp_kernel(const T* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ gain,
+                      const float* __restrict__ bias, T* __restrict__ y, int R, int D, float eps) {
+  pdl_trigger();
+  pdl_wait();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + warp;
+  if (r >= R) return;
+  const T* xi = x + (size_t)(rows ? rows[r] : r) * D;
+  float v[NCH][8];
+  float s = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int d = (c * 32 + lane) * 8;
+    if (d < D) {
+      if (sizeof(T) == 2) {
+        const uint4 u = *reinterpret_cast<const uint4*>(xi + d);
+        const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          v[c][2 * i] = __uint_as_float(w[i] << 16);
+          v[c][2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+      } else {
+        const float4 a = *reinterpret_cast<const float4*>(xi + d), b = *reinterpret_cast<const float4*>(xi + d + 4);
+        v[c][0] = a.x; v[c][1] = a.y; v[c][2] = a.z; v[c][3] = a.w;
+        v[c][4] = b.x; v[c][5] = b.y; v[c][6] = b.z; v[c][7] = b.w;
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) s += v[c][i];
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[c][i] = 0.f;
+    }
+  }
+  const float mean = warp_sum(s) / (float)D;
+  float q = 0.f;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    if ((c * 32 + lane) * 8 < D) {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { const float t = v[c][i] - mean; q += t * t; }
+    }
+  }
+  const float rstd = rsqrtf(warp_sum(q) / (float)D + eps);
+  T* yo = y + (size_t)r * D;
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int d = (c * 32 + lane) * 8;
+    if (d < D) {
+      float o[8];
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        o[i] = (v[c][i] - mean) * rstd * gain[d + i];
+        if (bias) o[i] += bias[d + i];
+      }
+      if (sizeof(T) == 2) {
+        uint4 u;
+        unsigned* w = reinterpret_cast<unsigned*>(&u);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const __nv_bfloat162 pr = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+          w[i] = *reinterpret_cast<const unsigned*>(&pr);
+        }
+        *reinterpret_cast<uint4*>(yo + d) = u;
+      } else {
+        *reinterpret_cast<float4*>(yo + d) = make_float4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<float4*>(yo + d + 4) = make_float4(o[4], o[5], o[6], o[7]);
+      }
+    }
+  }
+}
+
+template <typename T>
+static bool launch_warp(const void* x, const int* rows, const float* gain, const float* bias, void* y, int R, int D,
+                        float eps, cudaStream_t stream) {
+  if ((D & 7) || D > 2048 || ((uintptr_t)x & 15) || ((uintptr_t)y & 15)) return false;
+  const int nch = (D + 255) / 256;
+  const dim3 grid((R + 7) / 8), block(256);
+#define LNW(N_) launch_pdl(layernorm_warp_kernel<T, N_>, grid, block, 0, stream, (const T*)x, rows, gain, bias, (T*)y, R, D, eps)
+  switch (nch) {
+    case 1: LNW(1); break;
+    case 2: LNW(2); break;
+    case 3: LNW(3); break;
+    case 4: LNW(4); break;
+    case 5: LNW(5); break;
+    case 6: LNW(6); break;
+    case 7: LNW(7); break;
+    default: LNW(8); break;
+  }
+#undef LNW
+  return true;
+}
+
 // x: [*, D] of dtype; rows: int32[R] or null (then R rows of x in order);
 // gain, bias: float32[D] (bias may be null); y: [R, D] of dtype.
 MLXB_EXPORT int mlxb_layernorm(int dtype, const void* x, const int* rows, const float* gain, const float* bias,
                                void* y, int R, int D, float eps, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (D <= 0 || D > 49152) return mlxb_fail(MLXB_BAD_ARG, "layernorm: width %d is outside 1..49152", D);
+  if (dtype != MLXB_F32 && dtype != MLXB_BF16) return mlxb_fail(MLXB_BAD_DTYPE, "layernorm: dtype code %d", dtype);
+  if (dtype == MLXB_F32 ? launch_warp<float>(x, rows, gain, bias, y, R, D, eps, stream)
+                        : launch_warp<__nv_bfloat16>(x, rows, gain, bias, y, R, D, eps, stream))
+    return mlxb_check_launch("layernorm");
   const int threads = D >= 2048 ? 512 : (D >= 512 ? 256 : (D >= 128 ? 128 : 64));
   const size_t smem = (size_t)(D + 40) * sizeof(float);
   if (dtype == MLXB_F32) {
