@@ -58,6 +58,25 @@ __global__ void kv_write_kernel(const T* __restrict__ k_src, const T* __restrict
   }
   const int row = p % page;
   const int n = Hkv * Dh;
+  if ((Dh & 7) == 0 && (ld & 7) == 0 && (((uintptr_t)k_src | (uintptr_t)v_src | (uintptr_t)k_pool | (uintptr_t)v_pool) & 15) == 0) {
+    // 8 elements at a time (16 bytes of bfloat16, 32 of float32): a head's row is contiguous in the page
+    for (int i = threadIdx.x * 8; i < n; i += blockDim.x * 8) {
+      const int h = i / Dh, d = i - h * Dh;
+      const size_t dst = (((size_t)pg * Hkv + h) * page + row) * Dh + d;
+      const size_t src = (size_t)t * ld + i;
+      if (sizeof(T) == 2) {
+        *reinterpret_cast<uint4*>(k_pool + dst) = *reinterpret_cast<const uint4*>(k_src + src);
+        *reinterpret_cast<uint4*>(v_pool + dst) = *reinterpret_cast<const uint4*>(v_src + src);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 8; e += 4) {
+          *reinterpret_cast<float4*>(k_pool + dst + e) = *reinterpret_cast<const float4*>(k_src + src + e);
+          *reinterpret_cast<float4*>(v_pool + dst + e) = *reinterpret_cast<const float4*>(v_src + src + e);
+        }
+      }
+    }
+    return;
+  }
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const int h = i / Dh, d = i - h * Dh;
     const size_t dst = (((size_t)pg * Hkv + h) * page + row) * Dh + d;
@@ -157,7 +176,7 @@ MLXB_EXPORT int mlxb_kv_write(int dtype, const void* k_src, const void* v_src, i
                               cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (int e = check_common("kv_write", page, Hkv, Hkv, Dh)) return e;
-  const int threads = Hkv * Dh >= 512 ? 256 : 128;
+  const int threads = Hkv * Dh >= 2048 ? 256 : (Hkv * Dh >= 1024 ? 128 : 64);
   if (dtype == MLXB_F32)
     launch_pdl(kv_write_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)k_src,
                (const float*)v_src, ld, positions, token_req, block_table, max_pages, n_pages, page, Hkv, Dh,

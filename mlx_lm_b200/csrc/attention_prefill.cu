@@ -48,6 +48,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const unsigned (&a)[4], 
                : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (ex2.approx: relative error about 2^-22; 2^-inf = 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
   const __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
   return *reinterpret_cast<const unsigned*>(&v);
@@ -56,7 +62,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // tiles: int32 [n_tiles][4] = (row of the tile's first token among the step's tokens, queries in the tile
 // (1..64), block-table row of the request, position of the tile's first query).
 template <int DH>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, DH <= 64 ? 4 : 2)
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int4* __restrict__ tiles,
                          const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                          int window, float scale_log2e, const __nv_bfloat16* __restrict__ k_pool,
@@ -186,15 +192,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
       const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
       const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo, base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
-      const float corr_lo = exp2f(m_lo - base_lo), corr_hi = exp2f(m_hi - base_hi);   // exp2(-inf) = 0
+      const float corr_lo = fast_exp2(m_lo - base_lo), corr_hi = fast_exp2(m_hi - base_hi);   // 2^-inf = 0
       m_lo = mn_lo;
       m_hi = mn_hi;
       float sum_lo = 0.f, sum_hi = 0.f;
       unsigned pa[BKV / 16][4];
 #pragma unroll
       for (int i = 0; i < BKV / 8; ++i) {
-        const float e0 = exp2f(s[i][0] - base_lo), e1 = exp2f(s[i][1] - base_lo);
-        const float e2 = exp2f(s[i][2] - base_hi), e3 = exp2f(s[i][3] - base_hi);
+        const float e0 = fast_exp2(s[i][0] - base_lo), e1 = fast_exp2(s[i][1] - base_lo);
+        const float e2 = fast_exp2(s[i][2] - base_hi), e3 = fast_exp2(s[i][3] - base_hi);
         sum_lo += e0 + e1;
         sum_hi += e2 + e3;
         // accumulator tiles 2j and 2j+1 are the A fragment of the j-th 16-key step of P V

@@ -97,11 +97,17 @@ layernorm_warp_kernel(const T* __restrict__ x, const int* __restrict__ rows, con
   for (int c = 0; c < NCH; ++c) {
     const int d = (c * 32 + lane) * 8;
     if (d < D) {
-      float o[8];
+      float o[8], gn[8], bs[8];
+      *reinterpret_cast<float4*>(gn) = *reinterpret_cast<const float4*>(gain + d);
+      *reinterpret_cast<float4*>(gn + 4) = *reinterpret_cast<const float4*>(gain + d + 4);
+      if (bias) {
+        *reinterpret_cast<float4*>(bs) = *reinterpret_cast<const float4*>(bias + d);
+        *reinterpret_cast<float4*>(bs + 4) = *reinterpret_cast<const float4*>(bias + d + 4);
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        o[i] = (v[c][i] - mean) * rstd * gain[d + i];
-        if (bias) o[i] += bias[d + i];
+        o[i] = (v[c][i] - mean) * rstd * gn[i];
+        if (bias) o[i] += bs[i];
       }
       if (sizeof(T) == 2) {
         uint4 u;
@@ -123,7 +129,9 @@ layernorm_warp_kernel(const T* __restrict__ x, const int* __restrict__ rows, con
 template <typename T>
 static bool launch_warp(const void* x, const int* rows, const float* gain, const float* bias, void* y, int R, int D,
                         float eps, cudaStream_t stream) {
-  if ((D & 7) || D > 2048 || ((uintptr_t)x & 15) || ((uintptr_t)y & 15)) return false;
+  if ((D & 7) || D > 2048 || ((uintptr_t)x & 15) || ((uintptr_t)y & 15) || ((uintptr_t)gain & 15) ||
+      ((uintptr_t)bias & 15))
+    return false;
   const int nch = (D + 255) / 256;
   const dim3 grid((R + 7) / 8), block(256);
 #define LNW(N_) launch_pdl(layernorm_warp_kernel<T, N_>, grid, block, 0, stream, (const T*)x, rows, gain, bias, (T*)y, R, D, eps)

@@ -86,6 +86,31 @@ def _fn(libname: str, fname: str, argtypes):
 
 
 launch_count = 0   # kernel launches issued through this module (bench.py reads and resets it)
+_recording = None  # while a list: every launch is appended as (launcher, library, name, arguments)
+
+
+def start_recording() -> None:
+    """Begin to note every launch with its raw arguments, so that a step of the same shape can be
+    re-issued later without going through the checks and the parts again (``replay``)."""
+    global _recording
+    _recording = []
+
+
+def stop_recording():
+    global _recording
+    calls, _recording = _recording, None
+    return calls
+
+
+def replay(calls) -> None:
+    """Re-issue recorded launches.  The caller guarantees that every buffer they name is still where it was."""
+    global launch_count
+    for f, lib, fname, args in calls:
+        rc = f(*args)
+        if rc != 0:
+            msg = lib.mlxb_last_error()
+            raise KernelError(f"{fname} failed ({rc}): {msg.decode() if msg else ''}")
+    launch_count += len(calls)
 
 
 def _call(libname: str, fname: str, argtypes, *args) -> None:
@@ -96,6 +121,8 @@ def _call(libname: str, fname: str, argtypes, *args) -> None:
     if rc != 0:
         msg = lib.mlxb_last_error()
         raise KernelError(f"{fname} failed ({rc}): {msg.decode() if msg else ''}")
+    if _recording is not None:
+        _recording.append((f, lib, fname, args))
 
 
 # --------------------------------------------------------------------------

@@ -66,6 +66,11 @@ class StateSpec:
 
 class Part:
     kernel_libs: Tuple[str, ...] = ()   # names under csrc/ this part launches kernels from
+    # True if forward() does nothing but launch kernels through mlx_lm_b200.ops, with arguments that are
+    # fixed by the step's shape (token, request, wanted-row, single-token and tile counts).  The engine
+    # then re-issues a recorded step of the same shape without calling forward() again.  Leave it False
+    # for a part that does anything else (host-side loops over requests, torch operators, ...).
+    replayable: bool = False
 
     def param_specs(self) -> List[ParamSpec]:
         return []
@@ -81,6 +86,9 @@ class Part:
         for c in self.children():
             out.extend(c.all_param_specs())
         return out
+
+    def all_replayable(self) -> bool:
+        return self.replayable and all(c.all_replayable() for c in self.children())
 
     def all_kernel_libs(self) -> List[str]:
         out = list(self.kernel_libs)

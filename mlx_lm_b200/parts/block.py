@@ -9,6 +9,7 @@ from .base import Block, FeedForward, Mixer, Norm, register_part
 
 
 class PreNormBlock(Block):
+    replayable = True
     def __init__(self, norm_1: Norm, mixer: Mixer, norm_2: Norm, feed_forward: FeedForward):
         self.norm_1, self.mixer, self.norm_2, self.feed_forward = norm_1, mixer, norm_2, feed_forward
 

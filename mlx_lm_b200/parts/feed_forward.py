@@ -10,6 +10,7 @@ from .linear import ACTIVATIONS, Linear
 
 
 class MLP(FeedForward):
+    replayable = True
     def __init__(self, name: str, width: int, inner: int, activation: str = "gelu_new", bias: bool = True,
                  stored: str = "out_in", up_name: str = "c_fc", down_name: str = "c_proj", init: Init = Init(),
                  bias_init: Init = Init()):

@@ -20,6 +20,7 @@ ACTIVATIONS = {None: ops.EPI_NONE, "none": ops.EPI_NONE, "gelu_new": ops.EPI_GEL
 
 
 class Linear(Part):
+    replayable = True
     kernel_libs = ("gemm_simt", "gemm_smallm", "gemm_tcgen05")
 
     def __init__(self, name: str, n_in: int, n_out: int, bias: bool = True, stored: str = "out_in",

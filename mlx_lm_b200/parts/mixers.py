@@ -22,6 +22,7 @@ from .linear import Linear
 
 
 class Attention(Mixer):
+    replayable = True
     kernel_libs = ("attention", "attention_prefill")
 
     def __init__(self, name: str, width: int, n_heads: int, head_dim: int, n_kv_heads: Optional[int] = None,

@@ -34,6 +34,7 @@ class RunEntry:
 
 class TokenEmbedding(Part):
     """``h = table[token] * scale (+ position table[position])`` (mlx_lm/models/gpt2.py:132, 144)."""
+    replayable = True
     kernel_libs = ("embed",)
 
     def __init__(self, name: str, vocab_size: int, width: int, scale: float = 1.0, init: Init = Init()):
@@ -56,6 +57,7 @@ class TokenEmbedding(Part):
 class OutputHead(Part):
     """Logits in float32.  Tied: the embedding table is the weight and there is no bias
     (``wte.as_linear``, mlx_lm/models/gpt2.py:166-167); untied: a linear layer of its own."""
+    replayable = True
 
     def __init__(self, vocab_size: int, width: int, tied_to: Optional[TokenEmbedding] = None,
                  name: str = "lm_head", bias: bool = False):

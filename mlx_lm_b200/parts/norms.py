@@ -11,6 +11,7 @@ from .base import VECTOR, Init, Norm, ParamSpec, register_part
 
 
 class LayerNorm(Norm):
+    replayable = True
     kernel_libs = ("norm",)
 
     def __init__(self, name: str, width: int, eps: float, bias: bool = True, gain_init: Init = Init(1.0, 0.0),

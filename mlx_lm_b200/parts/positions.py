@@ -17,6 +17,7 @@ from .base import MATRIX, Init, ParamSpec, PositionEncoding, register_part
 
 
 class LearnedAbsolute(PositionEncoding):
+    replayable = True
     def __init__(self, name: str, n_positions: int, width: int, init: Init = Init()):
         self.name, self.n_positions, self.width, self.init = name, n_positions, width, init
         self.max_positions = n_positions
@@ -33,6 +34,7 @@ class LearnedAbsolute(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
+    replayable = True
     max_positions = None
 
 
