@@ -154,7 +154,8 @@ class Engine:
             if max_tokens is None:
                 max_tokens = max_requests * self.max_len
             n_pages = (max_tokens + page_size - 1) // page_size
-        kernel_build.ensure_built(d.kernel_libs())
+        libs = [n for n in d.kernel_libs() if model.dtype == torch.bfloat16 or n not in ops.BF16_ONLY_LIBS]
+        kernel_build.ensure_built(libs)      # compiled now, in parallel, if this is their first use
         self.cache = CacheManager(d.cache_specs(), page_size=page_size, n_pages=n_pages, max_requests=max_requests,
                                   max_len=self.max_len, dtype=model.dtype, device=model.device)
         self.ws = Workspace(model.device)

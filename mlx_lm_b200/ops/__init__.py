@@ -25,6 +25,9 @@ EPI_NONE, EPI_GELU_NEW = 0, 1
 
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
+# kernel sources that only a bfloat16 run launches from: a float32 run neither compiles nor loads them
+BF16_ONLY_LIBS = frozenset({"gemm_smallm", "gemm_tcgen05", "attention_prefill"})
+
 # status word bits set by kernels (csrc/common.cuh)
 ST_TOKEN_RANGE, ST_POSITION_RANGE, ST_PAGE_RANGE, ST_WAIT_TIMEOUT = 1, 2, 4, 8
 
