@@ -8,8 +8,8 @@
 // 128-byte swizzle, completion counted on an mbarrier per stage; rows and columns outside the
 // matrices arrive as zeros).  Warp 1 allocates tensor memory and issues tcgen05.mma (kind::f16, bf16
 // inputs, float32 accumulator of 128 lanes x BN columns in TMEM), four K=16 steps per stage, and
-// releases each stage with tcgen05.commit.  There are two accumulators in TMEM: while warps 2-9 (the
-// epilogue, two warps per quadrant of 32 TMEM lanes, each half of the columns) read a finished one
+// releases each stage with tcgen05.commit.  There are two accumulators in TMEM: while warps 2-17 (the
+// epilogue, four warps per quadrant of 32 TMEM lanes, each a quarter of the columns) read a finished one
 // with tcgen05.ld, add the bias, apply gelu_new, add the residual and store, the MMA warp already
 // fills the other with the next tile.
 // No multicast anywhere: every CTA fetches its own tiles.
@@ -30,7 +30,7 @@ MLXB_DEFINE_LAST_ERROR()
 enum { EPI_NONE = 0, EPI_GELU_NEW = 1 };
 
 constexpr int BM = 128, BK = 64;
-constexpr int EPI_WARPS = 8;                      // two per quadrant of TMEM lanes, each half of the columns
+constexpr int EPI_WARPS = 16;                     // four per quadrant of TMEM lanes, each a quarter of the columns
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
 
@@ -99,6 +99,15 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
         "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
         "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
         "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
       : "r"(taddr));
 }
 
@@ -277,11 +286,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       }
     }
   } else {
-    // epilogue: warps 2..9; warp w may touch TMEM lanes 32*(w%4) .. +31; the two warps of a quadrant
+    // epilogue: warps 2..17; warp w may touch TMEM lanes 32*(w%4) .. +31; the four warps of a quadrant
     // split the tile's columns
     const int q = warp & 3;
-    const int half = (warp - 2) >> 2;
-    constexpr int HALF_COLS = BN / 2;          // 64, 96 or 128: multiples of 32
+    const int half = (warp - 2) >> 2;          // which slice of the columns (0 .. EPI_WARPS/4 - 1)
+    constexpr int HALF_COLS = BN / (EPI_WARPS / 4);   // 32, 48 or 64 columns per warp
     const bool bias_vec = bias && (((uintptr_t)bias & 15) == 0);
     int it = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
@@ -295,7 +304,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll 1
       for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
         uint32_t r[32];
-        tmem_ld32(taddr + (uint32_t)c0, r);   // every lane takes part
+        if (c0 + 32 <= HALF_COLS) {
+          tmem_ld32(taddr + (uint32_t)c0, r);   // every lane takes part
+        } else {                                // 48 columns per warp (BN = 192): the last 16
+          tmem_ld16(taddr + (uint32_t)c0, r);
+        }
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (c0 + 32 >= HALF_COLS) {   // this warp's part of the accumulator is in registers: hand it back
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -305,7 +318,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int g8 = 0; g8 < 4; ++g8) {
             const int n8 = n0 + half * HALF_COLS + c0 + g8 * 8;
-            if (n8 < N) store8<TO, EPI>(r + g8 * 8, n8, N, row, bias, bias_vec, residual, C);
+            if (c0 + g8 * 8 < HALF_COLS && n8 < N) store8<TO, EPI>(r + g8 * 8, n8, N, row, bias, bias_vec, residual, C);
           }
         }
       }
@@ -399,6 +412,7 @@ MLXB_EXPORT int mlxb_linear_tcgen05(int out_f32, const void* A, const void* W, c
     const long long cost = ((tiles + sms - 1) / sms) * (BM + bn);
     if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
   }
+  if (const char* force = getenv("MLXB_TC_BN")) best = atoi(force);   // experiments only
 #define GO(BN_, ST_)                                                                                              \
   {                                                                                                               \
     if (out_f32) return launch<BN_, ST_, float>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, status, stream);  \
