@@ -1,7 +1,7 @@
 // Causal attention of prompt portions over the paged key/value cache, on tensor cores.
 //
-// A portion (the next n > 1 tokens of one request) is cut into tiles of 64 queries; one CTA of four
-// warps handles (tile, query head), 16 queries a warp.  It walks the request's keys in blocks of 64
+// A portion (the next n > 1 tokens of one request) is cut into tiles of 64 or 128 queries; one CTA of four
+// or eight warps handles (tile, query head), 16 queries a warp.  It walks the request's keys in blocks of 64
 // positions, from the first block the tile may see (0, or the window's lower edge) to the block of
 // the tile's last query; the keys of this very step are already in the pages.  K and V blocks are
 // gathered through the block table with 16-byte cp.async into double-buffered shared memory (rows
@@ -22,7 +22,7 @@
 
 MLXB_DEFINE_LAST_ERROR()
 
-constexpr int BKV = 64, WARPS = 4;   // 16 queries a warp: 64 queries a CTA
+constexpr int BKV = 64;   // keys per block; a warp owns 16 queries, a CTA of 4 or 8 warps a tile of 64 or 128
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
   const unsigned d = (unsigned)__cvta_generic_to_shared(dst);
@@ -60,18 +60,20 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 }
 
 // tiles: int32 [n_tiles][4] = (row of the tile's first token among the step's tokens, queries in the tile
-// (1..64), block-table row of the request, position of the tile's first query).
-template <int DH>
-__global__ void __launch_bounds__(WARPS * 32, DH <= 64 ? 4 : 2)
+// (1..16*WARPS), block-table row of the request, position of the tile's first query).
+template <int DH, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, (DH <= 64 ? 512 : 256) / (WARPS * 32))
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int4* __restrict__ tiles,
                          const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                          int window, float scale_log2e, const __nv_bfloat16* __restrict__ k_pool,
                          const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, int ldo,
                          int* __restrict__ status) {
+  constexpr int THREADS = WARPS * 32;
   constexpr int STRIDE = DH + 8;              // elements per shared-memory row (16 bytes of padding)
   constexpr int KS = DH / 16;                 // k steps of Q K^T
   constexpr int NT = DH / 8;                  // n tiles of the output
   constexpr int CHUNKS = DH / 8;              // 16-byte chunks per key row
+  constexpr int NIT = (BKV * CHUNKS + THREADS - 1) / THREADS;   // chunks a thread copies per block
   extern __shared__ __align__(16) uint8_t smem_raw[];
   __nv_bfloat16* sk = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [2][BKV][STRIDE]
   __nv_bfloat16* sv = sk + 2 * BKV * STRIDE;                             // [2][BKV][STRIDE]
@@ -89,13 +91,26 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
   const int first_key = (window > 0 && pos0 - window + 1 > 0) ? pos0 - window + 1 : 0;
   const int kb_lo = first_key / BKV, kb_hi = last_pos / BKV;
 
+  // Which chunks of a block this thread copies: fixed for the whole kernel.
+  int c_row[NIT], c_soff[NIT], c_goff[NIT];
+#pragma unroll
+  for (int j = 0; j < NIT; ++j) {
+    const int i = threadIdx.x + j * THREADS;
+    const int kr = i / CHUNKS, ch = i - kr * CHUNKS;
+    c_row[j] = i < BKV * CHUNKS ? kr : -1;
+    c_soff[j] = kr * STRIDE + ch * 8;
+    c_goff[j] = hk * page * DH + ch * 8;
+  }
+  const size_t page_elems = (size_t)Hkv * page * DH;
+
   // gather one block of keys and values into stage `st`
   auto load_block = [&](int kb, int st) {
     __nv_bfloat16* dk = sk + st * BKV * STRIDE;
     __nv_bfloat16* dv = sv + st * BKV * STRIDE;
-    for (int i = threadIdx.x; i < BKV * CHUNKS; i += WARPS * 32) {
-      const int kr = i / CHUNKS, ch = i - kr * CHUNKS;
-      const int key = kb * BKV + kr;
+#pragma unroll
+    for (int j = 0; j < NIT; ++j) {
+      if (c_row[j] < 0) continue;
+      const int key = kb * BKV + c_row[j];
       bool ok = key <= last_pos && key >= first_key;
       size_t off = 0;
       if (ok) {
@@ -105,11 +120,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
           atomicOr(status, pg < 0 ? MLXB_ST_POSITION_RANGE : MLXB_ST_PAGE_RANGE);
           ok = false;
         } else {
-          off = (((size_t)pg * Hkv + hk) * page + (key & (page - 1))) * DH + ch * 8;
+          off = (size_t)pg * page_elems + (size_t)((key & (page - 1)) * DH + c_goff[j]);
         }
       }
-      cp_async16(dk + kr * STRIDE + ch * 8, k_pool + off, ok);
-      cp_async16(dv + kr * STRIDE + ch * 8, v_pool + off, ok);
+      cp_async16(dk + c_soff[j], k_pool + off, ok);
+      cp_async16(dv + c_soff[j], v_pool + off, ok);
     }
     cp_async_commit();
   };
@@ -135,13 +150,17 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
       qa[ks][3] = v_hi ? *reinterpret_cast<const unsigned*>(q_hi + d + 8) : 0u;
     }
   }
-  const int warp_last_pos = min(last_pos, pos0 + warp * 16 + 15);
+  const int warp_first_pos = pos0 + warp * 16;
+  const int warp_last_pos = min(last_pos, warp_first_pos + 15);
+  const bool warp_whole = warp * 16 + 15 < n_rows;                       // all 16 rows are real queries
+  const int warp_floor = (window > 0 && warp_last_pos - window + 1 > 0) ? warp_last_pos - window + 1 : 0;
 
   float o[NT][4];
 #pragma unroll
   for (int i = 0; i < NT; ++i)
 #pragma unroll
     for (int c = 0; c < 4; ++c) o[i][c] = 0.f;
+  // running maximum in units of the exponent (score * scale * log2 e), running sum per lane
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
   const int mi = lane >> 3, mr = lane & 7;   // ldmatrix: which 8x8 matrix this lane addresses, and its row
@@ -170,27 +189,34 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
           mma_bf16(s[2 * np + 1], qa[ks], b[2], b[3]);
         }
       }
-      // mask, scale (to base-2 exponents) and running maximum
-      const int key0 = kb * BKV + 2 * qd;
+      // mask (only blocks that touch the diagonal, the window's edge or the tile's end need it) and row maxima
+      const bool open = warp_whole && kb * BKV + BKV - 1 <= warp_first_pos && kb * BKV >= warp_floor;
       float mx_lo = -INFINITY, mx_hi = -INFINITY;
+      if (open) {
 #pragma unroll
-      for (int i = 0; i < BKV / 8; ++i) {
+        for (int i = 0; i < BKV / 8; ++i) {
+          mx_lo = fmaxf(mx_lo, fmaxf(s[i][0], s[i][1]));
+          mx_hi = fmaxf(mx_hi, fmaxf(s[i][2], s[i][3]));
+        }
+      } else {
+        const int key0 = kb * BKV + 2 * qd;
 #pragma unroll
-        for (int c = 0; c < 2; ++c) {
-          const int key = key0 + i * 8 + c;
-          const float a = (key <= p_lo && key >= lo_lo) ? s[i][c] * scale_log2e : -INFINITY;
-          const float b2 = (key <= p_hi && key >= lo_hi) ? s[i][2 + c] * scale_log2e : -INFINITY;
-          s[i][c] = a;
-          s[i][2 + c] = b2;
-          mx_lo = fmaxf(mx_lo, a);
-          mx_hi = fmaxf(mx_hi, b2);
+        for (int i = 0; i < BKV / 8; ++i) {
+#pragma unroll
+          for (int c = 0; c < 2; ++c) {
+            const int key = key0 + i * 8 + c;
+            if (!(key <= p_lo && key >= lo_lo)) s[i][c] = -INFINITY;
+            if (!(key <= p_hi && key >= lo_hi)) s[i][2 + c] = -INFINITY;
+            mx_lo = fmaxf(mx_lo, s[i][c]);
+            mx_hi = fmaxf(mx_hi, s[i][2 + c]);
+          }
         }
       }
       mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1));
       mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1));
       mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
-      const float mn_lo = fmaxf(m_lo, mx_lo), mn_hi = fmaxf(m_hi, mx_hi);
+      const float mn_lo = fmaxf(m_lo, mx_lo * scale_log2e), mn_hi = fmaxf(m_hi, mx_hi * scale_log2e);   // scale > 0
       const float base_lo = mn_lo == -INFINITY ? 0.f : mn_lo, base_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
       const float corr_lo = fast_exp2(m_lo - base_lo), corr_hi = fast_exp2(m_hi - base_hi);   // 2^-inf = 0
       m_lo = mn_lo;
@@ -198,9 +224,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
       float sum_lo = 0.f, sum_hi = 0.f;
       unsigned pa[BKV / 16][4];
 #pragma unroll
-      for (int i = 0; i < BKV / 8; ++i) {
-        const float e0 = fast_exp2(s[i][0] - base_lo), e1 = fast_exp2(s[i][1] - base_lo);
-        const float e2 = fast_exp2(s[i][2] - base_hi), e3 = fast_exp2(s[i][3] - base_hi);
+      for (int i = 0; i < BKV / 8; ++i) {   // exponent = score * scale * log2(e) - maximum, one fused multiply-add
+        const float e0 = fast_exp2(fmaf(s[i][0], scale_log2e, -base_lo)), e1 = fast_exp2(fmaf(s[i][1], scale_log2e, -base_lo));
+        const float e2 = fast_exp2(fmaf(s[i][2], scale_log2e, -base_hi)), e3 = fast_exp2(fmaf(s[i][3], scale_log2e, -base_hi));
         sum_lo += e0 + e1;
         sum_hi += e2 + e3;
         // accumulator tiles 2j and 2j+1 are the A fragment of the j-th 16-key step of P V
@@ -242,12 +268,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
   }
 }
 
-template <int DH>
+template <int DH, int WARPS>
 static int launch(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table, int max_pages,
                   int n_pages, int page, int Hq, int Hkv, int window, float scale, const void* k_pool,
                   const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream) {
   const size_t smem = (size_t)2 * 2 * BKV * (DH + 8) * sizeof(__nv_bfloat16);
-  auto kern = attention_prefill_kernel<DH>;
+  auto kern = attention_prefill_kernel<DH, WARPS>;
   static bool raised = false;
   if (smem > 48 * 1024 && !raised) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -263,18 +289,26 @@ static int launch(const void* q, int ldq, const int* tiles, int n_tiles, const i
 // bfloat16 only.  q: [*, >= Hq*Dh] at row stride ldq; out: [*, Hq*Dh] at row stride ldo (both strides even,
 // bases 4-byte aligned); tiles: int32 [n_tiles][4], see the kernel; pools [n_pages, Hkv, page, Dh].
 // Dh: a multiple of 16 up to 128; other sizes are refused (the generic kernel takes them).
-MLXB_EXPORT int mlxb_attention_prefill(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table,
-                                       int max_pages, int n_pages, int page, int Hq, int Hkv, int Dh, int window,
-                                       float scale, const void* k_pool, const void* v_pool, void* out, int ldo,
-                                       int* status, cudaStream_t stream) {
+// tile_rows: queries per tile, 64 or 128 (the caller cut the portions into tiles of at most that many).
+MLXB_EXPORT int mlxb_attention_prefill(const void* q, int ldq, const int* tiles, int n_tiles, int tile_rows,
+                                       const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
+                                       int Dh, int window, float scale, const void* k_pool, const void* v_pool,
+                                       void* out, int ldo, int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (page <= 0 || (page & (page - 1))) return mlxb_fail(MLXB_BAD_ARG, "attention (portions): page size %d", page);
   if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || Hq > 65535)
     return mlxb_fail(MLXB_BAD_ARG, "attention (portions): %d query heads over %d key/value heads", Hq, Hkv);
   if ((ldq & 1) || (ldo & 1) || ((uintptr_t)q & 3) || ((uintptr_t)out & 3) || ((uintptr_t)tiles & 15))
     return mlxb_fail(MLXB_BAD_ARG, "attention (portions): rows must be 4-byte aligned, the tile list 16-byte aligned");
-#define GO(D) case D: return launch<D>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, \
-                                       scale, k_pool, v_pool, out, ldo, status, stream)
+  if (tile_rows != 64 && tile_rows != 128)
+    return mlxb_fail(MLXB_BAD_ARG, "attention (portions): tiles of %d queries (64 or 128)", tile_rows);
+#define GO(D)                                                                                                         \
+  case D:                                                                                                             \
+    if (tile_rows == 128)                                                                                             \
+      return launch<D, 8>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,      \
+                          k_pool, v_pool, out, ldo, status, stream);                                                  \
+    return launch<D, 4>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale, k_pool, \
+                        v_pool, out, ldo, status, stream)
   switch (Dh) {
     GO(16); GO(32); GO(48); GO(64); GO(80); GO(96); GO(112); GO(128);
     default:

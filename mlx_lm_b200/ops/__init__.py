@@ -350,10 +350,12 @@ def attention_generic(q, positions, token_req, block_table, k_pool, v_pool, out,
           stream)
 
 
-_PRE_ARGS = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+_PRE_ARGS = [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
 
-PREFILL_TILE = 64   # queries per CTA of the tensor-core attention kernel for portions
+import os as _os
+
+PREFILL_TILE = int(_os.environ.get("MLXB_PREFILL_TILE", "64"))   # queries per CTA of the attention kernel for portions
 
 
 def attention_portions_supported(dtype, head_dim: int) -> bool:
@@ -361,7 +363,7 @@ def attention_portions_supported(dtype, head_dim: int) -> bool:
 
 
 def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out, n_heads: int, scale: float,
-                       window: int, status, stream) -> None:
+                       window: int, status, stream, tile_rows: int = 0) -> None:
     """Causal attention of prompt portions on tensor cores (bfloat16, csrc/attention_prefill.cu).
 
     ``tiles``: int32 device tensor ``[n_tiles, 4]``: first token row of the tile, queries in it (1..64),
@@ -370,8 +372,9 @@ def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out,
     _need(tiles, torch.int32, "attention_portions tiles")
     if tiles.numel() < 4 * n_tiles:
         raise KernelError(f"attention_portions: {tiles.numel()} integers for {n_tiles} tiles")
+    tile_rows = tile_rows or PREFILL_TILE
     _call("attention_prefill", "mlxb_attention_prefill", _PRE_ARGS, _p(q), _rows(q, "attention q"), _p(tiles), n_tiles,
-          _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
+          tile_rows, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
           _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream)
 
 

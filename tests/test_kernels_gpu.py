@@ -346,10 +346,11 @@ def make_tiles(lens, new, tile=64):
     return torch.tensor(tiles, dtype=torch.int32).reshape(-1)
 
 
+@pytest.mark.parametrize("tile", [64, 128])
 @pytest.mark.parametrize("Hq,Hkv,Dh,page,window", [(4, 4, 16, 16, 0), (3, 3, 32, 16, 0), (6, 2, 48, 32, 0),
                                                     (5, 1, 80, 64, 0), (2, 2, 128, 16, 40), (8, 4, 64, 16, 17),
                                                     (16, 16, 64, 16, 0), (2, 1, 96, 16, 100), (1, 1, 112, 32, 0)])
-def test_attention_portions(ops, Hq, Hkv, Dh, page, window):
+def test_attention_portions(ops, Hq, Hkv, Dh, page, window, tile):
     """The tensor-core kernel on the portions of a mixed step (single-token requests are left to the other
     kernel): portions that start at position 0, that continue long contexts, that end inside a tile, of two tokens."""
     lens, new = [0, 37, 130, 64, 3, 200, 0], [21, 1, 135, 2, 64, 65, 300]
@@ -358,10 +359,10 @@ def test_attention_portions(ops, Hq, Hkv, Dh, page, window):
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
     qw = Hq * Dh
     scale = Dh ** -0.5
-    tiles = make_tiles(lens, new).cuda()
+    tiles = make_tiles(lens, new, tile).cuda()
     out = torch.zeros(c["T"], qw, dtype=torch.bfloat16, device="cuda")
     ops.attention_portions(dev["qkv"][:, :qw], tiles, tiles.numel() // 4, dev["bt"], dev["k_pool"], dev["v_pool"], out,
-                           Hq, scale, window, status, stream())
+                           Hq, scale, window, status, stream(), tile_rows=tile)
     ref = R.attention(c["qkv"][:, :qw], c["positions"], c["token_req"], c["bt"], c["k_pool"], c["v_pool"], Hq, scale,
                       window)
     assert int(status.item()) == 0
@@ -391,7 +392,7 @@ def test_attention_portions_sees_each_key_once(ops):
     tiles = make_tiles([0], [n]).cuda()
     out = torch.zeros(n, Dh, dtype=torch.bfloat16, device="cuda")
     ops.attention_portions(dev["qkv"][:, :Dh], tiles, tiles.numel() // 4, dev["bt"], dev["k_pool"], dev["v_pool"], out,
-                           Hq, Dh ** -0.5, 0, status, stream())
+                           Hq, Dh ** -0.5, 0, status, stream(), tile_rows=64)
     got = out.float().cpu()
     for i in range(n):
         j = target[i]
