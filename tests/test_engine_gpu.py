@@ -409,3 +409,113 @@ def test_a_toy_mixer_with_state_can_be_registered_built_and_stepped(tmp_path):
     rows.append(eng2.step([StepEntry("o", other[5:6], []), StepEntry("c", toks[7:9], [0, 1])]).clone())
     rows.append(eng2.step([StepEntry("c", toks[9:40], list(range(31)))]).clone())
     assert rel(torch.cat(rows), whole) <= 5e-5
+
+
+# ----------------------------------------------------------------------------------------------
+# Two more toy parts, defined here: a rotary position encoding (rotates q and k before keys enter the
+# cache) and a feed-forward that routes each token to one of two experts.  Neither becomes a model of
+# anyone's; they show that the interfaces of positions and feed-forwards carry such parts.
+
+def test_toy_rotary_positions_and_routed_feed_forward(tmp_path):
+    from mlx_lm_b200.config import BaseModelArgs, register_architecture
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.parts import (MLP, Attention, FeedForward, Init, LayerNorm, Linear, ModelDescription, OutputHead,
+                                   PositionEncoding, PreNormBlock, TokenEmbedding)
+    from mlx_lm_b200.weights import load_model, write_random_model
+    from safetensors.torch import load_file
+
+    W, H, Dh, V = 32, 2, 16, 61
+
+    def rotate_rows(t, positions, n_heads):
+        """Rotate pairs (d, d + Dh/2) of every head by angle position * 10000^(-2d/Dh), in float32."""
+        T = t.shape[0]
+        x = t.float().reshape(T, n_heads, 2, Dh // 2)
+        inv = 10000.0 ** (-torch.arange(Dh // 2, device=t.device, dtype=torch.float32) * 2 / Dh)
+        ang = positions.float()[:, None, None] * inv
+        c, s = torch.cos(ang), torch.sin(ang)
+        a, b = x[:, :, 0], x[:, :, 1]
+        return torch.stack([a * c - b * s, a * s + b * c], dim=2).reshape(T, n_heads * Dh)
+
+    class Rotary(PositionEncoding):
+        max_positions = None
+
+        def rotate(self, ctx, q, k):          # in place on this step's queries and keys (views of one buffer)
+            q.copy_(rotate_rows(q, ctx.positions, H).to(q.dtype))
+            k.copy_(rotate_rows(k, ctx.positions, H).to(k.dtype))
+
+    class Routed(FeedForward):
+        """Each token goes to the expert whose router logit is larger (float32 router)."""
+
+        def __init__(self, name, width, inner):
+            self.router = Linear(f"{name}.router", width, 2, bias=False, init=Init(0.0, 0.5))
+            self.experts = [MLP(f"{name}.e{i}", width, inner, up_name="up", down_name="down", init=Init(0.0, 0.2))
+                            for i in range(2)]
+
+        def children(self):
+            return (self.router, *self.experts)
+
+        def forward(self, ctx, x, residual):
+            logits = ctx.ws.get("router", x.shape[0], 2, torch.float32)
+            self.router.forward(ctx, x, logits)
+            choice = logits.argmax(dim=-1)
+            for i, e in enumerate(self.experts):
+                idx = (choice == i).nonzero().flatten()
+                if idx.numel():
+                    residual[idx] = e.forward(ctx, x[idx].contiguous(), residual[idx].contiguous())
+            return residual
+
+    from dataclasses import dataclass
+
+    @dataclass
+    class Args(BaseModelArgs):
+        model_type: str
+        n_layer: int
+
+    def build(a):
+        emb = TokenEmbedding("emb", V, W, init=Init(0.0, 0.5))
+        rot = Rotary()
+        blocks = [PreNormBlock(LayerNorm(f"l{i}.n1", W, 1e-5), Attention(f"l{i}.mix", W, H, Dh, qkv_name="qkv", out_name="out",
+                                                                         position=rot, init=Init(0.0, 0.3)),
+                               LayerNorm(f"l{i}.n2", W, 1e-5), Routed(f"l{i}.ff", W, 48)) for i in range(a.n_layer)]
+        return ModelDescription("toy_rotary_routed", W, V, emb, None, blocks, LayerNorm("nf", W, 1e-5),
+                                OutputHead(V, W, tied_to=emb), args=a)
+
+    register_architecture("toy_rotary_routed", Args, build, replace=True)
+    write_random_model(str(tmp_path), dict(model_type="toy_rotary_routed", n_layer=2), seed=5)
+    w = {k: v.float() for k, v in load_file(str(tmp_path / "model.safetensors")).items()}
+
+    def plain_toy(tokens):
+        T = len(tokens)
+        pos = torch.arange(T)
+        x = w["emb.weight"][torch.tensor(tokens)]
+        for i in range(2):
+            h = plain.layer_norm(x, w[f"l{i}.n1.weight"], w[f"l{i}.n1.bias"], 1e-5)
+            qkv = h @ w[f"l{i}.mix.qkv.weight"].T + w[f"l{i}.mix.qkv.bias"]
+            q, k, v = qkv[:, :W], qkv[:, W:2 * W], qkv[:, 2 * W:]
+            q, k = rotate_rows(q, pos, H), rotate_rows(k, pos, H)
+            hs = lambda t: t.reshape(T, H, Dh).permute(1, 0, 2)
+            x = x + plain.causal_attention(hs(q), hs(k), hs(v)) @ w[f"l{i}.mix.out.weight"].T + w[f"l{i}.mix.out.bias"]
+            h = plain.layer_norm(x, w[f"l{i}.n2.weight"], w[f"l{i}.n2.bias"], 1e-5)
+            choice = (h @ w[f"l{i}.ff.router.weight"].T).argmax(-1)
+            y = torch.zeros_like(x)
+            for e in range(2):
+                p = f"l{i}.ff.e{e}."
+                ye = plain.gelu_new(h @ w[p + "up.weight"].T + w[p + "up.bias"]) @ w[p + "down.weight"].T + w[p + "down.bias"]
+                y = torch.where((choice == e)[:, None], ye, y)
+            x = x + y
+        return plain.layer_norm(x, w["nf.weight"], w["nf.bias"], 1e-5) @ w["emb.weight"].T
+
+    model, _ = load_model(str(tmp_path), dtype="float32")
+    assert model.description.max_positions is None
+    eng = Engine(model, page_size=16, n_pages=8, max_requests=2, max_len=64)
+    assert not eng.use_replay                  # these parts do host-side work: their steps are never re-issued from a recording
+    toks = random_tokens(50, V, 3)
+    ref = plain_toy(toks)
+    eng.add_request("a")
+    rows = [eng.step([StepEntry("a", toks[:19], list(range(19)))]).clone(),
+            eng.step([StepEntry("a", toks[19:21], [0, 1])]).clone(),
+            eng.step([StepEntry("a", toks[21:50], list(range(29)))]).clone()]
+    assert rel(torch.cat(rows), ref) <= 1e-4
+    # both experts were used by this sequence (else the routing is not exercised)
+    h0 = plain.layer_norm(w["emb.weight"][torch.tensor(toks)], w["l0.n1.weight"], w["l0.n1.bias"], 1e-5)
+    assert ref.shape == (50, V) and h0.shape == (50, W)
