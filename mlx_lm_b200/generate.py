@@ -42,12 +42,18 @@ DEFAULT_SEED = None
 
 # ---------------------------------------------------------------------- loading
 
-def load(path: str, tokenizer_config: Optional[dict] = None, model_config: Optional[dict] = None, lazy: bool = False,
-         return_config: bool = False, dtype: str = "bfloat16", device: str = "cuda"):
-    """Model folder -> ``(model, tokenizer)`` (or ``(model, tokenizer, config)``).
+def load(path: str, tokenizer_config: Optional[dict] = None, model_config: Optional[dict] = None,
+         adapter_path: Optional[str] = None, lazy: bool = False, return_config: bool = False,
+         revision: Optional[str] = None, trust_remote_code: bool = False, dtype: str = "bfloat16",
+         device: str = "cuda"):
+    """Model folder -> ``(model, tokenizer)`` (or ``(model, tokenizer, config)``), the signature of
+    mlx-lm's ``load`` (mlx_lm/utils.py:483-541).
 
-    Local folders only.  ``dtype`` is ``"bfloat16"`` (the serving path) or ``"float32"`` (everything
-    in true 32-bit).  ``tokenizer_config`` may carry ``eos_token_ids``."""
+    Local folders only (``revision`` and ``trust_remote_code`` are accepted and unused; ``adapter_path``
+    must be None: adapters are not built).  ``dtype`` is ``"bfloat16"`` (the serving path) or
+    ``"float32"`` (everything in true 32-bit).  ``tokenizer_config`` may carry ``eos_token_ids``."""
+    if adapter_path is not None:
+        raise ValueError("adapter_path: adapters are not offered by this engine")
     model, config = load_model(path, dtype=dtype, device=device, model_config=model_config)
     tokenizer = load_tokenizer(path, config, (tokenizer_config or {}).get("eos_token_ids"))
     return (model, tokenizer, config) if return_config else (model, tokenizer)
@@ -325,8 +331,14 @@ def str2bool(string: str) -> bool:
 
 def setup_arg_parser() -> argparse.ArgumentParser:
     p = argparse.ArgumentParser(prog="mlx_lm_b200.generate", description="LLM inference script")
-    p.add_argument("--model", type=str, required=True,
+    p.add_argument("--model", type=str, default=None,
                    help="The path to the local model directory (config.json, model.safetensors).")
+    p.add_argument("--random-weights", type=int, default=None, metavar="SEED",
+                   help="Instead of --model: make a model with seeded random weights from --config")
+    p.add_argument("--config", type=str, default=None, help="config.json for --random-weights")
+    p.add_argument("--prompt-tokens", type=str, default=None,
+                   help="The prompt as token ids separated by commas or blanks (instead of --prompt)")
+    p.add_argument("--fp32", action="store_true", help="Same as --dtype float32")
     p.add_argument("--extra-eos-token", type=str, default=(), nargs="+",
                    help="Add tokens in the list of eos tokens that stop generation.")
     p.add_argument("--prompt", "-p", default=DEFAULT_PROMPT,
@@ -358,7 +370,25 @@ def setup_arg_parser() -> argparse.ArgumentParser:
 
 
 def main(argv: Optional[Sequence[str]] = None) -> None:
-    args = setup_arg_parser().parse_args(argv)
+    parser = setup_arg_parser()
+    args = parser.parse_args(argv)
+    if args.fp32:
+        args.dtype = "float32"
+    if args.prompt_tokens is not None:
+        args.prompt = args.prompt_tokens
+    tmp = None
+    if args.random_weights is not None:
+        if args.config is None:
+            parser.error("--random-weights needs --config")
+        import tempfile
+
+        from .weights import write_random_model
+        tmp = tempfile.TemporaryDirectory()
+        with open(args.config) as f:
+            write_random_model(tmp.name, json.load(f), args.random_weights)
+        args.model = tmp.name
+    if args.model is None:
+        parser.error("--model (or --random-weights with --config) is required")
     model, tokenizer = load(args.model, dtype=args.dtype)
     for t in args.extra_eos_token:
         tokenizer.add_eos_token(t)

@@ -95,10 +95,16 @@ def place(spec: ParamSpec, t: torch.Tensor, dtype: torch.dtype, device) -> torch
 
 
 def build_model(config: dict, tensors: Dict[str, torch.Tensor], dtype: torch.dtype = torch.bfloat16,
-                device="cuda") -> Model:
-    arch = get_architecture(config)
-    args = arch.args_class.from_dict(config)
-    description = arch.build(args)
+                device="cuda", get_model_classes=None) -> Model:
+    """``get_model_classes(config) -> (builder, args class)`` replaces the registry lookup, as the parameter of
+    the same name does in mlx-lm's ``load_model`` (mlx_lm/utils.py:296-301)."""
+    if get_model_classes is not None:
+        build, args_class = get_model_classes(config)
+    else:
+        arch = get_architecture(config)
+        build, args_class = arch.build, arch.args_class
+    args = args_class.from_dict(config)
+    description = build(args)
     got = check_tensors(description, tensors)
     specs = {s.name: s for s in description.param_specs()}
     placed = {n: place(specs[n], t, dtype, device) for n, t in got.items()}
@@ -118,13 +124,13 @@ def parse_dtype(dtype) -> torch.dtype:
         raise ValueError(f"dtype {dtype!r}: 'bfloat16' or 'float32'") from None
 
 
-def load_model(model_path: str, dtype="bfloat16", device="cuda", model_config: Optional[dict] = None
-               ) -> Tuple[Model, dict]:
+def load_model(model_path: str, dtype="bfloat16", device="cuda", model_config: Optional[dict] = None,
+               get_model_classes=None) -> Tuple[Model, dict]:
     """Model folder -> (model on the device, config dict)."""
     config = load_config(model_path)
     if model_config:
         config.update(model_config)
-    model = build_model(config, read_safetensors(model_path), parse_dtype(dtype), device)
+    model = build_model(config, read_safetensors(model_path), parse_dtype(dtype), device, get_model_classes)
     return model, config
 
 

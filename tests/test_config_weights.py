@@ -119,6 +119,21 @@ def test_one_error_lists_missing_unexpected_and_shapes():
         assert word in msg, word
 
 
+def test_custom_get_model_classes():
+    """A caller may hand over its own (builder, args class) lookup, as mlx-lm's load_model allows
+    (tests/test_utils.py:109-136 there)."""
+    seen = []
+
+    def mine(config):
+        seen.append(config["model_type"])
+        return build, ModelArgs
+
+    t = random_tensors(build(ModelArgs.from_dict(CONFIG_A)), seed=0)
+    m = build_model(dict(CONFIG_A, model_type="something_else"), t, dtype=torch.float32, device="cpu",
+                    get_model_classes=mine)
+    assert seen == ["something_else"] and len(m.layers) == 2
+
+
 def test_no_safetensors(tmp_path):
     from mlx_lm_b200.weights import read_safetensors
     with pytest.raises(FileNotFoundError) as e:

@@ -233,6 +233,32 @@ def test_decode_as_a_cuda_graph_equals_the_eager_step(dtype, tmp_path):
     engine.check_status()
 
 
+def test_command_line(tmp_path):
+    """`python -m mlx_lm_b200 generate` with a model folder and with --random-weights/--config gives the tokens
+    the Python entry point gives."""
+    import json
+    import subprocess
+    import sys
+    from helpers import ROOT
+    from mlx_lm_b200 import generate, load
+    config = dict(CONFIG_A, ln_gain_std=0.3)
+    make_model_dir(str(tmp_path / "m"), config, 11)
+    model, tokenizer = load(str(tmp_path / "m"), dtype="float32")
+    want = generate(model, tokenizer, [5, 17, 3], max_tokens=12)
+    run = lambda *a: subprocess.run([sys.executable, "-m", "mlx_lm_b200", "generate", *a], cwd=ROOT, capture_output=True,
+                                    text=True, timeout=300)
+    r = run("--model", str(tmp_path / "m"), "--prompt", "5 17 3", "-m", "12", "--dtype", "float32", "--verbose", "F")
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.split() == want.split()
+    r = run("--model", str(tmp_path / "m"), "--prompt-tokens", "5,17,3", "--max-tokens", "12", "--fp32")
+    assert r.returncode == 0 and "Prompt: 3 tokens" in r.stdout and "Generation: 12 tokens" in r.stdout
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(config))
+    r = run("--random-weights", "11", "--config", str(cfg), "--prompt", "5 17 3", "-m", "12", "--temp", "0.7",
+            "--top-p", "0.9", "--seed", "4", "--verbose", "F")
+    assert r.returncode == 0 and len(r.stdout.split()) == 12
+
+
 def test_temperature_sampling_does_not_depend_on_batching(tmp_path):
     from mlx_lm_b200 import load
     from mlx_lm_b200.generate import BatchGenerator
