@@ -133,8 +133,7 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
   load_w(warp, wv);
   pdl_wait();
 
-  for (int kb = warp; kb < n_blocks; kb += STEP) {
-    uint4 av[UNROLL][MT][2];
+  auto load_a = [&](int kb, uint4 (&dst)[UNROLL][MT][2]) {
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u) {
       const int k = (kb + u * WARPS) * 32;
@@ -142,10 +141,20 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
 #pragma unroll
       for (int i = 0; i < MT; ++i)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) av[u][i][h] = (kin && aok[i][h]) ? ldg_cached(arow[i][h] + k) : zero;
+        for (int h = 0; h < 2; ++h) dst[u][i][h] = (kin && aok[i][h]) ? ldg_cached(arow[i][h] + k) : zero;
     }
-    uint4 wn[UNROLL][NW];
-    load_w(kb + STEP, wn);          // next iteration's weights are in flight while this one multiplies
+  };
+  // With more than 32 rows the activation fragments are fetched an iteration ahead as well (their L2
+  // latency would otherwise sit in every iteration); with few rows that only costs registers.
+  constexpr bool AHEAD = MT >= 4;
+  uint4 av[UNROLL][MT][2];
+  if (AHEAD) load_a(warp, av);
+
+  for (int kb = warp; kb < n_blocks; kb += STEP) {
+    uint4 wn[UNROLL][NW], an[UNROLL][MT][2];
+    if (!AHEAD) load_a(kb, av);
+    load_w(kb + STEP, wn);          // the next iteration's operands are in flight while this one multiplies
+    if (AHEAD) load_a(kb + STEP, an);
 #pragma unroll
     for (int u = 0; u < UNROLL; ++u)
 #pragma unroll
@@ -156,9 +165,16 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
           mma_bf16(acc[i][j], av[u][i][0].z, av[u][i][1].z, av[u][i][0].w, av[u][i][1].w, wv[u][j].z, wv[u][j].w);
         }
 #pragma unroll
-    for (int u = 0; u < UNROLL; ++u)
+    for (int u = 0; u < UNROLL; ++u) {
 #pragma unroll
       for (int j = 0; j < NW; ++j) wv[u][j] = wn[u][j];
+      if (AHEAD) {
+#pragma unroll
+        for (int i = 0; i < MT; ++i)
+#pragma unroll
+          for (int h = 0; h < 2; ++h) av[u][i][h] = an[u][i][h];
+      }
+    }
   }
 
   constexpr int PER = MT * NW * 4;
