@@ -31,6 +31,9 @@ sys.path.insert(0, ROOT)
 
 MEDIUM = dict(model_type="gpt2", n_layer=24, n_embd=1024, n_head=16, n_inner=4096, vocab_size=50257,
               n_positions=1024, layer_norm_epsilon=1e-5, activation_function="gelu_new")
+SIZES = {"medium": MEDIUM,
+         "large": dict(MEDIUM, n_layer=36, n_embd=1280, n_head=20, n_inner=5120),
+         "xl": dict(MEDIUM, n_layer=48, n_embd=1600, n_head=25, n_inner=6400)}
 PROMPT_LEN = 512
 CONTEXT = 1024
 
@@ -158,6 +161,41 @@ def decode_loop(engine, sampler_cls, model, batch, prompt_len, steps, warmup, vo
     return ms, launches, mean_ctx
 
 
+def mixed_workload(model, engine, vocab, args, n_requests=64, new_tokens=128, seed=3):
+    """Continuous batching: 64 requests, prompt lengths uniform in [16, 1024 - new_tokens], portions of 256 tokens
+    beside decoding requests, everything through the scheduler; wall-clock tokens per second."""
+    import torch
+
+    from mlx_lm_b200.generate import BatchGenerator
+
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(16, 1024 - new_tokens, (n_requests,), generator=g).tolist()
+    prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+
+    def run():
+        gen = BatchGenerator(model, max_tokens=new_tokens, engine=engine, completion_batch_size=64,
+                             prefill_batch_size=8, prefill_step_size=256, max_tokens_per_step=2048)
+        gen.insert(prompts)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        n_out = 0
+        while gen.scheduler.has_work():
+            n_out += len(gen.next()[1])
+        torch.cuda.synchronize()
+        dt = time.perf_counter() - t0
+        st = gen.scheduler.stats
+        return dt, n_out, st
+
+    run()                                   # warm-up: graphs, launch plans, workspaces
+    dt, n_out, st = run()
+    engine.check_status()
+    return {"only": "mixed", "size": args.size, "requests": n_requests, "prompt_tokens": sum(lens),
+            "generated_tokens": n_out, "seconds": round(dt, 4), "steps": st.steps,
+            "prompt_tokens_per_s": round(sum(lens) / dt, 1), "generated_tokens_per_s": round(n_out / dt, 1),
+            "tokens_per_s": round((sum(lens) + n_out) / dt, 1), "preemptions": st.preemptions,
+            "replayed_steps": engine.n_replayed}
+
+
 def run_ours(args):
     import torch
 
@@ -168,7 +206,7 @@ def run_ours(args):
     from mlx_lm_b200.weights import load_model, write_random_model
 
     pk = peaks()
-    cfg = dict(MEDIUM)
+    cfg = dict(SIZES[args.size])
     n_layer_full = cfg["n_layer"]
     cfg["n_layer"] = args.layers or n_layer_full
     B, K, W = args.batch, args.steps, args.warmup
@@ -183,6 +221,9 @@ def run_ours(args):
     engine = Engine(model, page_size=16, max_tokens=max_b * CONTEXT, max_requests=max_b)
     weight_bytes, kv_per_token, lin_flops = model_bytes_and_flops(cfg, cfg["n_layer"])
 
+    if args.only == "mixed":
+        print(json.dumps(mixed_workload(model, engine, vocab, args)))
+        return
     if args.only == "decode":
         ms, launches, mean_ctx = decode_loop(engine, DeviceSampler, model, B, PROMPT_LEN, K, W, vocab)
         print(json.dumps({"only": "decode", "batch": B, "ms_per_step": round(ms, 4), "launches_per_step": launches}))
@@ -252,11 +293,11 @@ def run_ours(args):
            "d2h_bytes_per_step": int(4 * (64 + B))}
 
     out = {
-        "metric": "decode tokens/s, GPT-2 medium, batch 8, 512-token prompts, context 1024",
+        "metric": f"decode tokens/s, GPT-2 {args.size}, batch {B}, 512-token prompts, context 1024",
         "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random prompt tokens",
-        "config": {"model": "gpt2-medium", "n_layer": cfg["n_layer"], "n_layer_of_configuration": n_layer_full,
+        "config": {"model": f"gpt2-{args.size}", "n_layer": cfg["n_layer"], "n_layer_of_configuration": n_layer_full,
                    "n_embd": cfg["n_embd"], "n_head": cfg["n_head"], "n_inner": cfg["n_inner"],
                    "vocab_size": vocab, "n_positions": cfg["n_positions"], "global_batch": B,
                    "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": 16, "parallelism": "single_gpu",
@@ -276,8 +317,11 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 24 (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill"],
-                    help="run just this part and print its figures (for profiling a short run)")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed"],
+                    help="run just this part and print its figures (decode / prefill: short runs for profiling; "
+                         "mixed: 64 requests with prompts of 16..1024 tokens through the scheduler, 256-token portions "
+                         "beside decoding requests)")
+    ap.add_argument("--size", default="medium", choices=sorted(SIZES), help="layer sizes: GPT-2 medium, large or XL")
     a = ap.parse_args()
     if a.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
