@@ -74,10 +74,21 @@ class DecodeGraph:
 
         # once eagerly on a side stream (loads libraries, sizes the workspace), then capture
         self.dev.copy_(self.host)
+        self.program = None
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
-            self._launch()
+            ops.start_recording()
+            try:
+                self._launch()
+            finally:
+                calls = ops.stop_recording()
+            if engine.use_program and engine.model.dtype == torch.bfloat16:
+                # the model's launches (all but the sampler's) as one persistent kernel, where each has a phase
+                from ..ops import program
+                self.program = program.compile_program(calls[:-1], dev)
+                if self.program is not None:
+                    self._launch()
         side.synchronize()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph, stream=side):
@@ -89,8 +100,12 @@ class DecodeGraph:
         ctx = self.ctx
         ctx.stream = ops.current_stream()
         before = ops.launch_count
-        logits = self.engine.model.run(ctx)
-        ops.sample(logits, self.params, self.tok, self.lp, ctx.stream)
+        if self.program is not None:
+            from ..ops import program
+            program.launch(self.program, self.engine.status, ctx.stream)
+        else:
+            self.logits = self.engine.model.run(ctx)
+        ops.sample(self.logits, self.params, self.tok, self.lp, ctx.stream)
         self._count = ops.launch_count - before
 
     def run(self, entries: Sequence[StepEntry], requests: Sequence, seed: int) -> Tuple[List[int], List[float]]:

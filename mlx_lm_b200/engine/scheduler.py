@@ -173,35 +173,48 @@ class Scheduler:
         self.stats.preemptions += 1
         self.waiting.appendleft(victim)
 
-    def _fits(self, planned: List[PlannedEntry], r: Request, n: int) -> bool:
-        wants = [(p.request.uid, p.n_tokens) for p in planned] + [(r.uid, n)]
-        return self.engine.cache.can_reserve(wants)
+    def _fits(self, taken: List[int], r: Request, n: int) -> Optional[List[int]]:
+        """The pages per group that n more tokens of r take, if the pools still have them beside the ``taken``
+        pages of the entries planned so far; else None."""
+        cache = self.engine.cache
+        need = cache.pages_needed(r.uid, n)
+        for t, c, g in zip(taken, need, cache.kv_groups):
+            if t + c > g.pool.n_free:
+                return None
+        return need
 
-    def _largest_portion(self, planned: List[PlannedEntry], r: Request, n: int) -> int:
+    def _largest_portion(self, taken: List[int], r: Request, n: int) -> int:
         """The longest portion <= n of r's tokens whose pages are free (0 if not even one token fits)."""
-        if self._fits(planned, r, n):
+        if self._fits(taken, r, n) is not None:
             return n
         lo, hi = 0, n - 1
         while lo < hi:
             mid = (lo + hi + 1) // 2
-            if self._fits(planned, r, mid):
+            if self._fits(taken, r, mid) is not None:
                 lo = mid
             else:
                 hi = mid - 1
         return lo
 
+    def _take(self, taken: List[int], r: Request, n: int) -> None:
+        for g, c in enumerate(self.engine.cache.pages_needed(r.uid, n)):
+            taken[g] += c
+
     def plan(self) -> List[PlannedEntry]:
         """Decide this step's entries; admits and preempts as a side effect."""
         while True:
             planned: List[PlannedEntry] = []
+            taken = [0] * len(self.engine.cache.kv_groups)      # pages the planned entries will take, per group
             budget = self.max_tokens_per_step
             starved: Optional[Request] = None
             # decoding requests first, oldest first
             for r in sorted(self.running, key=lambda r: r.admitted_at):
                 if r.remaining != 1 or budget <= 0:
                     continue
-                if self._fits(planned, r, 1):
+                need = self._fits(taken, r, 1)
+                if need is not None:
                     planned.append(PlannedEntry(r, 1, True))
+                    taken = [t + c for t, c in zip(taken, need)]
                     budget -= 1
                 else:
                     starved = r
@@ -214,9 +227,10 @@ class Scheduler:
             for r in sorted(self.running, key=lambda r: r.admitted_at):
                 if r.remaining <= 1 or budget <= 0:
                     continue
-                n = self._largest_portion(planned, r, min(r.remaining, self.prefill_step_size, budget))
+                n = self._largest_portion(taken, r, min(r.remaining, self.prefill_step_size, budget))
                 if n > 0:
                     planned.append(PlannedEntry(r, n, n == r.remaining))
+                    self._take(taken, r, n)
                     budget -= n
             # admissions
             while (self.waiting and budget > 0 and len(self.running) < self.max_requests
@@ -224,10 +238,11 @@ class Scheduler:
                    and self.engine.cache.has_free_slot()):
                 r = self.waiting[0]
                 self.engine.add_request(r.uid)
-                n = self._largest_portion(planned, r, min(r.remaining, self.prefill_step_size, budget))
+                n = self._largest_portion(taken, r, min(r.remaining, self.prefill_step_size, budget))
                 if n == 0:
                     self.engine.finish(r.uid)
                     break
+                self._take(taken, r, n)
                 self.waiting.popleft()
                 r.admitted_at = self._admissions
                 self._admissions += 1

@@ -18,6 +18,8 @@ into one pinned host buffer and reach the device in one copy.
 
 from __future__ import annotations
 
+import os
+
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -155,6 +157,15 @@ class Engine:
                 max_tokens = max_requests * self.max_len
             n_pages = (max_tokens + page_size - 1) // page_size
         libs = [n for n in d.kernel_libs() if model.dtype == torch.bfloat16 or n not in ops.BF16_ONLY_LIBS]
+        # Steps of single tokens can run as one persistent kernel over a table of phases where every launch of the
+        # step has a phase (ops/program.py): MLXB_DECODE_PROGRAM=1.  The default is the chain of kernels.
+        self.use_program = os.environ.get("MLXB_DECODE_PROGRAM", "0") == "1"
+        head_dims = {spec.head_dim for spec in d.cache_specs().values() if hasattr(spec, "head_dim")}
+        if self.use_program and model.dtype == torch.bfloat16 and len(head_dims) == 1:
+            tpk = 2
+            while tpk * 8 < next(iter(head_dims)):
+                tpk *= 2
+            libs.append(f"decode_program:MLXB_DP_TPK={tpk}")
         kernel_build.ensure_built(libs)      # compiled now, in parallel, if this is their first use
         self.cache = CacheManager(d.cache_specs(), page_size=page_size, n_pages=n_pages, max_requests=max_requests,
                                   max_len=self.max_len, dtype=model.dtype, device=model.device)
@@ -237,19 +248,39 @@ class Engine:
         self._validate(entries)
 
         ctx = StepContext(self)
-        R = len(entries)
-        T = sum(len(e.tokens) for e in entries)
-        L = sum(len(e.want) for e in entries)
+        TQ = ops.PREFILL_TILE
         W = mgr.table_width
         pad = lambda n: (n + 3) & ~3
+        n_real = len(entries)
+        L = sum(len(e.want) for e in entries)
         n_single = sum(1 for e in entries if len(e.tokens) == 1)
-        mixed = 0 < n_single < R
-        TQ = ops.PREFILL_TILE
+        n_portions = n_real - n_single
+        # Shapes are rounded up so that few distinct step shapes occur (each shape's launches are recorded once
+        # and re-issued): every portion gets a span of rows that is a multiple of the attention tile, and the
+        # number of single-token entries goes up to the next power of two (multiples of 64 above 64).  The extra
+        # rows carry request index -1: the cache write and the attention kernels skip them, the other kernels
+        # compute rows nobody reads.  Models with parts that loop over the step's entries on the host keep exact shapes.
+        rounding = self.use_replay
+        span = [len(e.tokens) if len(e.tokens) == 1 or not rounding else (len(e.tokens) + TQ - 1) // TQ * TQ
+                for e in entries]
+        n_fake = 0
+        if rounding and n_single:
+            bucket = 1
+            while bucket < n_single and bucket < 64:
+                bucket *= 2
+            if n_single > 64:
+                bucket = (n_single + 63) // 64 * 64
+            n_fake = bucket - n_single
+        R = n_real + n_fake
+        T = sum(span) + n_fake
+        n_single_rows = n_single + n_fake
+        mixed = 0 < n_single_rows < R
         n_tiles = sum((len(e.tokens) + TQ - 1) // TQ for e in entries if len(e.tokens) > 1)
-        off, sizes = {}, [("tokens", T), ("positions", T), ("token_req", T), ("logit_rows", L), ("slots", R),
+        L_rows = max(L, n_single_rows + n_portions) if rounding and L else L   # wanted rows first, then filler
+        off, sizes = {}, [("tokens", T), ("positions", T), ("token_req", T), ("logit_rows", L_rows), ("slots", R),
                           ("req_first_token", R + 1), ("req_first_position", R),
-                          ("single_rows", n_single if mixed else 0), ("portion_rows", T - n_single if mixed else 0),
-                          ("tiles", 4 * n_tiles)]
+                          ("single_rows", n_single_rows if mixed else 0),
+                          ("portion_rows", T - n_single_rows if mixed else 0), ("tiles", 4 * n_tiles)]
         sizes += [(f"table{g}", R * W) for g in range(len(mgr.kv_groups))]
         total = 0
         for name, n in sizes:
@@ -257,6 +288,9 @@ class Engine:
             total += pad(max(n, 1))
         hi, host, dev = self._int_buffers(total)
         h = host.numpy()
+        h[off["tokens"]: off["tokens"] + T] = 0
+        h[off["positions"]: off["positions"] + T] = 0
+        h[off["token_req"]: off["token_req"] + T] = -1
         t0 = 0
         rows: List[int] = []
         single_rows: List[int] = []
@@ -274,47 +308,58 @@ class Engine:
             h[off["req_first_position"] + r] = start
             rows.extend(t0 + w for w in e.want)
             if mixed:
-                (single_rows if n == 1 else portion_rows).extend(range(t0, t0 + n))
+                (single_rows if n == 1 else portion_rows).extend(range(t0, t0 + span[r]))
             if n > 1:
                 tiles.extend((t0 + a, min(TQ, n - a), r, start + a) for a in range(0, n, TQ))
             ctx.spans.append(RequestSpan(e.rid, slot, t0, n, start))
             ctx.max_q_len = max(ctx.max_q_len, n)
-            t0 += n
+            t0 += span[r]
+        for f in range(n_fake):                      # filler single-token entries
+            r = n_real + f
+            h[off["slots"] + r] = 0
+            h[off["req_first_token"] + r] = t0
+            h[off["req_first_position"] + r] = 0
+            if mixed:
+                single_rows.append(t0)
+            t0 += 1
         h[off["req_first_token"] + R] = T
-        if L:
-            h[off["logit_rows"]: off["logit_rows"] + L] = rows
+        if L_rows:
+            rows.extend([rows[0]] * (L_rows - L))
+            h[off["logit_rows"]: off["logit_rows"] + L_rows] = rows
         if mixed:
-            h[off["single_rows"]: off["single_rows"] + n_single] = single_rows
-            h[off["portion_rows"]: off["portion_rows"] + T - n_single] = portion_rows
+            h[off["single_rows"]: off["single_rows"] + n_single_rows] = single_rows
+            h[off["portion_rows"]: off["portion_rows"] + T - n_single_rows] = portion_rows
         if n_tiles:
             tiles.sort(key=lambda t: -(t[3] + t[1]))     # tiles with the most keys start first
             h[off["tiles"]: off["tiles"] + 4 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
         rids = [e.rid for e in entries]
         for g in range(len(mgr.kv_groups)):
             o = off[f"table{g}"]
-            mgr.block_table(g, rids, out=h[o: o + R * W].reshape(R, W))
+            h[o: o + R * W] = -1
+            mgr.block_table(g, rids, out=h[o: o + n_real * W].reshape(n_real, W))
         self._upload(hi, total)
 
         view = lambda name, n: dev[off[name]: off[name] + n]
         ctx.stream = ops.current_stream()
-        ctx.n_tokens, ctx.n_requests, ctx.n_logit_rows = T, R, L
+        ctx.n_tokens, ctx.n_requests, ctx.n_logit_rows = T, R, L_rows
         ctx.tokens, ctx.positions, ctx.token_req = view("tokens", T), view("positions", T), view("token_req", T)
-        ctx.logit_rows = view("logit_rows", L)
+        ctx.logit_rows = view("logit_rows", L_rows)
         ctx.req_first_token, ctx.req_first_position = view("req_first_token", R + 1), view("req_first_position", R)
         ctx._slots = view("slots", R)
-        ctx.n_single, ctx.n_portion = n_single, T - n_single
+        ctx.n_single, ctx.n_portion = n_single_rows, T - n_single_rows
         if mixed:
-            ctx.single_rows, ctx.portion_rows = view("single_rows", n_single), view("portion_rows", T - n_single)
+            ctx.single_rows = view("single_rows", n_single_rows)
+            ctx.portion_rows = view("portion_rows", T - n_single_rows)
         if n_tiles:
             ctx.portion_tiles, ctx.n_portion_tiles = view("tiles", 4 * n_tiles), n_tiles
         ctx._tables = [view(f"table{g}", R * W).view(R, W) for g in range(len(mgr.kv_groups))]
         try:
-            logits = self._run(ctx, (T, R, L, n_single, n_tiles, ctx.stream, dev.data_ptr()))
+            logits = self._run(ctx, (T, R, L_rows, n_single_rows, n_tiles, ctx.stream, dev.data_ptr()))
         finally:
             for e in entries:
                 mgr.commit(e.rid)
         self.n_steps += 1
-        return logits
+        return logits if logits is None or L_rows == L else logits[:L]
 
     def _run(self, ctx: "StepContext", shape: tuple) -> Optional[torch.Tensor]:
         if not self.use_replay:
@@ -362,6 +407,10 @@ class Engine:
         s = int(self.status.item())
         if s:
             self.status.zero_()
+        if s & ops.ST_WAIT_TIMEOUT:
+            for g in self._graphs.values():    # a persistent kernel that gave up left its barrier words behind
+                if g.program is not None:
+                    g.program.reset()
         return s
 
     def check_status(self) -> None:

@@ -3,7 +3,8 @@
 Each ``csrc/<name>.cu`` becomes ``<build dir>/<name>-<hash>.so`` with plain
 ``extern "C"`` launchers; the hash covers the source, the shared headers and
 the compiler flags, so an edited file is rebuilt and a stale library is never
-loaded.  Nothing is compiled until a library is first asked for, and a model
+loaded.  A name of the form ``file:MACRO=value`` is that source built with the
+macro defined (a variant for one head size, say), a library of its own.  Nothing is compiled until a library is first asked for, and a model
 asks only for the libraries its parts name (``ensure_built``), so a first
 call compiles what that model needs and nothing else.  While compiling, a
 line per library goes to stderr.
@@ -59,12 +60,19 @@ def _headers() -> List[str]:
     return sorted(os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".cuh", ".h")))
 
 
+def _split(name: str):
+    """``"file"`` or ``"file:MACRO=value,MACRO=value"``: a source and the macros of one of its variants."""
+    src, _, defs = name.partition(":")
+    return src, [d for d in defs.split(",") if d]
+
+
 def _digest(name: str) -> str:
+    src, defines = _split(name)
     h = hashlib.sha1()
-    for path in [os.path.join(CSRC, name + ".cu")] + _headers():
+    for path in [os.path.join(CSRC, src + ".cu")] + _headers():
         with open(path, "rb") as f:
             h.update(f.read())
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + defines).encode())
     return h.hexdigest()[:12]
 
 
@@ -91,34 +99,39 @@ def build_dir() -> str:
 
 
 def lib_path(name: str) -> str:
-    return os.path.join(build_dir(), f"{name}-{_digest(name)}.so")
+    src, defines = _split(name)
+    stem = src + "".join("." + d.replace("=", "_") for d in defines)
+    return os.path.join(build_dir(), f"{stem}-{_digest(name)}.so")
 
 
 def _compile(name: str) -> str:
     out = lib_path(name)
     if os.path.exists(out):
         return out
-    src = os.path.join(CSRC, name + ".cu")
+    stem, defines = _split(name)
+    src = os.path.join(CSRC, stem + ".cu")
     if not os.path.exists(src):
         raise KernelBuildError(f"no kernel source {src}")
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [_nvcc()] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, src, "-lcuda"]
+    cmd = [_nvcc()] + NVCC_FLAGS + ["-D" + d for d in defines] + ["-I", CSRC, "-o", tmp, src, "-lcuda"]
     t0 = time.time()
-    print(f"[mlx_lm_b200] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
+    label = stem + ".cu" + (" with " + ", ".join(defines) if defines else "")
+    print(f"[mlx_lm_b200] compiling {label} for sm_100a ...", file=sys.stderr, flush=True)
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     proc = subprocess.run(cmd, capture_output=True, text=True, env=env)
     if proc.returncode != 0:
-        raise KernelBuildError(f"nvcc failed on {name}.cu:\n{proc.stdout}\n{proc.stderr}")
+        raise KernelBuildError(f"nvcc failed on {label}:\n{proc.stdout}\n{proc.stderr}")
     os.replace(tmp, out)
     d = os.path.dirname(out)
+    prefix = os.path.basename(out).rsplit("-", 1)[0] + "-"
     for f in os.listdir(d):  # drop libraries of older versions of this source
-        if f.startswith(name + "-") and f.endswith(".so") and os.path.join(d, f) != out:
+        if f.startswith(prefix) and f.endswith(".so") and os.path.join(d, f) != out:
             try:
                 os.unlink(os.path.join(d, f))
             except OSError:
                 pass
-    print(f"[mlx_lm_b200] compiled {name}.cu in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
+    print(f"[mlx_lm_b200] compiled {label} in {time.time() - t0:.1f} s", file=sys.stderr, flush=True)
     return out
 
 
