@@ -41,6 +41,8 @@ __global__ void kv_write_kernel(const T* __restrict__ k_src, const T* __restrict
                                 int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
+  k_src = after_wait(k_src);
+  v_src = after_wait(v_src);
   const int t = blockIdx.x;
   const int p = positions[t];
   const int r = token_req[t];
@@ -98,6 +100,9 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, const int* __restrict
   extern __shared__ float sq[];  // [warps][Dh]
   pdl_trigger();
   pdl_wait();
+  q = after_wait(q);
+  k_pool = after_wait(k_pool);
+  v_pool = after_wait(v_pool);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int w = blockIdx.x * (blockDim.x >> 5) + warp;
   if (w >= n_tokens * Hq) return;
@@ -245,6 +250,8 @@ template <typename T> struct Raw8;
 template <> struct Raw8<__nv_bfloat16> {
   uint4 u;
   __device__ __forceinline__ void load(const __nv_bfloat16* p) { u = *reinterpret_cast<const uint4*>(p); }
+  // past L1: for a row whose cache line may have been fetched before its last writer finished
+  __device__ __forceinline__ void load_fresh(const __nv_bfloat16* p) { u = __ldcg(reinterpret_cast<const uint4*>(p)); }
   __device__ __forceinline__ void zero() { u = make_uint4(0u, 0u, 0u, 0u); }
   __device__ __forceinline__ void get(float (&v)[8]) const {
     const unsigned w[4] = {u.x, u.y, u.z, u.w};
@@ -260,6 +267,10 @@ template <> struct Raw8<float> {
   __device__ __forceinline__ void load(const float* p) {
     a = *reinterpret_cast<const float4*>(p);
     b = *reinterpret_cast<const float4*>(p + 4);
+  }
+  __device__ __forceinline__ void load_fresh(const float* p) {
+    a = __ldcg(reinterpret_cast<const float4*>(p));
+    b = __ldcg(reinterpret_cast<const float4*>(p + 4));
   }
   __device__ __forceinline__ void zero() { a = make_float4(0.f, 0.f, 0.f, 0.f); b = a; }
   __device__ __forceinline__ void get(float (&v)[8]) const {
@@ -282,18 +293,17 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
   constexpr int U = sizeof(T) == 2 ? 8 : 4;   // keys in flight per thread
   extern __shared__ float sm[];               // per warp: m | l | o[Dh]
   __shared__ int s_last;
+  // The kernel before this one wrote the queries and, into the pages, the key and value of each row's own
+  // position.  Everything else this kernel reads is older: the step's inputs (requests, positions, block
+  // tables) and the keys and values of earlier positions.  So the chain of dependent loads (request ->
+  // page ids -> first batch of keys and values) goes out before the wait for that kernel, and only the
+  // query and the row's own key and value are fetched after it.
   pdl_trigger();
-  pdl_wait();
   const int c = blockIdx.x, h = blockIdx.y, ri = blockIdx.z;
   const int t = rows ? rows[ri] : ri;
   const int grp = threadIdx.x / TPK, j = threadIdx.x % TPK;
   const int d0 = 8 * j;
   const bool active = d0 < Dh;
-  // the query does not depend on the request's bookkeeping: its load goes out with theirs
-  float qv[8];
-#pragma unroll
-  for (int i = 0; i < 8; ++i) qv[i] = 0.f;
-  if (active) load8<T>(q + (size_t)t * ldq + h * Dh + d0, qv);
   const int r = token_req[t];
   const int p = positions[t];
   if (r < 0) return;
@@ -304,8 +314,6 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
   const int hk = h / (Hq / Hkv);
   const int* bt = block_table + (size_t)r * max_pages;
   const int shift = __ffs(page) - 1;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) qv[i] *= scale;
 
   float m = -INFINITY, l = 0.f, o[8];
 #pragma unroll
@@ -320,10 +328,12 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
     const int lp = key >> shift;
     pg_next[u] = (key < k_end && lp < max_pages) ? bt[lp] : -1;
   }
-  for (int it = 0; it < iters; ++it) {
-    // page ids were fetched one batch ahead; now all key and value rows of the batch, then the arithmetic
+  Raw8<T> kr[U], vr[U];
+  bool ok[U];
+  // All key and value rows of batch `it`; the page ids were fetched one batch ahead.  With `early`, the
+  // row's own position is left for fetch_own(): it is not in memory yet.
+  auto fetch = [&](int it, bool early) {
     int pg[U];
-    bool ok[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int key = k_begin + (it * U + u) * GROUPS + grp;
@@ -332,7 +342,6 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
       const int nkey = key + U * GROUPS, nlp = nkey >> shift;
       pg_next[u] = (nkey < k_end && nlp < max_pages) ? bt[nlp] : -1;
     }
-    Raw8<T> kr[U], vr[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {
       const int key = k_begin + (it * U + u) * GROUPS + grp;
@@ -340,7 +349,7 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
         if (j == 0) atomicOr(status, pg[u] < 0 ? MLXB_ST_POSITION_RANGE : MLXB_ST_PAGE_RANGE);
         ok[u] = false;
       }
-      if (ok[u] && active) {
+      if (ok[u] && active && !(early && key == p)) {
         const size_t off = (((size_t)pg[u] * Hkv + hk) * page + (key & (page - 1))) * Dh + d0;
         kr[u].load(k_pool + off);
         vr[u].load(v_pool + off);
@@ -349,6 +358,36 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
         vr[u].zero();
       }
     }
+  };
+  fetch(0, true);
+  int own_pg = -1;   // page of the row's own position, if it belongs to this chunk's first batch
+  if (p >= k_begin && p < k_end && p - k_begin < GROUPS * U) {
+    const int lp = p >> shift;
+    own_pg = lp < max_pages ? bt[lp] : -1;
+  }
+  pdl_wait();
+  const T* q_now = after_wait(q);
+  const T* k_now = after_wait(k_pool);
+  const T* v_now = after_wait(v_pool);
+  float qv[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) qv[i] = 0.f;
+  if (active) load8<T>(q_now + (size_t)t * ldq + h * Dh + d0, qv);
+  if (own_pg >= 0 && own_pg < n_pages && active && (p - k_begin) % GROUPS == grp) {
+    const int u_own = (p - k_begin) / GROUPS;
+    const size_t off = (((size_t)own_pg * Hkv + hk) * page + (p & (page - 1))) * Dh + d0;
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (u == u_own) {
+        kr[u].load_fresh(k_now + off);
+        vr[u].load_fresh(v_now + off);
+      }
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) qv[i] *= scale;
+
+  for (int it = 0; it < iters; ++it) {
+    if (it > 0) fetch(it, false);   // these rows are older than this step, whichever pointer they are read through
     float sc[U];
 #pragma unroll
     for (int u = 0; u < U; ++u) {

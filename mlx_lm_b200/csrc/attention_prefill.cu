@@ -80,6 +80,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
 
   pdl_trigger();
   pdl_wait();
+  q = after_wait(q);
+  k_pool = after_wait(k_pool);
+  v_pool = after_wait(v_pool);
   const int4 tile = tiles[blockIdx.x];
   const int row0 = tile.x, n_rows = tile.y, req = tile.z, pos0 = tile.w;
   const int h = blockIdx.y, hk = h / (Hq / Hkv);

@@ -61,6 +61,15 @@ static inline int mlxb_check_launch(const char* what) {
 // attribute off (every kernel then starts after its predecessor has finished, as usual).
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+// A pointer to memory the predecessor writes, as seen after pdl_wait().  A `const __restrict__` parameter
+// promises the compiler that nobody writes the memory while the kernel runs, which would allow it to move
+// a load through such a pointer up into the code before the wait; passing the pointer through this (empty)
+// statement after the wait ties every load through the result to a point after it.
+template <typename T>
+__device__ __forceinline__ T* after_wait(T* p) {
+  asm volatile("" : "+l"(p)::"memory");
+  return p;
+}
 
 static inline bool mlxb_pdl_enabled() {
   static int on = -1;

@@ -25,6 +25,8 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, const float* 
   __shared__ float sW[BK][BN + 4];
   pdl_trigger();
   pdl_wait();
+  A = after_wait(A);
+  residual = after_wait(residual);
   const int tid = threadIdx.x;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
   const int tx = tid & 15, ty = tid >> 4;  // 16 x 16 threads; thread owns rows ty*4.., cols tx*4..

@@ -64,6 +64,31 @@ struct KvScatter {
   int max_pages, n_pages, page, Hkv, Dh, q_width;
 };
 
+// Where the key or value element of output column n (>= q_width) of token m lives in the pages; null for a
+// padding row or an index out of range (which sets the status bit).
+__device__ __forceinline__ __nv_bfloat16* kv_slot(const KvScatter& kv, int m, int n) {
+  const int r = kv.token_req[m];
+  if (r < 0) return nullptr;
+  const int pos = kv.positions[m];
+  const int lp = pos / kv.page;
+  const int pg = (pos >= 0 && lp < kv.max_pages) ? kv.block_table[(size_t)r * kv.max_pages + lp] : -2;
+  if (pg == -2) {
+    atomicOr(kv.status, MLXB_ST_POSITION_RANGE);
+    return nullptr;
+  }
+  if (pg >= kv.n_pages) {
+    atomicOr(kv.status, MLXB_ST_PAGE_RANGE);
+    return nullptr;
+  }
+  if (pg < 0) return nullptr;
+  const int kvw = kv.Hkv * kv.Dh;
+  int c2 = n - kv.q_width;
+  __nv_bfloat16* pool = kv.k_pool;
+  if (c2 >= kvw) { c2 -= kvw; pool = kv.v_pool; }
+  const int hh = c2 / kv.Dh, d = c2 - hh * kv.Dh;
+  return pool + (((size_t)pg * kv.Hkv + hh) * kv.page + (pos % kv.page)) * kv.Dh + d;
+}
+
 // MT: 16-row token tiles (M <= 16*MT); NW: 8-row weight tiles per CTA; WARPS: warps that share the K blocks.
 template <int MT, int NW, int WARPS, typename TO, int EPI, bool SCATTER>
 __global__ void __launch_bounds__(WARPS * 32)
@@ -117,7 +142,7 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     }
   };
 
-  // Before waiting for the previous kernel: everything that touches only W.
+  // Before waiting for the previous kernel: everything that touches only W and the step's inputs.
   pdl_trigger();
   {
     const int lines_per_row = (K * 2 + 127) >> 7;
@@ -131,7 +156,50 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
   }
   uint4 wv[UNROLL][NW];
   load_w(warp, wv);
+  // What the epilogue needs besides the sums comes from memory too (bias; for the fused cache write the
+  // token's request, position and page: three loads that depend on one another).  With few elements per
+  // thread these are fetched here, where their latency hides behind the weight stream, instead of after
+  // the reduction.  None of it is written by a kernel: bias is a weight, the rest are the step's inputs.
+  constexpr int PER = MT * NW * 4;
+  constexpr int EPT = (PER + WARPS - 1) / WARPS;     // output elements per thread
+  constexpr bool HOIST = EPT <= 2;
+  float e_bias[HOIST ? EPT : 1];
+  __nv_bfloat16* e_dst[HOIST ? EPT : 1];             // where a key or value element goes (null: nowhere)
+  float e_res[HOIST ? EPT : 1];
+  auto elem_mn = [&](int e, int& m, int& n) {
+    const int idx = e >> 5, ln = e & 31;
+    const int c = idx & 3, j = (idx >> 2) % NW, i = (idx >> 2) / NW;
+    m = i * 16 + (ln >> 2) + ((c & 2) ? 8 : 0);
+    n = n0 + j * 8 + 2 * (ln & 3) + (c & 1);
+  };
+  if (HOIST) {
+#pragma unroll
+    for (int x = 0; x < EPT; ++x) {
+      const int e = threadIdx.x + x * WARPS * 32;
+      int m, n;
+      elem_mn(e, m, n);
+      const bool in = e < PER * 32 && m < M && n < N;
+      e_bias[x] = (in && bias) ? bias[n] : 0.f;
+      e_dst[x] = nullptr;
+      if (SCATTER && in && n >= kv.q_width) e_dst[x] = kv_slot(kv, m, n);
+    }
+  }
   pdl_wait();
+  A = after_wait(A);
+  residual = after_wait(residual);
+#pragma unroll
+  for (int i = 0; i < MT; ++i)
+#pragma unroll
+    for (int h = 0; h < 2; ++h) arow[i][h] = after_wait(arow[i][h]);
+  if (HOIST) {
+#pragma unroll
+    for (int x = 0; x < EPT; ++x) {
+      const int e = threadIdx.x + x * WARPS * 32;
+      int m, n;
+      elem_mn(e, m, n);
+      e_res[x] = (residual && e < PER * 32 && m < M && n < N) ? __bfloat162float(residual[(size_t)m * ldc + n]) : 0.f;
+    }
+  }
 
   auto load_a = [&](int kb, uint4 (&dst)[UNROLL][MT][2]) {
 #pragma unroll
@@ -177,7 +245,6 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     }
   }
 
-  constexpr int PER = MT * NW * 4;
 #pragma unroll
   for (int i = 0; i < MT; ++i)
 #pragma unroll
@@ -185,39 +252,44 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
 #pragma unroll
       for (int c = 0; c < 4; ++c) part[(warp * PER + (i * NW + j) * 4 + c) * 32 + lane] = acc[i][j][c];
   __syncthreads();
-  for (int e = threadIdx.x; e < PER * 32; e += WARPS * 32) {
-    float v = 0.f;
+  if (HOIST) {
 #pragma unroll
-    for (int w = 0; w < WARPS; ++w) v += part[w * PER * 32 + e];
-    const int idx = e >> 5, ln = e & 31;
-    const int c = idx & 3, j = (idx >> 2) % NW, i = (idx >> 2) / NW;
-    const int m = i * 16 + (ln >> 2) + ((c & 2) ? 8 : 0);
-    const int n = n0 + j * 8 + 2 * (ln & 3) + (c & 1);
-    if (m < M && n < N) {
-      if (bias) v += bias[n];
-      if (EPI == EPI_GELU_NEW) v = gelu_new_fast(v);
-      if (residual) v += __bfloat162float(residual[(size_t)m * ldc + n]);
-      if (SCATTER && n >= kv.q_width) {
-        const int r = kv.token_req[m];
-        if (r >= 0) {
-          const int pos = kv.positions[m];
-          const int lp = pos / kv.page;
-          const int pg = (pos >= 0 && lp < kv.max_pages) ? kv.block_table[(size_t)r * kv.max_pages + lp] : -2;
-          if (pg == -2) {
-            atomicOr(kv.status, MLXB_ST_POSITION_RANGE);
-          } else if (pg >= kv.n_pages) {
-            atomicOr(kv.status, MLXB_ST_PAGE_RANGE);
-          } else if (pg >= 0) {
-            const int kvw = kv.Hkv * kv.Dh;
-            int c2 = n - kv.q_width;
-            __nv_bfloat16* pool = kv.k_pool;
-            if (c2 >= kvw) { c2 -= kvw; pool = kv.v_pool; }
-            const int hh = c2 / kv.Dh, d = c2 - hh * kv.Dh;
-            pool[(((size_t)pg * kv.Hkv + hh) * kv.page + (pos % kv.page)) * kv.Dh + d] = __float2bfloat16_rn(v);
-          }
+    for (int x = 0; x < EPT; ++x) {
+      const int e = threadIdx.x + x * WARPS * 32;
+      if (e >= PER * 32) break;
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) v += part[w * PER * 32 + e];
+      int m, n;
+      elem_mn(e, m, n);
+      if (m < M && n < N) {
+        v += e_bias[x];
+        if (EPI == EPI_GELU_NEW) v = gelu_new_fast(v);
+        v += e_res[x];
+        if (SCATTER && n >= kv.q_width) {
+          if (e_dst[x]) *e_dst[x] = __float2bfloat16_rn(v);
+        } else {
+          C[(size_t)m * ldc + n] = from_f<TO>(v);
         }
-      } else {
-        C[(size_t)m * ldc + n] = from_f<TO>(v);
+      }
+    }
+  } else {
+    for (int e = threadIdx.x; e < PER * 32; e += WARPS * 32) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < WARPS; ++w) v += part[w * PER * 32 + e];
+      int m, n;
+      elem_mn(e, m, n);
+      if (m < M && n < N) {
+        if (bias) v += bias[n];
+        if (EPI == EPI_GELU_NEW) v = gelu_new_fast(v);
+        if (residual) v += __bfloat162float(residual[(size_t)m * ldc + n]);
+        if (SCATTER && n >= kv.q_width) {
+          __nv_bfloat16* dst = kv_slot(kv, m, n);
+          if (dst) *dst = __float2bfloat16_rn(v);
+        } else {
+          C[(size_t)m * ldc + n] = from_f<TO>(v);
+        }
       }
     }
   }

@@ -229,6 +229,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   volatile int* abort_flag = &sm.abort_flag;
   pdl_trigger();
   pdl_wait();   // A (and the residual) come from the previous kernel
+  residual = after_wait(residual);
 
   if (warp == 0) {
     if (lane == 0) {

@@ -20,7 +20,7 @@ __global__ void layernorm_kernel(const T* __restrict__ x, const int* __restrict_
   pdl_trigger();
   pdl_wait();
   const int r = blockIdx.x;
-  const T* xi = x + (size_t)(rows ? rows[r] : r) * D;
+  const T* xi = after_wait(x) + (size_t)(rows ? rows[r] : r) * D;
   float s = 0.f;
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float v = to_f(xi[d]);
@@ -51,11 +51,22 @@ __global__ void __launch_bounds__(256)
 layernorm_warp_kernel(const T* __restrict__ x, const int* __restrict__ rows, const float* __restrict__ gain,
                       const float* __restrict__ bias, T* __restrict__ y, int R, int D, float eps) {
   pdl_trigger();
-  pdl_wait();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int r = blockIdx.x * 8 + warp;
   if (r >= R) return;
-  const T* xi = x + (size_t)(rows ? rows[r] : r) * D;
+  // gain and bias are weights: their lines are asked for before the wait for the kernel that writes x,
+  // so that the loads after the statistics find them in L1
+#pragma unroll
+  for (int c = 0; c < NCH; ++c) {
+    const int d = (c * 32 + lane) * 8;
+    if (d < D) {
+      asm volatile("prefetch.global.L1 [%0];" ::"l"(gain + d));
+      if (bias) asm volatile("prefetch.global.L1 [%0];" ::"l"(bias + d));
+    }
+  }
+  const int src_row = rows ? rows[r] : r;      // a step input, not written by a kernel
+  pdl_wait();
+  const T* xi = after_wait(x) + (size_t)src_row * D;
   float v[NCH][8];
   float s = 0.f;
 #pragma unroll

@@ -128,6 +128,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleParam
   __shared__ int redi[40];
   pdl_trigger();
   pdl_wait();
+  logits = after_wait(logits);
   const int row = blockIdx.x;
   const float* lg = logits + (size_t)row * ld;
   const SampleParams P = params[row];
