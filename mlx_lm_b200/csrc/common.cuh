@@ -124,6 +124,93 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- eight bfloat16 values in one 16-byte register group
+__device__ __forceinline__ void unpack8(const uint4& u, float (&v)[8]) {
+  const unsigned w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    v[2 * i] = __uint_as_float(w[i] << 16);
+    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+  }
+}
+__device__ __forceinline__ uint4 pack8(const float (&o)[8]) {
+  uint4 u;
+  unsigned* w = reinterpret_cast<unsigned*>(&u);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const __nv_bfloat162 pr = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
+    w[i] = *reinterpret_cast<const unsigned*>(&pr);
+  }
+  return u;
+}
+
+// LayerNorm of eight consecutive elements d..d+7 of a row with known statistics, rounded to bfloat16:
+// (x - mean) * rstd * gain + bias, the arithmetic of norm.cu.
+__device__ __forceinline__ uint4 normalise8(const uint4& raw, float mean, float rstd, const float* gain,
+                                            const float* bias, int d) {
+  float v[8], o[8], gn[8];
+  unpack8(raw, v);
+  *reinterpret_cast<float4*>(gn) = __ldg(reinterpret_cast<const float4*>(gain + d));
+  *reinterpret_cast<float4*>(gn + 4) = __ldg(reinterpret_cast<const float4*>(gain + d + 4));
+#pragma unroll
+  for (int i = 0; i < 8; ++i) o[i] = (v[i] - mean) * rstd * gn[i];
+  if (bias) {
+    float bs[8];
+    *reinterpret_cast<float4*>(bs) = __ldg(reinterpret_cast<const float4*>(bias + d));
+    *reinterpret_cast<float4*>(bs + 4) = __ldg(reinterpret_cast<const float4*>(bias + d + 4));
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] += bs[i];
+  }
+  return pack8(o);
+}
+
+// Mean and 1/sqrt(var + eps) of one bfloat16 row of width D (a multiple of 8), by one warp, with the order
+// of additions of the one-warp-per-row kernel of norm.cu.  `load` fetches 16 bytes.  Rows up to 2048 wide
+// stay in registers between the two passes; wider rows are read twice.
+template <typename Load>
+__device__ __forceinline__ void row_stats_bf16(const __nv_bfloat16* xr, int D, float eps, int lane, float& mean,
+                                               float& rstd, Load load) {
+  constexpr int KEEP = 8;
+  uint4 keep[KEEP];
+  float s = 0.f;
+#pragma unroll
+  for (int c = 0; c < KEEP; ++c) {
+    const int d = (c * 32 + lane) * 8;
+    keep[c] = d < D ? load(xr + d) : make_uint4(0u, 0u, 0u, 0u);
+  }
+#pragma unroll
+  for (int c = 0; c < KEEP; ++c) {
+    float v[8];
+    unpack8(keep[c], v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += v[i];
+  }
+  for (int d = (KEEP * 32 + lane) * 8; d < D; d += 256) {
+    float v[8];
+    unpack8(load(xr + d), v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += v[i];
+  }
+  mean = warp_sum(s) / (float)D;
+  float q = 0.f;
+#pragma unroll
+  for (int c = 0; c < KEEP; ++c) {
+    if ((c * 32 + lane) * 8 < D) {
+      float v[8];
+      unpack8(keep[c], v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) { const float t = v[i] - mean; q += t * t; }
+    }
+  }
+  for (int d = (KEEP * 32 + lane) * 8; d < D; d += 256) {
+    float v[8];
+    unpack8(load(xr + d), v);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) { const float t = v[i] - mean; q += t * t; }
+  }
+  rstd = rsqrtf(warp_sum(q) / (float)D + eps);
+}
+
 // Block-wide sum; every thread gets the result.  `red` is shared memory of at
 // least 33 floats.  The order of additions is fixed by the block size alone.
 __device__ __forceinline__ float block_sum(float v, float* red) {

@@ -109,24 +109,6 @@ __device__ __forceinline__ unsigned ld_acquire_u32(const unsigned* p) {
 __device__ __forceinline__ void red_release_inc(unsigned* p) {
   asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p) : "memory");
 }
-__device__ __forceinline__ void unpack8(const uint4& u, float (&v)[8]) {
-  const unsigned w[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    v[2 * i] = __uint_as_float(w[i] << 16);
-    v[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
-  }
-}
-__device__ __forceinline__ uint4 pack8(const float (&o)[8]) {
-  uint4 u;
-  unsigned* w = reinterpret_cast<unsigned*>(&u);
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const __nv_bfloat162 pr = __floats2bfloat162_rn(o[2 * i], o[2 * i + 1]);
-    w[i] = *reinterpret_cast<const unsigned*>(&pr);
-  }
-  return u;
-}
 __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1, unsigned a2, unsigned a3,
                                          unsigned b0, unsigned b1) {
   asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
@@ -179,68 +161,9 @@ __device__ __forceinline__ void prefetch_share(const void* p, long long bytes) {
 }
 
 // ------------------------------------------------------------------------------------------ norm statistics
-// Mean and 1/sqrt(var + eps) of one bfloat16 row of width D (a multiple of 8), by one warp.  Same
-// order of additions as the one-warp-per-row kernel of norm.cu.  Rows up to 2048 wide stay in registers
-// between the two passes; wider rows are read twice.
 __device__ __forceinline__ void row_stats(const __nv_bfloat16* xr, int D, float eps, int lane, float& mean,
                                           float& rstd) {
-  constexpr int KEEP = 8;
-  uint4 keep[KEEP];
-  float s = 0.f;
-#pragma unroll
-  for (int c = 0; c < KEEP; ++c) {
-    const int d = (c * 32 + lane) * 8;
-    keep[c] = d < D ? ld_act(xr + d) : make_uint4(0u, 0u, 0u, 0u);
-  }
-#pragma unroll
-  for (int c = 0; c < KEEP; ++c) {
-    float v[8];
-    unpack8(keep[c], v);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) s += v[i];
-  }
-  for (int d = (KEEP * 32 + lane) * 8; d < D; d += 256) {
-    float v[8];
-    unpack8(ld_act(xr + d), v);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) s += v[i];
-  }
-  mean = warp_sum(s) / (float)D;
-  float q = 0.f;
-#pragma unroll
-  for (int c = 0; c < KEEP; ++c) {
-    if ((c * 32 + lane) * 8 < D) {
-      float v[8];
-      unpack8(keep[c], v);
-#pragma unroll
-      for (int i = 0; i < 8; ++i) { const float t = v[i] - mean; q += t * t; }
-    }
-  }
-  for (int d = (KEEP * 32 + lane) * 8; d < D; d += 256) {
-    float v[8];
-    unpack8(ld_act(xr + d), v);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) { const float t = v[i] - mean; q += t * t; }
-  }
-  rstd = rsqrtf(warp_sum(q) / (float)D + eps);
-}
-
-__device__ __forceinline__ uint4 normalise8(const uint4& raw, float mean, float rstd, const float* gain,
-                                            const float* bias, int d) {
-  float v[8], o[8], gn[8];
-  unpack8(raw, v);
-  *reinterpret_cast<float4*>(gn) = __ldg(reinterpret_cast<const float4*>(gain + d));
-  *reinterpret_cast<float4*>(gn + 4) = __ldg(reinterpret_cast<const float4*>(gain + d + 4));
-#pragma unroll
-  for (int i = 0; i < 8; ++i) o[i] = (v[i] - mean) * rstd * gn[i];
-  if (bias) {
-    float bs[8];
-    *reinterpret_cast<float4*>(bs) = __ldg(reinterpret_cast<const float4*>(bias + d));
-    *reinterpret_cast<float4*>(bs + 4) = __ldg(reinterpret_cast<const float4*>(bias + d + 4));
-#pragma unroll
-    for (int i = 0; i < 8; ++i) o[i] += bs[i];
-  }
-  return pack8(o);
+  row_stats_bf16(xr, D, eps, lane, mean, rstd, [](const __nv_bfloat16* p) { return ld_act(p); });
 }
 
 // ------------------------------------------------------------------------------------------ phases

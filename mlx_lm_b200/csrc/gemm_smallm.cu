@@ -54,40 +54,7 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
                : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-struct KvScatter {
-  const int* positions;     // [M]
-  const int* token_req;     // [M] row of the block table, < 0 for padding rows
-  const int* block_table;   // [*, max_pages]
-  __nv_bfloat16* k_pool;    // [n_pages, Hkv, page, Dh]
-  __nv_bfloat16* v_pool;
-  int* status;
-  int max_pages, n_pages, page, Hkv, Dh, q_width;
-};
-
-// Where the key or value element of output column n (>= q_width) of token m lives in the pages; null for a
-// padding row or an index out of range (which sets the status bit).
-__device__ __forceinline__ __nv_bfloat16* kv_slot(const KvScatter& kv, int m, int n) {
-  const int r = kv.token_req[m];
-  if (r < 0) return nullptr;
-  const int pos = kv.positions[m];
-  const int lp = pos / kv.page;
-  const int pg = (pos >= 0 && lp < kv.max_pages) ? kv.block_table[(size_t)r * kv.max_pages + lp] : -2;
-  if (pg == -2) {
-    atomicOr(kv.status, MLXB_ST_POSITION_RANGE);
-    return nullptr;
-  }
-  if (pg >= kv.n_pages) {
-    atomicOr(kv.status, MLXB_ST_PAGE_RANGE);
-    return nullptr;
-  }
-  if (pg < 0) return nullptr;
-  const int kvw = kv.Hkv * kv.Dh;
-  int c2 = n - kv.q_width;
-  __nv_bfloat16* pool = kv.k_pool;
-  if (c2 >= kvw) { c2 -= kvw; pool = kv.v_pool; }
-  const int hh = c2 / kv.Dh, d = c2 - hh * kv.Dh;
-  return pool + (((size_t)pg * kv.Hkv + hh) * kv.page + (pos % kv.page)) * kv.Dh + d;
-}
+#include "kv_scatter.cuh"
 
 // MT: 16-row token tiles (M <= 16*MT); NW: 8-row weight tiles per CTA; WARPS: warps that share the K blocks.
 template <int MT, int NW, int WARPS, typename TO, int EPI, bool SCATTER>

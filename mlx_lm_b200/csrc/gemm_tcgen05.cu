@@ -24,6 +24,7 @@
 #include <cuda.h>
 
 #include "common.cuh"
+#include "kv_scatter.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
 
@@ -194,11 +195,37 @@ __device__ __forceinline__ void store8(const uint32_t* r, int n8, int N, size_t 
   }
 }
 
-template <int BN, int STAGES, typename TO, int EPI>
+// Eight key or value columns n8..n8+7 (n8 >= q_width, a multiple of 8; N = q_width + 2*Hkv*Dh with Dh a
+// multiple of 8, so the eight stay inside one head and all of them exist) of one token, with the bias, into
+// the token's page: one 16-byte store.
+__device__ __forceinline__ void scatter8(const uint32_t* r, int n8, const float* __restrict__ bias, bool bias_vec,
+                                         const KvScatter& kv, long long slot, int in_page) {
+  float v[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+  if (bias) {
+    if (bias_vec) {
+      const float4 b0 = *reinterpret_cast<const float4*>(bias + n8), b1 = *reinterpret_cast<const float4*>(bias + n8 + 4);
+      v[0] += b0.x; v[1] += b0.y; v[2] += b0.z; v[3] += b0.w;
+      v[4] += b1.x; v[5] += b1.y; v[6] += b1.z; v[7] += b1.w;
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] += bias[n8 + i];
+    }
+  }
+  const int kvw = kv.Hkv * kv.Dh;
+  int c2 = n8 - kv.q_width;
+  __nv_bfloat16* pool = kv.k_pool;
+  if (c2 >= kvw) { c2 -= kvw; pool = kv.v_pool; }
+  const int hh = c2 / kv.Dh, d = c2 - hh * kv.Dh;
+  *reinterpret_cast<uint4*>(pool + ((size_t)slot + (size_t)hh * kv.page + in_page) * kv.Dh + d) = pack8(v);
+}
+
+template <int BN, int STAGES, typename TO, int EPI, bool SCATTER>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, const __nv_bfloat16* residual, TO* C, int M, int N, int K,
-                    int ldc, int* __restrict__ status) {
+                    int ldc, int* __restrict__ status, KvScatter kv) {
   extern __shared__ uint8_t smem_raw[];
   Smem<BN, STAGES>& sm = *reinterpret_cast<Smem<BN, STAGES>*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -301,6 +328,21 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
       const int m = m0 + q * 32 + lane;
       const size_t row = (size_t)m * ldc;
+      // fused cache write: this row's slot in its page (an element offset before the head and dim are added);
+      // -1 for a padding row or an index out of range
+      long long slot = -1;
+      int in_page = 0;
+      if (SCATTER && m < M && n0 + BN > kv.q_width) {
+        const int r = kv.token_req[m];
+        if (r >= 0) {
+          const int pos = kv.positions[m];
+          const int lp = pos / kv.page;
+          const int pg = (pos >= 0 && lp < kv.max_pages) ? kv.block_table[(size_t)r * kv.max_pages + lp] : -2;
+          if (pg == -2) atomicOr(kv.status, MLXB_ST_POSITION_RANGE);
+          else if (pg >= kv.n_pages) atomicOr(kv.status, MLXB_ST_PAGE_RANGE);
+          else if (pg >= 0) { slot = (long long)pg * kv.Hkv * kv.page; in_page = pos % kv.page; }
+        }
+      }
       const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * BN + half * HALF_COLS);
 #pragma unroll 1
       for (int c0 = 0; c0 < HALF_COLS; c0 += 32) {
@@ -319,7 +361,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #pragma unroll
           for (int g8 = 0; g8 < 4; ++g8) {
             const int n8 = n0 + half * HALF_COLS + c0 + g8 * 8;
-            if (c0 + g8 * 8 < HALF_COLS && n8 < N) store8<TO, EPI>(r + g8 * 8, n8, N, row, bias, bias_vec, residual, C);
+            if (c0 + g8 * 8 < HALF_COLS && n8 < N) {
+              if (SCATTER && n8 >= kv.q_width) {
+                if (slot >= 0) scatter8(r + g8 * 8, n8, bias, bias_vec, kv, slot, in_page);
+              } else {
+                store8<TO, EPI>(r + g8 * 8, n8, N, row, bias, bias_vec, residual, C);
+              }
+            }
           }
         }
       }
@@ -365,15 +413,15 @@ static int sm_count() {
   return n;
 }
 
-template <int BN, int STAGES, typename TO>
+template <int BN, int STAGES, typename TO, bool SCATTER = false>
 static int launch(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N, int K,
-                  int lda, int ldc, int epi, int* status, cudaStream_t stream) {
+                  int lda, int ldc, int epi, int* status, cudaStream_t stream, const KvScatter& kv = KvScatter{}) {
   CUtensorMap ma, mw;
   if (int e = make_map(&ma, A, M, K, lda, BM)) return e;
   if (int e = make_map(&mw, W, N, K, K, BN)) return e;
   const size_t smem = sizeof(Smem<BN, STAGES>) + 1024;
-  auto k0 = gemm_tcgen05_kernel<BN, STAGES, TO, EPI_NONE>;
-  auto k1 = gemm_tcgen05_kernel<BN, STAGES, TO, EPI_GELU_NEW>;
+  auto k0 = gemm_tcgen05_kernel<BN, STAGES, TO, EPI_NONE, SCATTER>;
+  auto k1 = gemm_tcgen05_kernel<BN, STAGES, TO, SCATTER ? EPI_NONE : EPI_GELU_NEW, SCATTER>;
   auto kern = epi == EPI_GELU_NEW ? k1 : k0;
   static bool raised[2] = {false, false};
   if (!raised[epi == EPI_GELU_NEW]) {
@@ -385,8 +433,23 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
   const int n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const dim3 grid(n_tiles < sm_count() ? n_tiles : sm_count());
   launch_pdl(kern, grid, dim3(THREADS), smem, stream, ma, mw, bias, (const __nv_bfloat16*)residual, (TO*)C, M, N, K,
-             ldc, status);
+             ldc, status, kv);
   return mlxb_check_launch("linear (tensor cores)");
+}
+
+// Tile width: the one whose waves of tiles over the SMs cost least, a tile's cost being the bytes it streams
+// from L2 per K step (128 rows of A plus BN rows of W).
+static int tile_width(int M, int N) {
+  const int tiles_m = (M + BM - 1) / BM, sms = sm_count();
+  int best = 128;
+  long long best_cost = -1;
+  for (int bn : {256, 192, 128}) {
+    const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn);
+    const long long cost = ((tiles + sms - 1) / sms) * (BM + bn);
+    if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
+  }
+  if (const char* force = getenv("MLXB_TC_BN")) best = atoi(force);   // experiments only
+  return best;
 }
 
 // A: bfloat16 [M, K] at row stride lda; W: bfloat16 [N, K] contiguous; bias float32[N] or null; residual bfloat16
@@ -403,17 +466,7 @@ MLXB_EXPORT int mlxb_linear_tcgen05(int out_f32, const void* A, const void* W, c
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15))
     return mlxb_fail(MLXB_BAD_ARG, "linear (tensor cores): operands must be 16-byte aligned");
   if (epi != EPI_NONE && epi != EPI_GELU_NEW) return mlxb_fail(MLXB_BAD_ARG, "linear: epilogue code %d", epi);
-  // Tile width: the one whose waves of tiles over the SMs cost least, a tile's cost being the bytes it streams
-  // from L2 per K step (128 rows of A plus BN rows of W).
-  const int tiles_m = (M + BM - 1) / BM, sms = sm_count();
-  int best = 128;
-  long long best_cost = -1;
-  for (int bn : {256, 192, 128}) {
-    const long long tiles = (long long)tiles_m * ((N + bn - 1) / bn);
-    const long long cost = ((tiles + sms - 1) / sms) * (BM + bn);
-    if (best_cost < 0 || cost < best_cost) { best = bn; best_cost = cost; }
-  }
-  if (const char* force = getenv("MLXB_TC_BN")) best = atoi(force);   // experiments only
+  const int best = tile_width(M, N);
 #define GO(BN_, ST_)                                                                                              \
   {                                                                                                               \
     if (out_f32) return launch<BN_, ST_, float>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, status, stream);  \
@@ -423,4 +476,31 @@ MLXB_EXPORT int mlxb_linear_tcgen05(int out_f32, const void* A, const void* W, c
   if (best == 192) GO(192, 5)
   GO(128, 6)
 #undef GO
+}
+
+
+// The fused [q | k | v] projection with the cache write in its epilogue, for many rows: columns [0, q_width) go
+// to C (bfloat16, row stride ldc); key and value columns go into k_pool / v_pool [n_pages, Hkv, page, Dh] at each
+// token's page and row.  N = q_width + 2*Hkv*Dh; q_width and Dh multiples of 8.  Rows with token_req < 0 write
+// no keys or values.
+MLXB_EXPORT int mlxb_linear_tcgen05_qkv(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
+                                        int lda, int ldc, const int* positions, const int* token_req,
+                                        const int* block_table, int max_pages, int n_pages, int page, int Hkv, int Dh,
+                                        int q_width, void* k_pool, void* v_pool, int* status, cudaStream_t stream) {
+  if (M <= 0 || N <= 0) return 0;
+  if (K <= 0 || (K & 7) || (lda & 7) || lda < K || ldc < N)
+    return mlxb_fail(MLXB_BAD_ARG, "linear (tensor cores): K %d and row stride %d must be multiples of 8 (ldc %d, N %d)",
+                     K, lda, ldc, N);
+  if (((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))
+    return mlxb_fail(MLXB_BAD_ARG, "linear (tensor cores): operands must be 16-byte aligned");
+  if (Hkv <= 0 || Dh <= 0 || (Dh & 7) || page <= 0 || q_width < 0 || (q_width & 7) || N != q_width + 2 * Hkv * Dh)
+    return mlxb_fail(MLXB_BAD_ARG, "linear (q|k|v): %d outputs for %d query columns and 2 x %d x %d", N, q_width, Hkv, Dh);
+  const KvScatter kv = {positions, token_req, block_table, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, status,
+                        max_pages, n_pages, page, Hkv, Dh, q_width};
+  const int best = tile_width(M, N);
+  if (best == 256)
+    return launch<256, 4, __nv_bfloat16, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, status, stream, kv);
+  if (best == 192)
+    return launch<192, 5, __nv_bfloat16, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, status, stream, kv);
+  return launch<128, 6, __nv_bfloat16, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, status, stream, kv);
 }

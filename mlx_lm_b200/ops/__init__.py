@@ -278,9 +278,10 @@ _QKV_ARGS = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
 
 def linear_qkv_to_cache(x, w, bias, out, positions, token_req, block_table, k_pool, v_pool, q_width: int, status,
                         stream) -> None:
-    """The fused ``[q | k | v]`` projection of at most 64 bfloat16 rows with the cache write in its epilogue:
-    query columns go to ``out[:, :q_width]``, key and value columns straight into the pages
-    ``[n_pages, Hkv, page, Dh]`` (the other columns of ``out`` are not written)."""
+    """The fused ``[q | k | v]`` projection of bfloat16 rows with the cache write in its epilogue: query columns
+    go to ``out[:, :q_width]``, key and value columns straight into the pages ``[n_pages, Hkv, page, Dh]`` (the
+    other columns of ``out`` are not written).  Up to 64 rows run in the weight-streaming kernel, more in the
+    tcgen05 kernel."""
     _need(x, torch.bfloat16, "linear x")
     _need(w, torch.bfloat16, "linear w")
     _need(out, torch.bfloat16, "linear out")
@@ -294,7 +295,8 @@ def linear_qkv_to_cache(x, w, bias, out, positions, token_req, block_table, k_po
         raise KernelError(f"linear (q|k|v): {N} outputs for {q_width} query columns and pools {tuple(k_pool.shape)}")
     if bias is not None:
         _need(bias, torch.float32, "linear bias")
-    _call("gemm_smallm", "mlxb_linear_smallm_qkv", _QKV_ARGS, _p(x), _p(w), _p(bias), _p(out), M, N, K,
+    lib, fn = ("gemm_smallm", "mlxb_linear_smallm_qkv") if M <= SMALL_M else ("gemm_tcgen05", "mlxb_linear_tcgen05_qkv")
+    _call(lib, fn, _QKV_ARGS, _p(x), _p(w), _p(bias), _p(out), M, N, K,
           _rows(x, "linear x"), _rows(out, "linear out"), _p(positions), _p(token_req), _p(block_table),
           block_table.shape[1], n_pages, page, Hkv, Dh, q_width, _p(k_pool), _p(v_pool), _p(status), stream)
 

@@ -53,9 +53,10 @@ class Attention(Mixer):
         T = x.shape[0]
         qkv = ctx.ws.get("qkv", T, self.q_width + 2 * self.kv_width, x.dtype)
         q = qkv[:, :self.q_width]
-        if (cache.write and self.position is None and x.dtype == torch.bfloat16 and T <= ops.SMALL_M
-                and self.width % 8 == 0):
-            # few rows: the projection's epilogue puts keys and values into the pages itself
+        if (cache.write and self.position is None and x.dtype == torch.bfloat16 and self.width % 8 == 0
+                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
+            # nothing to do to q and k before the cache: the projection's epilogue puts keys and values
+            # into the pages itself
             ops.linear_qkv_to_cache(x, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, ctx.token_req,
                                     cache.block_table, cache.k, cache.v, self.q_width, ctx.status, ctx.stream)
         else:

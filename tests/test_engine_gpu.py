@@ -233,6 +233,43 @@ def test_decode_as_a_cuda_graph_equals_the_eager_step(dtype, tmp_path):
     engine.check_status()
 
 
+@pytest.mark.parametrize("config,seed,lens", [(CONFIG_A, 21, (5, 40, 17)), (CONFIG_B, 22, (90, 3, 33, 64, 12))])
+def test_decode_step_as_one_persistent_kernel(config, seed, lens, tmp_path):
+    """The opt-in path that runs a whole decode step as one cooperative kernel over a table of phases
+    (csrc/decode_program.cu): its logits are those of the plain implementation, step after step, over page
+    edges, for a batch smaller than its bucket, and the barrier words survive many launches."""
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.engine.scheduler import Request
+    from mlx_lm_b200.sampling import Sampler
+    from mlx_lm_b200.sampling.device import DeviceSampler
+    from mlx_lm_b200.weights import load_model
+    weights = make_model_dir(str(tmp_path), dict(config, ln_gain_std=0.3), seed, peaky=6.0)
+    model, _ = load_model(str(tmp_path), dtype="bfloat16")
+    n_steps = 36
+    seqs = [random_tokens(n + n_steps, config["vocab_size"], seed + n) for n in lens]
+    refs = [plain.logits(t, weights, config) for t in seqs]
+    eng = Engine(model, page_size=16, n_pages=sum((len(t) + 15) // 16 for t in seqs), max_requests=len(seqs))
+    eng.use_program = True
+    sampler = DeviceSampler(model.device, seed=0)
+    reqs = []
+    for i, (n, t) in enumerate(zip(lens, seqs)):
+        eng.add_request(i)
+        eng.step([StepEntry(i, t[:n], [])])
+        reqs.append(Request(i, list(t[:n + 1]), n + 1, 1000, Sampler()))
+    worst = 0.0
+    for s in range(n_steps):
+        entries = [StepEntry(r.uid, [r.tokens[-1]], [0]) for r in reqs]
+        eng.decode_sampled(entries, reqs, sampler)
+        graph = eng._graphs[next(b for b in eng.GRAPH_BUCKETS if b >= len(reqs))]
+        assert graph.program is not None, "the step has no program: the test would not test it"
+        for i, (r, n) in enumerate(zip(reqs, lens)):
+            worst = max(worst, rel(graph.logits[i], refs[i][n + s]))
+            if s + 1 < n_steps:
+                r.tokens.append(seqs[i][n + s + 1])        # the given sequence, not the sampled token
+    eng.check_status()
+    assert worst <= TOL["bfloat16"], worst
+
+
 def test_command_line(tmp_path):
     """`python -m mlx_lm_b200 generate` with a model folder and with --random-weights/--config gives the tokens
     the Python entry point gives."""

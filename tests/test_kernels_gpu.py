@@ -230,6 +230,38 @@ def test_linear_qkv_to_cache(ops, Hq, Hkv, Dh, page, K):
     assert int(changed.sum()) <= 5 * Hkv
 
 
+@pytest.mark.parametrize("Hq,Hkv,Dh,page,K", [(3, 3, 32, 16, 96), (6, 2, 48, 32, 288), (16, 16, 64, 16, 1024),
+                                              (5, 1, 80, 16, 200)])
+def test_linear_qkv_to_cache_many_rows(ops, Hq, Hkv, Dh, page, K):
+    """More than 64 rows (portions of prompts): the tcgen05 kernel's epilogue does the same cache write.  Rows of
+    several requests, starting in the middle of a page, with padding rows between them."""
+    lens, new = [0, 37, 130, 5], [150, 75, 1, 91]
+    c = paged_case(torch.bfloat16, lens=lens, new=new, Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=K + 1)
+    g = torch.Generator().manual_seed(K)
+    n_pad = 7
+    M, N = c["T"] + n_pad, (Hq + 2 * Hkv) * Dh
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    cut = 150                                                      # padding rows after the first request's rows
+    positions = torch.cat([c["positions"][:cut], torch.zeros(n_pad, dtype=torch.int32), c["positions"][cut:]])
+    token_req = torch.cat([c["token_req"][:cut], torch.full((n_pad,), -1, dtype=torch.int32), c["token_req"][cut:]])
+    ref = R.linear(x, w, b).to(torch.bfloat16)
+    qw, kw = Hq * Dh, Hkv * Dh
+    rk, rv = R.kv_write(ref[:, qw:qw + kw], ref[:, qw + kw:], positions, token_req, c["bt"], c["k_pool"], c["v_pool"])
+    kp, vp = c["k_pool"].cuda(), c["v_pool"].cuda()
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.linear_qkv_to_cache(x.cuda(), w.cuda(), b.cuda(), out, positions.cuda(), token_req.cuda(), c["bt"].cuda(), kp, vp,
+                            qw, status, stream())
+    assert int(status.item()) == 0
+    assert rel_err(out[:, :qw], ref[:, :qw].float()) <= 8e-3
+    assert rel_err(kp, rk.float()) <= 8e-3 and rel_err(vp, rv.float()) <= 8e-3
+    changed = (kp.cpu() != c["k_pool"]).any(dim=-1)
+    assert int(changed.sum()) <= c["T"] * Hkv
+    assert float(out[:, qw:].abs().max()) == 0.0                   # key and value columns of the output stay untouched
+
+
 def test_linear_few_rows_refuses_odd_inner_size(ops):
     x = torch.zeros(2, 12, dtype=torch.bfloat16, device="cuda")
     w = torch.zeros(5, 12, dtype=torch.bfloat16, device="cuda")
