@@ -13,8 +13,13 @@
 //                    window, rows beyond the tile
 //   O += P V         P rounded to bf16 as the A operand (the accumulator layout of S is the A layout
 //                    of the next product), V through ldmatrix.trans
+// Key split: a tile's key blocks form a chain that the CTA walks one after the other, and the tiles with the
+// longest chains (the last queries of a long prompt) decide how long the kernel runs.  With KSPLIT = 2 the
+// CTA has two groups of warps for the same queries; group g takes the key blocks whose index is g modulo 2,
+// each group with shared-memory stages and barriers of its own, and the groups' partial results (maximum,
+// sum, output) are merged through shared memory at the end.  The chain a warp walks is half as long.
 // The order in which a query's keys are added depends only on its position: blocks of 64 positions
-// from block 0 (or the window's first block) upward.
+// from block 0 (or the window's first block) upward, even and odd blocks apart, then the two merged.
 //
 // (tcgen05 has no place here yet: with 64-wide heads the softmax, not the products, is the long pole
 // of this kernel; the linear layers, which carry 92 % of a prompt's flops, use tcgen05.)
@@ -61,22 +66,29 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 
 // tiles: int32 [n_tiles][4] = (row of the tile's first token among the step's tokens, queries in the tile
 // (1..16*WARPS), block-table row of the request, position of the tile's first query).
-template <int DH, int WARPS>
-__global__ void __launch_bounds__(WARPS * 32, (DH <= 64 ? 512 : 256) / (WARPS * 32))
+__device__ __forceinline__ void group_barrier(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// QW: warps that share the tile's queries (16 each); KSPLIT: groups of QW warps that share the key blocks.
+template <int DH, int QW, int KSPLIT>
+__global__ void __launch_bounds__(QW * KSPLIT * 32, (DH <= 64 ? 512 : 256) / (QW * KSPLIT * 32))
 attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int4* __restrict__ tiles,
                          const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                          int window, float scale_log2e, const __nv_bfloat16* __restrict__ k_pool,
                          const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, int ldo,
                          int* __restrict__ status) {
-  constexpr int THREADS = WARPS * 32;
+  constexpr int THREADS = QW * 32;            // threads of one group: they gather and use the same key blocks
   constexpr int STRIDE = DH + 8;              // elements per shared-memory row (16 bytes of padding)
   constexpr int KS = DH / 16;                 // k steps of Q K^T
   constexpr int NT = DH / 8;                  // n tiles of the output
   constexpr int CHUNKS = DH / 8;              // 16-byte chunks per key row
   constexpr int NIT = (BKV * CHUNKS + THREADS - 1) / THREADS;   // chunks a thread copies per block
   extern __shared__ __align__(16) uint8_t smem_raw[];
-  __nv_bfloat16* sk = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [2][BKV][STRIDE]
-  __nv_bfloat16* sv = sk + 2 * BKV * STRIDE;                             // [2][BKV][STRIDE]
+  const int group = (threadIdx.x >> 5) / QW;            // which share of the key blocks
+  const int gtid = threadIdx.x - group * THREADS;       // thread index within the group
+  __nv_bfloat16* sk = reinterpret_cast<__nv_bfloat16*>(smem_raw) + group * (4 * BKV * STRIDE);   // [2][BKV][STRIDE]
+  __nv_bfloat16* sv = sk + 2 * BKV * STRIDE;                                                     // [2][BKV][STRIDE]
 
   pdl_trigger();
   pdl_wait();
@@ -86,7 +98,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
   const int4 tile = tiles[blockIdx.x];
   const int row0 = tile.x, n_rows = tile.y, req = tile.z, pos0 = tile.w;
   const int h = blockIdx.y, hk = h / (Hq / Hkv);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, qd = lane & 3;
+  const int warp = gtid >> 5, lane = threadIdx.x & 31, g = lane >> 2, qd = lane & 3;
   const int* bt = block_table + (size_t)req * max_pages;
   const int shift = __ffs(page) - 1;
 
@@ -98,7 +110,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
   int c_row[NIT], c_soff[NIT], c_goff[NIT];
 #pragma unroll
   for (int j = 0; j < NIT; ++j) {
-    const int i = threadIdx.x + j * THREADS;
+    const int i = gtid + j * THREADS;
     const int kr = i / CHUNKS, ch = i - kr * CHUNKS;
     c_row[j] = i < BKV * CHUNKS ? kr : -1;
     c_soff[j] = kr * STRIDE + ch * 8;
@@ -132,7 +144,9 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
     cp_async_commit();
   };
 
-  load_block(kb_lo, 0);
+  // this group's blocks: kb_first, kb_first + KSPLIT, ... (block indices congruent to `group`)
+  const int kb_first = kb_lo + ((group - kb_lo) % KSPLIT + KSPLIT) % KSPLIT;
+  if (kb_first <= kb_hi) load_block(kb_first, 0);
 
   // this warp's 16 queries: rows r_lo = 16*warp + g and r_hi = r_lo + 8 of the tile
   const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
@@ -168,11 +182,12 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
 
   const int mi = lane >> 3, mr = lane & 7;   // ldmatrix: which 8x8 matrix this lane addresses, and its row
 
-  for (int kb = kb_lo; kb <= kb_hi; ++kb) {
-    const int st = (kb - kb_lo) & 1;
-    if (kb < kb_hi) load_block(kb + 1, st ^ 1);
-    if (kb < kb_hi) cp_async_wait<1>(); else cp_async_wait<0>();
-    __syncthreads();
+  for (int kb = kb_first; kb <= kb_hi; kb += KSPLIT) {
+    const int st = ((kb - kb_first) / KSPLIT) & 1;
+    const bool more = kb + KSPLIT <= kb_hi;
+    if (more) load_block(kb + KSPLIT, st ^ 1);
+    if (more) cp_async_wait<1>(); else cp_async_wait<0>();
+    if (KSPLIT == 1) __syncthreads(); else group_barrier(1 + group, THREADS);
 
     if (kb * BKV <= warp_last_pos) {     // otherwise every key of the block lies after this warp's queries
       const __nv_bfloat16* bk = sk + st * BKV * STRIDE;
@@ -254,7 +269,48 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
         }
       }
     }
-    __syncthreads();   // everyone is done with stage st before it is loaded again
+    // everyone is done with stage st before it is loaded again
+    if (KSPLIT == 1) __syncthreads(); else group_barrier(1 + group, THREADS);
+  }
+
+  if (KSPLIT > 1) {
+    // merge the groups: thread t of every group holds the same elements of the same queries
+    float* xch = reinterpret_cast<float*>(smem_raw);   // [KSPLIT - 1][NT * 4 + 4][THREADS]; the stages are free now
+    __syncthreads();
+    if (group > 0) {
+      float* dst = xch + (size_t)(group - 1) * (NT * 4 + 4) * THREADS + gtid;
+#pragma unroll
+      for (int i = 0; i < NT; ++i)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) dst[(i * 4 + c) * THREADS] = o[i][c];
+      dst[(NT * 4 + 0) * THREADS] = m_lo;
+      dst[(NT * 4 + 1) * THREADS] = m_hi;
+      dst[(NT * 4 + 2) * THREADS] = l_lo;
+      dst[(NT * 4 + 3) * THREADS] = l_hi;
+    }
+    __syncthreads();
+    if (group > 0) return;
+#pragma unroll
+    for (int gg = 1; gg < KSPLIT; ++gg) {
+      const float* src = xch + (size_t)(gg - 1) * (NT * 4 + 4) * THREADS + gtid;
+      const float om_lo = src[(NT * 4 + 0) * THREADS], om_hi = src[(NT * 4 + 1) * THREADS];
+      const float ol_lo = src[(NT * 4 + 2) * THREADS], ol_hi = src[(NT * 4 + 3) * THREADS];
+      const float mn_lo = fmaxf(m_lo, om_lo), mn_hi = fmaxf(m_hi, om_hi);
+      const float b_lo = mn_lo == -INFINITY ? 0.f : mn_lo, b_hi = mn_hi == -INFINITY ? 0.f : mn_hi;
+      const float wa_lo = fast_exp2(m_lo - b_lo), wb_lo = fast_exp2(om_lo - b_lo);   // 2^-inf = 0
+      const float wa_hi = fast_exp2(m_hi - b_hi), wb_hi = fast_exp2(om_hi - b_hi);
+      l_lo = l_lo * wa_lo + ol_lo * wb_lo;
+      l_hi = l_hi * wa_hi + ol_hi * wb_hi;
+#pragma unroll
+      for (int i = 0; i < NT; ++i) {
+        o[i][0] = o[i][0] * wa_lo + src[(i * 4 + 0) * THREADS] * wb_lo;
+        o[i][1] = o[i][1] * wa_lo + src[(i * 4 + 1) * THREADS] * wb_lo;
+        o[i][2] = o[i][2] * wa_hi + src[(i * 4 + 2) * THREADS] * wb_hi;
+        o[i][3] = o[i][3] * wa_hi + src[(i * 4 + 3) * THREADS] * wb_hi;
+      }
+      m_lo = mn_lo;
+      m_hi = mn_hi;
+    }
   }
 
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1);
@@ -271,12 +327,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
   }
 }
 
-template <int DH, int WARPS>
+template <int DH, int QW, int KSPLIT>
 static int launch(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table, int max_pages,
                   int n_pages, int page, int Hq, int Hkv, int window, float scale, const void* k_pool,
                   const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream) {
-  const size_t smem = (size_t)2 * 2 * BKV * (DH + 8) * sizeof(__nv_bfloat16);
-  auto kern = attention_prefill_kernel<DH, WARPS>;
+  constexpr int WARPS = QW * KSPLIT;
+  size_t smem = (size_t)KSPLIT * 2 * 2 * BKV * (DH + 8) * sizeof(__nv_bfloat16);
+  const size_t merge = (size_t)(KSPLIT - 1) * (DH / 8 * 4 + 4) * QW * 32 * sizeof(float);
+  if (merge > smem) smem = merge;
+  auto kern = attention_prefill_kernel<DH, QW, KSPLIT>;
   static bool raised = false;
   if (smem > 48 * 1024 && !raised) {
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -308,10 +367,10 @@ MLXB_EXPORT int mlxb_attention_prefill(const void* q, int ldq, const int* tiles,
 #define GO(D)                                                                                                         \
   case D:                                                                                                             \
     if (tile_rows == 128)                                                                                             \
-      return launch<D, 8>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,      \
-                          k_pool, v_pool, out, ldo, status, stream);                                                  \
-    return launch<D, 4>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale, k_pool, \
-                        v_pool, out, ldo, status, stream)
+      return launch<D, 8, 1>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,   \
+                             k_pool, v_pool, out, ldo, status, stream);                                               \
+    return launch<D, 4, 2>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,     \
+                           k_pool, v_pool, out, ldo, status, stream)
   switch (Dh) {
     GO(16); GO(32); GO(48); GO(64); GO(80); GO(96); GO(112); GO(128);
     default:

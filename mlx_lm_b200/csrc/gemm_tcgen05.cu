@@ -131,7 +131,8 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 // One 8-column group of an output row: bias, activation, residual, store.
 template <typename TO, int EPI>
 __device__ __forceinline__ void store8(const uint32_t* r, int n8, int N, size_t row, const float* __restrict__ bias,
-                                       bool bias_vec, const __nv_bfloat16* residual, TO* C) {
+                                       bool bias_vec, const __nv_bfloat16* residual, TO* C,
+                                       bool have_fetched = false, uint4 fetched = uint4{0u, 0u, 0u, 0u}) {
   float v[8];
   const bool whole = n8 + 8 <= N;
 #pragma unroll
@@ -152,8 +153,8 @@ __device__ __forceinline__ void store8(const uint32_t* r, int n8, int N, size_t 
     for (int i = 0; i < 8; ++i) v[i] = gelu_new_fast(v[i]);
   }
   if (residual) {
-    if (whole && ((row + n8) & 7) == 0) {
-      const uint4 u = *reinterpret_cast<const uint4*>(residual + row + n8);
+    if (have_fetched || (whole && ((row + n8) & 7) == 0)) {
+      const uint4 u = have_fetched ? fetched : *reinterpret_cast<const uint4*>(residual + row + n8);
       const uint32_t w[4] = {u.x, u.y, u.z, u.w};
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
@@ -323,11 +324,31 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     int it = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++it) {
       const int b = it & 1;
-      if (!mbar_wait(&sm.acc_full[b], (it >> 1) & 1, abort_flag)) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int m0 = (tile % tiles_m) * BM, n0 = (tile / tiles_m) * BN;
       const int m = m0 + q * 32 + lane;
       const size_t row = (size_t)m * ldc;
+      // The residual of this lane's row, 32 columns at a time (64 contiguous bytes), is fetched a chunk ahead:
+      // the first chunk while the tile's products are still running, each further one while the chunk before
+      // it is worked on.  Bit g of `have` says that group g of the chunk was fetched (whole and aligned).
+      uint4 res0, res1, res2, res3, nx0, nx1, nx2, nx3;
+      res0 = res1 = res2 = res3 = nx0 = nx1 = nx2 = nx3 = make_uint4(0u, 0u, 0u, 0u);
+      unsigned have = 0, have_next = 0;
+#define FETCH_RESIDUAL(C0, D0, D1, D2, D3, HAVE)                                                        \
+      {                                                                                                   \
+        HAVE = 0;                                                                                         \
+        if (residual != nullptr && m < M) {                                                               \
+          const int nb = n0 + half * HALF_COLS + (C0);                                                    \
+          const __nv_bfloat16* rp = residual + row + nb;                                                  \
+          const bool al = ((row + nb) & 7) == 0;                                                          \
+          if (al && (C0) + 0 < HALF_COLS && nb + 8 <= N) { D0 = *reinterpret_cast<const uint4*>(rp); HAVE |= 1u; }          \
+          if (al && (C0) + 8 < HALF_COLS && nb + 16 <= N) { D1 = *reinterpret_cast<const uint4*>(rp + 8); HAVE |= 2u; }     \
+          if (al && (C0) + 16 < HALF_COLS && nb + 24 <= N) { D2 = *reinterpret_cast<const uint4*>(rp + 16); HAVE |= 4u; }   \
+          if (al && (C0) + 24 < HALF_COLS && nb + 32 <= N) { D3 = *reinterpret_cast<const uint4*>(rp + 24); HAVE |= 8u; }   \
+        }                                                                                                 \
+      }
+      FETCH_RESIDUAL(0, res0, res1, res2, res3, have)
+      if (!mbar_wait(&sm.acc_full[b], (it >> 1) & 1, abort_flag)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // fused cache write: this row's slot in its page (an element offset before the head and dim are added);
       // -1 for a padding row or an index out of range
       long long slot = -1;
@@ -352,6 +373,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         } else {                                // 48 columns per warp (BN = 192): the last 16
           tmem_ld16(taddr + (uint32_t)c0, r);
         }
+        if (c0 + 32 < HALF_COLS) FETCH_RESIDUAL(c0 + 32, nx0, nx1, nx2, nx3, have_next)
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         if (c0 + 32 >= HALF_COLS) {   // this warp's part of the accumulator is in registers: hand it back
           asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -365,12 +387,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               if (SCATTER && n8 >= kv.q_width) {
                 if (slot >= 0) scatter8(r + g8 * 8, n8, bias, bias_vec, kv, slot, in_page);
               } else {
-                store8<TO, EPI>(r + g8 * 8, n8, N, row, bias, bias_vec, residual, C);
+                store8<TO, EPI>(r + g8 * 8, n8, N, row, bias, bias_vec, residual, C, (have >> g8) & 1,
+                                g8 == 0 ? res0 : (g8 == 1 ? res1 : (g8 == 2 ? res2 : res3)));
               }
             }
           }
         }
+        res0 = nx0; res1 = nx1; res2 = nx2; res3 = nx3;
+        have = have_next;
       }
+#undef FETCH_RESIDUAL
     }
   }
 
