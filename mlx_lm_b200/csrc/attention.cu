@@ -279,8 +279,9 @@ template <> struct Raw8<float> {
 };
 
 // partial: float [n_rows][Hq][n_chunks_max][Dh + 2] = (m, l, o[Dh]) per chunk.
-// DEC_THREADS: 512 when there are few (row, head) pairs (one CTA streams a whole row's keys with many loads in
-// flight), 256 when there are many (two CTAs per SM, so that one CTA's merge overlaps the other's loads).
+// DEC_THREADS: 512 when there are no more (row, head) pairs than SMs (one CTA streams a whole row's keys with
+// many loads in flight), 256 when there are more (two CTAs per SM, so that one CTA's merge overlaps the
+// other's loads; a third CTA per SM would need 80 registers a thread, and the spills cost more than it gains).
 template <typename T, int TPK, int DEC_THREADS>
 __global__ void __launch_bounds__(DEC_THREADS)
 attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict__ rows,
@@ -519,7 +520,13 @@ static int launch_decode(const void* q, int ldq, const int* rows, const int* pos
   int tpk = 2;
   while (tpk < chunks8) tpk <<= 1;
   const dim3 grid(n_chunks_max, Hq, n_rows);
-  const bool many = (long long)n_rows * Hq >= 592;
+  static int sms = 0;
+  if (sms == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+  }
+  const bool many = (long long)n_rows * Hq > sms;   // more (row, head) pairs than SMs: several smaller CTAs per SM
 #define DEC2(TPK_, TH_)                                                                                              \
   {                                                                                                                  \
     const size_t smem = (size_t)(TH_ / 32) * (Dh + 2) * sizeof(float);                                               \

@@ -283,18 +283,20 @@ static int launch_epi(const void* A, const void* W, const float* bias, const voi
 template <typename TO, bool SCATTER>
 static int launch(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N, int K,
                   int lda, int ldc, int epi, const KvScatter& kv, cudaStream_t stream) {
-  // Weight tiles per CTA: as many as keep at least ~2 CTAs per SM; more tiles re-use each
-  // activation fragment for more weight rows, which matters once M is large.
+  // Weight tiles per CTA.  Every CTA reads all M rows of the activations from L2, so with many rows and many
+  // CTAs that traffic (M x K x 2 bytes per CTA) exceeds the weight stream itself; wide outputs therefore get
+  // more tiles per CTA once M is large (measured at 1024-wide models: 3072 and 4096 outputs at 33-64 rows
+  // are a quarter faster with four tiles, 4096 outputs at 17-32 rows with two; narrow outputs need the CTAs).
   const int tiles = (N + 7) / 8;
   const int mt = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
   int nw = 1;
-  if (mt == 4) nw = tiles >= 4 * 296 ? 4 : (tiles >= 2 * 148 ? 2 : 1);
-  else if (mt == 2) nw = tiles >= 2 * 296 ? 2 : 1;
+  if (mt == 4) nw = tiles >= 384 ? 4 : (tiles >= 2 * 148 ? 2 : 1);
+  else if (mt == 2) nw = tiles >= 512 ? 2 : 1;
   // K blocks are shared by 8 warps; a long K with few output tiles gets 16 so that a warp's chain of
   // dependent loads stays short.
 #define GO(MT_, NW_)                                                                                              \
   {                                                                                                               \
-    if (K >= 2048 && MT_ * NW_ == 1)                                                                              \
+    if (K >= 2048 && NW_ == 1)                                                                                    \
       return launch_epi<MT_, NW_, 16, TO, SCATTER>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, kv, stream);  \
     return launch_epi<MT_, NW_, 8, TO, SCATTER>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, kv, stream);     \
   }

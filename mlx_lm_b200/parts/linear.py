@@ -58,7 +58,10 @@ class Linear(Part):
         epi = ACTIVATIONS[activation]
         fast = (x.dtype == torch.bfloat16 and self.n_in % 8 == 0 and x.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0)
-        if fast and x.shape[0] <= ops.SMALL_M:
+        few = x.shape[0] <= ops.SMALL_M
+        if few and x.shape[0] > 32 and self.n_out >= 16384:
+            few = False       # a vocabulary-sized output at 33-64 rows: measured faster on the tcgen05 kernel
+        if fast and few:
             ops.linear_few_rows(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual)
         elif fast:
             ops.linear_tensor_cores(x, self.weight, self.bias, out, ctx.status, ctx.stream, epilogue=epi,
