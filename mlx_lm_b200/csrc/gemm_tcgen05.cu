@@ -128,15 +128,31 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// A LayerNorm folded into the weights (see NormFold in gemm_smallm.cuh): the epilogue turns the product of the
+// rows as they are into rstd * (sum - mean * colsum[n]).  stats[m] = (mean, rstd) of row m, from row_stats.
+struct NormFoldRows {
+  const float* colsum;    // [N], null: no fold
+  const float2* stats;    // [M]
+};
+
+__device__ __forceinline__ void unfold8(float (&v)[8], int n8, int N, const float* __restrict__ colsum, float mean,
+                                        float rstd) {
+#pragma unroll
+  for (int i = 0; i < 8; ++i)
+    if (n8 + i < N) v[i] = rstd * (v[i] - mean * colsum[n8 + i]);
+}
+
 // One 8-column group of an output row: bias, activation, residual, store.
 template <typename TO, int EPI>
 __device__ __forceinline__ void store8(const uint32_t* r, int n8, int N, size_t row, const float* __restrict__ bias,
                                        bool bias_vec, const __nv_bfloat16* residual, TO* C,
-                                       bool have_fetched = false, uint4 fetched = uint4{0u, 0u, 0u, 0u}) {
+                                       bool have_fetched, uint4 fetched, const float* __restrict__ colsum, float mean,
+                                       float rstd) {
   float v[8];
   const bool whole = n8 + 8 <= N;
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+  if (colsum) unfold8(v, n8, N, colsum, mean, rstd);
   if (bias) {
     if (whole && bias_vec) {   // the same 32 bytes for every lane of the warp: two broadcast loads
       const float4 b0 = *reinterpret_cast<const float4*>(bias + n8), b1 = *reinterpret_cast<const float4*>(bias + n8 + 4);
@@ -200,10 +216,12 @@ __device__ __forceinline__ void store8(const uint32_t* r, int n8, int N, size_t 
 // multiple of 8, so the eight stay inside one head and all of them exist) of one token, with the bias, into
 // the token's page: one 16-byte store.
 __device__ __forceinline__ void scatter8(const uint32_t* r, int n8, const float* __restrict__ bias, bool bias_vec,
-                                         const KvScatter& kv, long long slot, int in_page) {
+                                         const KvScatter& kv, long long slot, int in_page,
+                                         const float* __restrict__ colsum, float mean, float rstd) {
   float v[8];
 #pragma unroll
   for (int i = 0; i < 8; ++i) v[i] = __uint_as_float(r[i]);
+  if (colsum) unfold8(v, n8, n8 + 8, colsum, mean, rstd);
   if (bias) {
     if (bias_vec) {
       const float4 b0 = *reinterpret_cast<const float4*>(bias + n8), b1 = *reinterpret_cast<const float4*>(bias + n8 + 4);
@@ -226,7 +244,7 @@ template <int BN, int STAGES, typename TO, int EPI, bool SCATTER>
 __global__ void __launch_bounds__(THREADS)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     const float* __restrict__ bias, const __nv_bfloat16* residual, TO* C, int M, int N, int K,
-                    int ldc, int* __restrict__ status, KvScatter kv) {
+                    int ldc, int* __restrict__ status, KvScatter kv, NormFoldRows fold) {
   extern __shared__ uint8_t smem_raw[];
   Smem<BN, STAGES>& sm = *reinterpret_cast<Smem<BN, STAGES>*>(
       (reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -330,6 +348,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
       // The residual of this lane's row, 32 columns at a time (64 contiguous bytes), is fetched a chunk ahead:
       // the first chunk while the tile's products are still running, each further one while the chunk before
       // it is worked on.  Bit g of `have` says that group g of the chunk was fetched (whole and aligned).
+      float mean = 0.f, rstd = 1.f;
+      if (fold.colsum != nullptr && m < M) {
+        const float2 st = fold.stats[m];
+        mean = st.x;
+        rstd = st.y;
+      }
       uint4 res0, res1, res2, res3, nx0, nx1, nx2, nx3;
       res0 = res1 = res2 = res3 = nx0 = nx1 = nx2 = nx3 = make_uint4(0u, 0u, 0u, 0u);
       unsigned have = 0, have_next = 0;
@@ -385,10 +409,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int n8 = n0 + half * HALF_COLS + c0 + g8 * 8;
             if (c0 + g8 * 8 < HALF_COLS && n8 < N) {
               if (SCATTER && n8 >= kv.q_width) {
-                if (slot >= 0) scatter8(r + g8 * 8, n8, bias, bias_vec, kv, slot, in_page);
+                if (slot >= 0) scatter8(r + g8 * 8, n8, bias, bias_vec, kv, slot, in_page, fold.colsum, mean, rstd);
               } else {
                 store8<TO, EPI>(r + g8 * 8, n8, N, row, bias, bias_vec, residual, C, (have >> g8) & 1,
-                                g8 == 0 ? res0 : (g8 == 1 ? res1 : (g8 == 2 ? res2 : res3)));
+                                g8 == 0 ? res0 : (g8 == 1 ? res1 : (g8 == 2 ? res2 : res3)), fold.colsum, mean, rstd);
               }
             }
           }
@@ -441,7 +465,8 @@ static int sm_count() {
 
 template <int BN, int STAGES, typename TO, bool SCATTER = false>
 static int launch(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N, int K,
-                  int lda, int ldc, int epi, int* status, cudaStream_t stream, const KvScatter& kv = KvScatter{}) {
+                  int lda, int ldc, int epi, int* status, cudaStream_t stream, const KvScatter& kv = KvScatter{},
+                  const NormFoldRows& fold = NormFoldRows{}) {
   CUtensorMap ma, mw;
   if (int e = make_map(&ma, A, M, K, lda, BM)) return e;
   if (int e = make_map(&mw, W, N, K, K, BN)) return e;
@@ -459,7 +484,7 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
   const int n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const dim3 grid(n_tiles < sm_count() ? n_tiles : sm_count());
   launch_pdl(kern, grid, dim3(THREADS), smem, stream, ma, mw, bias, (const __nv_bfloat16*)residual, (TO*)C, M, N, K,
-             ldc, status, kv);
+             ldc, status, kv, fold);
   return mlxb_check_launch("linear (tensor cores)");
 }
 
@@ -482,9 +507,29 @@ static int tile_width(int M, int N) {
 // [M, N] at row stride ldc or null (may alias C); C bfloat16 or float32 (out_f32) [M, N] at row stride ldc.
 // K, lda multiples of 8; A and W 16-byte aligned.  status: int32 word that receives MLXB_ST_WAIT_TIMEOUT if a
 // bounded wait inside the kernel gives up.
+static int linear_tcgen05(int out_f32, const void* A, const void* W, const float* bias, const void* residual, void* C,
+                          int M, int N, int K, int lda, int ldc, int epi, int* status, const NormFoldRows& fold,
+                          cudaStream_t stream);
+
 MLXB_EXPORT int mlxb_linear_tcgen05(int out_f32, const void* A, const void* W, const float* bias, const void* residual,
                                     void* C, int M, int N, int K, int lda, int ldc, int epi, int* status,
                                     cudaStream_t stream) {
+  return linear_tcgen05(out_f32, A, W, bias, residual, C, M, N, K, lda, ldc, epi, status, NormFoldRows{}, stream);
+}
+
+// The same with a folded LayerNorm: W and bias are the folded ones, colsum float32[N], stats float32[M][2]
+// (mean, rstd of the rows of A, from mlxb_row_stats).
+MLXB_EXPORT int mlxb_linear_tcgen05_fold(int out_f32, const void* A, const void* W, const float* bias,
+                                         const void* residual, void* C, int M, int N, int K, int lda, int ldc, int epi,
+                                         int* status, const float* colsum, const void* stats, cudaStream_t stream) {
+  if (colsum == nullptr || stats == nullptr) return mlxb_fail(MLXB_BAD_ARG, "linear (folded norm): column sums or row statistics missing");
+  return linear_tcgen05(out_f32, A, W, bias, residual, C, M, N, K, lda, ldc, epi, status,
+                        NormFoldRows{colsum, (const float2*)stats}, stream);
+}
+
+static int linear_tcgen05(int out_f32, const void* A, const void* W, const float* bias, const void* residual, void* C,
+                          int M, int N, int K, int lda, int ldc, int epi, int* status, const NormFoldRows& fold,
+                          cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (lda & 7) || lda < K || ldc < N)
     return mlxb_fail(MLXB_BAD_ARG, "linear (tensor cores): K %d and row stride %d must be multiples of 8 (ldc %d, N %d)",
@@ -495,8 +540,11 @@ MLXB_EXPORT int mlxb_linear_tcgen05(int out_f32, const void* A, const void* W, c
   const int best = tile_width(M, N);
 #define GO(BN_, ST_)                                                                                              \
   {                                                                                                               \
-    if (out_f32) return launch<BN_, ST_, float>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, status, stream);  \
-    return launch<BN_, ST_, __nv_bfloat16>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, status, stream);       \
+    if (out_f32)                                                                                                  \
+      return launch<BN_, ST_, float>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, status, stream, KvScatter{}, \
+                                     fold);                                                                       \
+    return launch<BN_, ST_, __nv_bfloat16>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, status, stream,        \
+                                           KvScatter{}, fold);                                                    \
   }
   if (best == 256) GO(256, 4)
   if (best == 192) GO(192, 5)
@@ -509,10 +557,35 @@ MLXB_EXPORT int mlxb_linear_tcgen05(int out_f32, const void* A, const void* W, c
 // to C (bfloat16, row stride ldc); key and value columns go into k_pool / v_pool [n_pages, Hkv, page, Dh] at each
 // token's page and row.  N = q_width + 2*Hkv*Dh; q_width and Dh multiples of 8.  Rows with token_req < 0 write
 // no keys or values.
+static int linear_tcgen05_qkv(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int lda,
+                              int ldc, const int* positions, const int* token_req, const int* block_table,
+                              int max_pages, int n_pages, int page, int Hkv, int Dh, int q_width, void* k_pool,
+                              void* v_pool, int* status, const NormFoldRows& fold, cudaStream_t stream);
+
 MLXB_EXPORT int mlxb_linear_tcgen05_qkv(const void* A, const void* W, const float* bias, void* C, int M, int N, int K,
                                         int lda, int ldc, const int* positions, const int* token_req,
                                         const int* block_table, int max_pages, int n_pages, int page, int Hkv, int Dh,
                                         int q_width, void* k_pool, void* v_pool, int* status, cudaStream_t stream) {
+  return linear_tcgen05_qkv(A, W, bias, C, M, N, K, lda, ldc, positions, token_req, block_table, max_pages, n_pages,
+                            page, Hkv, Dh, q_width, k_pool, v_pool, status, NormFoldRows{}, stream);
+}
+
+// The same with a folded LayerNorm (see mlxb_linear_tcgen05_fold).
+MLXB_EXPORT int mlxb_linear_tcgen05_qkv_fold(const void* A, const void* W, const float* bias, void* C, int M, int N,
+                                             int K, int lda, int ldc, const int* positions, const int* token_req,
+                                             const int* block_table, int max_pages, int n_pages, int page, int Hkv,
+                                             int Dh, int q_width, void* k_pool, void* v_pool, int* status,
+                                             const float* colsum, const void* stats, cudaStream_t stream) {
+  if (colsum == nullptr || stats == nullptr) return mlxb_fail(MLXB_BAD_ARG, "linear (folded norm): column sums or row statistics missing");
+  return linear_tcgen05_qkv(A, W, bias, C, M, N, K, lda, ldc, positions, token_req, block_table, max_pages, n_pages,
+                            page, Hkv, Dh, q_width, k_pool, v_pool, status, NormFoldRows{colsum, (const float2*)stats},
+                            stream);
+}
+
+static int linear_tcgen05_qkv(const void* A, const void* W, const float* bias, void* C, int M, int N, int K, int lda,
+                              int ldc, const int* positions, const int* token_req, const int* block_table,
+                              int max_pages, int n_pages, int page, int Hkv, int Dh, int q_width, void* k_pool,
+                              void* v_pool, int* status, const NormFoldRows& fold, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (K <= 0 || (K & 7) || (lda & 7) || lda < K || ldc < N)
     return mlxb_fail(MLXB_BAD_ARG, "linear (tensor cores): K %d and row stride %d must be multiples of 8 (ldc %d, N %d)",
@@ -525,8 +598,8 @@ MLXB_EXPORT int mlxb_linear_tcgen05_qkv(const void* A, const void* W, const floa
                         max_pages, n_pages, page, Hkv, Dh, q_width};
   const int best = tile_width(M, N);
   if (best == 256)
-    return launch<256, 4, __nv_bfloat16, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, status, stream, kv);
+    return launch<256, 4, __nv_bfloat16, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, status, stream, kv, fold);
   if (best == 192)
-    return launch<192, 5, __nv_bfloat16, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, status, stream, kv);
-  return launch<128, 6, __nv_bfloat16, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, status, stream, kv);
+    return launch<192, 5, __nv_bfloat16, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, status, stream, kv, fold);
+  return launch<128, 6, __nv_bfloat16, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, status, stream, kv, fold);
 }

@@ -188,3 +188,30 @@ MLXB_EXPORT int mlxb_layernorm(int dtype, const void* x, const int* rows, const 
   }
   return mlxb_check_launch("layernorm");
 }
+
+
+// Mean and 1/sqrt(var + eps) of bfloat16 rows (width a multiple of 8): stats[r] = (mean, rstd).  For a
+// LayerNorm that has been folded into the weights of the linear layer after it, whose epilogue needs only
+// these two numbers per row.  One warp per row, same order of additions as the norm itself.
+__global__ void __launch_bounds__(256)
+row_stats_kernel(const __nv_bfloat16* __restrict__ x, float2* __restrict__ stats, int R, int D, int ld, float eps) {
+  pdl_trigger();
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * 8 + warp;
+  if (r >= R) return;
+  pdl_wait();
+  const __nv_bfloat16* xr = after_wait(x) + (size_t)r * ld;
+  float mean, rstd;
+  row_stats_bf16(xr, D, eps, lane, mean, rstd, [](const __nv_bfloat16* p) { return *reinterpret_cast<const uint4*>(p); });
+  if (lane == 0) stats[r] = make_float2(mean, rstd);
+}
+
+// x: bfloat16 [R, D] at row stride ld (elements; multiple of 8, base 16-byte aligned); stats: float32 [R, 2].
+MLXB_EXPORT int mlxb_row_stats(const void* x, void* stats, int R, int D, int ld, float eps, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (D <= 0 || (D & 7) || (ld & 7) || ld < D || ((uintptr_t)x & 15) || ((uintptr_t)stats & 7))
+    return mlxb_fail(MLXB_BAD_ARG, "row_stats: width %d, row stride %d (multiples of 8, 16-byte aligned rows)", D, ld);
+  launch_pdl(row_stats_kernel, dim3((R + 7) / 8), dim3(256), 0, stream, (const __nv_bfloat16*)x, (float2*)stats, R, D,
+             ld, eps);
+  return mlxb_check_launch("row_stats");
+}

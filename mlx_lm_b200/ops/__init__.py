@@ -26,7 +26,7 @@ EPI_NONE, EPI_GELU_NEW = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 # kernel sources that only a bfloat16 run launches from: a float32 run neither compiles nor loads them
-BF16_ONLY_LIBS = frozenset({"gemm_smallm", "gemm_tcgen05", "attention_prefill"})
+BF16_ONLY_LIBS = frozenset({"gemm_smallm", "gemm_smallm_fold", "gemm_tcgen05", "attention_prefill"})
 
 # status word bits set by kernels (csrc/common.cuh)
 ST_TOKEN_RANGE, ST_POSITION_RANGE, ST_PAGE_RANGE, ST_WAIT_TIMEOUT = 1, 2, 4, 8
@@ -176,6 +176,20 @@ def layernorm(x, gain, bias, out, eps: float, stream, rows=None) -> None:
           R, D, eps, stream)
 
 
+_STATS_ARGS = [c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p]
+
+
+def row_stats(x, stats, eps: float, stream) -> None:
+    """``stats[r] = (mean, 1/sqrt(var + eps))`` of the bfloat16 rows of ``x`` (float32 ``[R, 2]``): what the
+    epilogue of a linear layer with a folded LayerNorm needs of the rows."""
+    _need(x, torch.bfloat16, "row_stats x")
+    _need(stats, torch.float32, "row_stats stats")
+    R, D = x.shape
+    if stats.shape != (R, 2) or not stats.is_contiguous():
+        raise KernelError(f"row_stats: statistics {tuple(stats.shape)} for {R} rows")
+    _call("norm", "mlxb_row_stats", _STATS_ARGS, _p(x), _p(stats), R, D, _rows(x, "row_stats x"), eps, stream)
+
+
 # --------------------------------------------------------------------------
 # linear layers
 
@@ -217,11 +231,26 @@ _SMALLM_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, 
 
 SMALL_M = 64
 
+_SMALLM_FOLD_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                     c_void_p, c_float, c_void_p]
 
-def linear_few_rows(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=None) -> None:
+
+def _fold_args(fold, N: int, what: str):
+    colsum, eps = fold
+    _need(colsum, torch.float32, what + " column sums")
+    if colsum.numel() != N or not colsum.is_contiguous():
+        raise KernelError(f"{what}: {colsum.numel()} column sums for {N} outputs")
+    return colsum, float(eps)
+
+
+def linear_few_rows(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=None, fold=None) -> None:
     """``linear_generic``'s contract for bfloat16 and at most 64 rows: the weight is streamed from HBM once
-    with 16-byte loads and multiplied on the tensor cores (csrc/gemm_smallm.cu).  ``K`` and the row stride of
-    ``x`` must be multiples of 8."""
+    with 16-byte loads and multiplied on the tensor cores (csrc/gemm_smallm.cuh).  ``K`` and the row stride of
+    ``x`` must be multiples of 8.
+
+    ``fold = (colsum, eps)``: ``x`` holds the rows before a LayerNorm that has been folded into ``w`` and ``bias``
+    (``parts.linear.Linear.fold_norm``); the kernel computes ``rstd (x w^T - mean colsum) + bias`` with the
+    rows' mean and 1/std found on the way."""
     _need(x, torch.bfloat16, "linear x")
     _need(w, torch.bfloat16, "linear w")
     M, K = x.shape
@@ -239,6 +268,11 @@ def linear_few_rows(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=
         _need(residual, torch.bfloat16, "linear residual")
         if residual.shape != out.shape or _rows(residual, "linear residual") != ldc:
             raise KernelError("linear: residual must have the output's shape and row stride")
+    if fold is not None:
+        colsum, eps = _fold_args(fold, N, "linear")
+        _call("gemm_smallm_fold", "mlxb_linear_smallm_fold", _SMALLM_FOLD_ARGS, int(out.dtype == torch.float32), _p(x),
+              _p(w), _p(bias), _p(residual), _p(out), M, N, K, lda, ldc, epilogue, _p(colsum), eps, stream)
+        return
     _call("gemm_smallm", "mlxb_linear_smallm", _SMALLM_ARGS, int(out.dtype == torch.float32), _p(x), _p(w), _p(bias),
           _p(residual), _p(out), M, N, K, lda, ldc, epilogue, stream)
 
@@ -247,10 +281,16 @@ _TC_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_in
             c_void_p, c_void_p]
 
 
-def linear_tensor_cores(x, w, bias, out, status, stream, epilogue: int = EPI_NONE, residual=None) -> None:
+_TC_FOLD_ARGS = _TC_ARGS[:-1] + [c_void_p, c_void_p, c_void_p]
+
+
+def linear_tensor_cores(x, w, bias, out, status, stream, epilogue: int = EPI_NONE, residual=None, fold=None) -> None:
     """``linear_generic``'s contract for bfloat16 and many rows, on tcgen05 tensor cores with TMA-fed
     shared-memory stages and the accumulator in tensor memory (csrc/gemm_tcgen05.cu).  ``K`` and the row
-    stride of ``x`` must be multiples of 8.  ``status`` receives ``ST_WAIT_TIMEOUT`` if a bounded wait gives up."""
+    stride of ``x`` must be multiples of 8.  ``status`` receives ``ST_WAIT_TIMEOUT`` if a bounded wait gives up.
+
+    ``fold = (colsum, stats)``: a LayerNorm folded into ``w`` and ``bias``; ``x`` holds the rows before the norm
+    and ``stats`` their ``(mean, rstd)`` from ``row_stats``."""
     _need(x, torch.bfloat16, "linear x")
     _need(w, torch.bfloat16, "linear w")
     M, K = x.shape
@@ -268,6 +308,15 @@ def linear_tensor_cores(x, w, bias, out, status, stream, epilogue: int = EPI_NON
         _need(residual, torch.bfloat16, "linear residual")
         if residual.shape != out.shape or _rows(residual, "linear residual") != ldc:
             raise KernelError("linear: residual must have the output's shape and row stride")
+    if fold is not None:
+        colsum, stats = fold
+        _need(colsum, torch.float32, "linear column sums")
+        _need(stats, torch.float32, "linear row statistics")
+        if colsum.numel() != N or stats.shape != (M, 2) or not stats.is_contiguous():
+            raise KernelError(f"linear: {colsum.numel()} column sums, statistics {tuple(stats.shape)} for {M} x {N}")
+        _call("gemm_tcgen05", "mlxb_linear_tcgen05_fold", _TC_FOLD_ARGS, int(out.dtype == torch.float32), _p(x), _p(w),
+              _p(bias), _p(residual), _p(out), M, N, K, lda, ldc, epilogue, _p(status), _p(colsum), _p(stats), stream)
+        return
     _call("gemm_tcgen05", "mlxb_linear_tcgen05", _TC_ARGS, int(out.dtype == torch.float32), _p(x), _p(w), _p(bias),
           _p(residual), _p(out), M, N, K, lda, ldc, epilogue, _p(status), stream)
 
@@ -276,12 +325,17 @@ _QKV_ARGS = [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
              c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
 
 
+_QKV_FOLD_ARGS = _QKV_ARGS[:-1] + [c_void_p, c_float, c_void_p]
+_QKV_TC_FOLD_ARGS = _QKV_ARGS[:-1] + [c_void_p, c_void_p, c_void_p]
+
+
 def linear_qkv_to_cache(x, w, bias, out, positions, token_req, block_table, k_pool, v_pool, q_width: int, status,
-                        stream) -> None:
+                        stream, fold=None) -> None:
     """The fused ``[q | k | v]`` projection of bfloat16 rows with the cache write in its epilogue: query columns
     go to ``out[:, :q_width]``, key and value columns straight into the pages ``[n_pages, Hkv, page, Dh]`` (the
     other columns of ``out`` are not written).  Up to 64 rows run in the weight-streaming kernel, more in the
-    tcgen05 kernel."""
+    tcgen05 kernel.  ``fold``: ``(colsum, eps)`` as in ``linear_few_rows`` for up to 64 rows, ``(colsum, stats)`` as
+    in ``linear_tensor_cores`` for more."""
     _need(x, torch.bfloat16, "linear x")
     _need(w, torch.bfloat16, "linear w")
     _need(out, torch.bfloat16, "linear out")
@@ -295,6 +349,23 @@ def linear_qkv_to_cache(x, w, bias, out, positions, token_req, block_table, k_po
         raise KernelError(f"linear (q|k|v): {N} outputs for {q_width} query columns and pools {tuple(k_pool.shape)}")
     if bias is not None:
         _need(bias, torch.float32, "linear bias")
+    if fold is not None and M > SMALL_M:
+        colsum, stats = fold
+        _need(colsum, torch.float32, "linear column sums")
+        if not torch.is_tensor(stats) or stats.dtype != torch.float32 or stats.shape != (M, 2) or not stats.is_contiguous():
+            raise KernelError(f"linear (q|k|v): more than {SMALL_M} rows need float32 row statistics [{M}, 2]")
+        _call("gemm_tcgen05", "mlxb_linear_tcgen05_qkv_fold", _QKV_TC_FOLD_ARGS, _p(x), _p(w), _p(bias), _p(out), M, N, K,
+              _rows(x, "linear x"), _rows(out, "linear out"), _p(positions), _p(token_req), _p(block_table),
+              block_table.shape[1], n_pages, page, Hkv, Dh, q_width, _p(k_pool), _p(v_pool), _p(status), _p(colsum),
+              _p(stats), stream)
+        return
+    if fold is not None:
+        colsum, eps = _fold_args(fold, N, "linear (q|k|v)")
+        _call("gemm_smallm_fold", "mlxb_linear_smallm_qkv_fold", _QKV_FOLD_ARGS, _p(x), _p(w), _p(bias), _p(out), M, N, K,
+              _rows(x, "linear x"), _rows(out, "linear out"), _p(positions), _p(token_req), _p(block_table),
+              block_table.shape[1], n_pages, page, Hkv, Dh, q_width, _p(k_pool), _p(v_pool), _p(status), _p(colsum), eps,
+              stream)
+        return
     lib, fn = ("gemm_smallm", "mlxb_linear_smallm_qkv") if M <= SMALL_M else ("gemm_tcgen05", "mlxb_linear_tcgen05_qkv")
     _call(lib, fn, _QKV_ARGS, _p(x), _p(w), _p(bias), _p(out), M, N, K,
           _rows(x, "linear x"), _rows(out, "linear out"), _p(positions), _p(token_req), _p(block_table),

@@ -106,6 +106,35 @@ class Norm(Part):
     def forward(self, ctx, x, rows=None):
         raise NotImplementedError
 
+    def fold_args(self):
+        """``(gain, bias, eps)`` if this is a LayerNorm (mean and variance over the row, gain, optional bias)
+        that a linear layer can fold into its weights, else None."""
+        return None
+
+    def deferred(self, ctx, x, rows=None, tag: str = "normed") -> "Normed":
+        """This norm of ``x`` as a value that is computed when (and if) somebody asks for the tensor."""
+        return Normed(ctx, self, x, rows, tag)
+
+
+class Normed:
+    """The output of a norm that has not run yet.  A consumer that has folded the norm into its own weights
+    (``Linear.fold_norm``) takes ``source``, the rows before the norm, and saves the norm's kernel; any other
+    consumer calls ``tensor()``, which runs the norm once.  A block hands a ``Normed`` only to a mixer or
+    feed-forward whose ``fold_input_norm`` said yes when the weights were bound; parts that do not know this
+    class never see it."""
+
+    def __init__(self, ctx, norm: Norm, source: torch.Tensor, rows, tag: str):
+        self.ctx, self.norm, self.source, self.rows, self.tag = ctx, norm, source, rows, tag
+        n = source.shape[0] if rows is None else rows.numel()
+        self.shape = (n, source.shape[1])
+        self.dtype = source.dtype
+        self._tensor: Optional[torch.Tensor] = None
+
+    def tensor(self) -> torch.Tensor:
+        if self._tensor is None:
+            self._tensor = self.norm.forward(self.ctx, self.source, rows=self.rows, tag=self.tag)
+        return self._tensor
+
 
 class PositionEncoding(Part):
     max_positions: Optional[int] = None
@@ -118,6 +147,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    def fold_input_norm(self, norm: Norm) -> bool:
+        """Called once the weights are bound: may this part be given the rows before ``norm`` (as a ``Normed``)
+        instead of the normed tensor?  True only if it applies the norm itself."""
+        return False
+
     def cache_spec(self):
         return None
 
@@ -126,6 +160,9 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    def fold_input_norm(self, norm: Norm) -> bool:
+        return False
+
     def forward(self, ctx, x, residual):
         raise NotImplementedError
 

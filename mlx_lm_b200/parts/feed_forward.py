@@ -23,6 +23,9 @@ class MLP(FeedForward):
     def children(self):
         return (self.up, self.down)
 
+    def fold_input_norm(self, norm) -> bool:
+        return self.up.fold_norm(norm)
+
     def forward(self, ctx, x, residual):
         h = self.up.forward(ctx, x, ctx.ws.get("ffn_hidden", x.shape[0], self.inner, x.dtype),
                             activation=self.activation)

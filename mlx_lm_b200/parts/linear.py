@@ -9,19 +9,20 @@ activation and the residual add run in the kernel's epilogue.
 
 from __future__ import annotations
 
+from types import SimpleNamespace
 from typing import List, Optional
 
 import torch
 
 from .. import ops
-from .base import MATRIX, VECTOR, Init, ParamSpec, Part
+from .base import MATRIX, VECTOR, Init, Normed, ParamSpec, Part
 
 ACTIVATIONS = {None: ops.EPI_NONE, "none": ops.EPI_NONE, "gelu_new": ops.EPI_GELU_NEW}
 
 
 class Linear(Part):
     replayable = True
-    kernel_libs = ("gemm_simt", "gemm_smallm", "gemm_tcgen05")
+    kernel_libs = ("gemm_simt", "gemm_smallm", "gemm_smallm_fold", "gemm_tcgen05")
 
     def __init__(self, name: str, n_in: int, n_out: int, bias: bool = True, stored: str = "out_in",
                  weight_suffix: str = ".weight", init: Init = Init(), bias_init: Init = Init()):
@@ -32,6 +33,7 @@ class Linear(Part):
         self.init, self.bias_init = init, bias_init
         self.weight: Optional[torch.Tensor] = None
         self.bias: Optional[torch.Tensor] = None
+        self.folded = None        # see fold_norm
 
     def param_specs(self) -> List[ParamSpec]:
         shape = (self.n_out, self.n_in) if self.stored == "out_in" else (self.n_in, self.n_out)
@@ -51,21 +53,63 @@ class Linear(Part):
         """Share another part's ``[out, in]`` tensor (a tied output head)."""
         self.weight = weight
 
+    def fold_norm(self, norm) -> bool:
+        """Fold the LayerNorm that feeds this layer into its weights:
+        ``LayerNorm(x) W^T + b = rstd (x W'^T - mean colsum) + b'`` with ``W' = W diag(gain)`` (rounded to
+        bfloat16 once, here), ``colsum = W' 1`` and ``b' = b + W norm_bias``.  The layer then takes the rows
+        before the norm (a ``Normed``): the products run on them as they are and the epilogue applies mean and
+        1/std, which the few-rows kernel finds from the fragments it loads anyway (csrc/gemm_smallm.cuh) and
+        which for more rows come from a statistics kernel (``ops.row_stats``).  ``W'`` replaces ``W``: every
+        step, of few rows or many, goes through the same weights and the same arithmetic."""
+        args = norm.fold_args()
+        w = self.weight
+        if args is None or w is None or w.dtype != torch.bfloat16 or self.n_in % 8 or self.folded is not None:
+            return False
+        gain, nbias, eps = args
+        w32 = w.float()
+        folded = (w32 * gain.float()[None, :]).to(torch.bfloat16)
+        bias = self.bias.float().clone() if self.bias is not None else torch.zeros(self.n_out, device=w.device)
+        if nbias is not None:
+            bias += w32 @ nbias.float()
+        self.folded = SimpleNamespace(norm=norm, colsum=folded.float().sum(dim=1).contiguous(), eps=float(eps))
+        self.weight, self.bias = folded, bias.contiguous()
+        return True
+
+    def fold_of(self, ctx, x: Normed):
+        """The ``fold`` argument of the kernels for this step's rows."""
+        f, src = self.folded, x.source
+        if (f is None or f.norm is not x.norm or x.rows is not None or src.stride(1) != 1 or src.stride(0) % 8
+                or src.data_ptr() % 16):
+            raise ops.KernelError(f"{self.name}: the norm before this layer is folded into its weights; it takes "
+                                  f"the rows before that norm, contiguous and 16-byte aligned")
+        if x.shape[0] <= ops.SMALL_M:
+            return (f.colsum, f.eps)
+        stats = ctx.ws.get("row_stats", x.shape[0], 2, torch.float32)
+        ops.row_stats(src, stats, f.eps, ctx.stream)
+        return (f.colsum, stats)
+
     def forward(self, ctx, x, out, activation=None, residual=None) -> torch.Tensor:
         """float32: the generic kernel (true 32-bit arithmetic).  bfloat16: the weight-streaming kernel for up
         to 64 rows, the tcgen05 kernel for more; an inner size that is no multiple of 8 (no 16-byte rows)
         goes to the generic kernel."""
         epi = ACTIVATIONS[activation]
+        fold = None
+        if isinstance(x, Normed):
+            fold = self.fold_of(ctx, x)
+            x = x.source
+        elif self.folded is not None:
+            raise ops.KernelError(f"{self.name}: the norm before this layer is folded into its weights; it takes a "
+                                  f"Normed, not a tensor")
         fast = (x.dtype == torch.bfloat16 and self.n_in % 8 == 0 and x.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0)
         few = x.shape[0] <= ops.SMALL_M
         if few and x.shape[0] > 32 and self.n_out >= 16384:
             few = False       # a vocabulary-sized output at 33-64 rows: measured faster on the tcgen05 kernel
         if fast and few:
-            ops.linear_few_rows(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual)
+            ops.linear_few_rows(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual, fold=fold)
         elif fast:
             ops.linear_tensor_cores(x, self.weight, self.bias, out, ctx.status, ctx.stream, epilogue=epi,
-                                    residual=residual)
+                                    residual=residual, fold=fold)
         else:
             ops.linear_generic(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual)
         return out

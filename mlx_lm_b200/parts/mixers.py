@@ -17,7 +17,7 @@ from typing import List, Optional
 import torch
 
 from .. import ops
-from .base import Init, Mixer, PagedKVSpec, PositionEncoding, register_part
+from .base import Init, Mixer, Normed, PagedKVSpec, PositionEncoding, register_part
 from .linear import Linear
 
 
@@ -49,16 +49,22 @@ class Attention(Mixer):
     def cache_spec(self):
         return PagedKVSpec(self.n_kv_heads, self.head_dim, self.window)
 
+    def fold_input_norm(self, norm) -> bool:
+        return self.qkv.fold_norm(norm)
+
     def forward(self, ctx, x, residual, cache):
         T = x.shape[0]
         qkv = ctx.ws.get("qkv", T, self.q_width + 2 * self.kv_width, x.dtype)
         q = qkv[:, :self.q_width]
+        src = x.source if isinstance(x, Normed) else x      # a Normed: the norm is folded into the projection
         if (cache.write and self.position is None and x.dtype == torch.bfloat16 and self.width % 8 == 0
-                and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
+                and src.stride(0) % 8 == 0 and src.data_ptr() % 16 == 0):
             # nothing to do to q and k before the cache: the projection's epilogue puts keys and values
             # into the pages itself
-            ops.linear_qkv_to_cache(x, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, ctx.token_req,
-                                    cache.block_table, cache.k, cache.v, self.q_width, ctx.status, ctx.stream)
+            fold = self.qkv.fold_of(ctx, x) if isinstance(x, Normed) else None
+            ops.linear_qkv_to_cache(src, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, ctx.token_req,
+                                    cache.block_table, cache.k, cache.v, self.q_width, ctx.status, ctx.stream,
+                                    fold=fold)
         else:
             self.qkv.forward(ctx, x, qkv)
             k = qkv[:, self.q_width:self.q_width + self.kv_width]

@@ -30,6 +30,9 @@ class LayerNorm(Norm):
         self.gain = tensors[self.name + ".weight"]
         self.bias = tensors[self.name + ".bias"] if self.has_bias else None
 
+    def fold_args(self):
+        return (self.gain, self.bias, self.eps)
+
     def forward(self, ctx, x, rows=None, tag: str = "normed"):
         n = x.shape[0] if rows is None else rows.numel()
         out = ctx.ws.get(tag, n, self.width, x.dtype)

@@ -234,7 +234,7 @@ def test_decode_as_a_cuda_graph_equals_the_eager_step(dtype, tmp_path):
 
 
 @pytest.mark.parametrize("config,seed,lens", [(CONFIG_A, 21, (5, 40, 17)), (CONFIG_B, 22, (90, 3, 33, 64, 12))])
-def test_decode_step_as_one_persistent_kernel(config, seed, lens, tmp_path):
+def test_decode_step_as_one_persistent_kernel(config, seed, lens, tmp_path, monkeypatch):
     """The opt-in path that runs a whole decode step as one cooperative kernel over a table of phases
     (csrc/decode_program.cu): its logits are those of the plain implementation, step after step, over page
     edges, for a batch smaller than its bucket, and the barrier words survive many launches."""
@@ -243,6 +243,8 @@ def test_decode_step_as_one_persistent_kernel(config, seed, lens, tmp_path):
     from mlx_lm_b200.sampling import Sampler
     from mlx_lm_b200.sampling.device import DeviceSampler
     from mlx_lm_b200.weights import load_model
+    import mlx_lm_b200.parts.block as block
+    monkeypatch.setattr(block, "FOLD_NORMS", False)    # the program has phases for the plain kernels only
     weights = make_model_dir(str(tmp_path), dict(config, ln_gain_std=0.3), seed, peaky=6.0)
     model, _ = load_model(str(tmp_path), dtype="bfloat16")
     n_steps = 36
