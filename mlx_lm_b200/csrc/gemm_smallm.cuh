@@ -63,6 +63,12 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], unsigned a0, unsigned a1
 // so the products run on the rows as they are, with no pass over them beforehand, and the rows' mean and
 // 1/std are only needed in the epilogue.  Every thread adds up x and x^2 of the activation fragments it loads
 // anyway; the sums are completed across the CTA together with the partial products.
+// Accuracy: the variance comes from one pass, E[x^2] - mean^2 in float32, whose relative error grows like
+// 1e-7 (mean/std)^2; and the epilogue's difference sum - mean * colsum amplifies the rounding of the
+// accumulation by about |mean|/std as well.  Both stay below bfloat16 resolution while |mean| is not more
+// than a hundred times the row's spread, which bfloat16 rows can hardly exceed (three significant digits)
+// and the inputs of a transformer's norms do not come near.  (Taking the variance about the row's first
+// element instead was measured: 6 % more time per decode step for accuracy the difference above does not keep.)
 struct NormFold {
   const float* colsum;   // [N], null: no fold
   float eps;

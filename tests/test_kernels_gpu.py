@@ -76,6 +76,61 @@ def test_layernorm(ops, dtype, R_, D, eps):
     assert rel_err(out3, R.layernorm(x.cpu(), gain.cpu(), bias.cpu(), eps, rows.cpu())) <= tol(dtype, 2e-6, 4e-3)
 
 
+@pytest.mark.parametrize("R_,D,shift", [(1, 64, 0.0), (33, 96, 1.5), (130, 1600, 40.0), (5, 4096, -3.0)])
+def test_row_stats(ops, R_, D, shift):
+    g = torch.Generator().manual_seed(D + 1)
+    x = (torch.randn(R_, D, generator=g) * 3 + shift).to(torch.bfloat16).cuda()
+    stats = torch.empty(R_, 2, device="cuda")
+    ops.row_stats(x, stats, 1e-5, stream())
+    xd = x.cpu().double()
+    mean = xd.mean(dim=1)
+    rstd = (xd.var(dim=1, unbiased=False) + 1e-5).rsqrt()
+    assert float((stats[:, 0].cpu().double() - mean).abs().max()) <= 1e-5 * max(1.0, abs(shift))
+    assert float((stats[:, 1].cpu().double() / rstd - 1).abs().max()) <= 1e-5
+
+
+@pytest.mark.parametrize("M,N,K,shift", [(1, 200, 96, 0.0), (7, 1000, 320, 1.5), (16, 72, 1600, 40.0), (33, 200, 96, -2.0),
+                                         (64, 1000, 320, 0.5), (200, 264, 96, 1.5), (130, 1000, 1600, 40.0)])
+def test_linear_with_folded_norm(ops, M, N, K, shift):
+    """LayerNorm folded into the weights (parts.linear.Linear.fold_norm): the few-rows kernel (statistics from its
+    own fragments) and the tcgen05 kernel (statistics from row_stats) against LayerNorm followed by the linear
+    layer, with gelu and a residual, for rows whose mean is far from zero too."""
+    from types import SimpleNamespace
+    from mlx_lm_b200.parts.linear import Linear
+    from mlx_lm_b200.parts.norms import LayerNorm
+    g = torch.Generator().manual_seed(M + N + K)
+    x = (torch.randn(M, K, generator=g) * 3 + shift).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    b = torch.randn(N, generator=g)
+    gain = torch.randn(K, generator=g) * 0.3 + 1
+    nbias = torch.randn(K, generator=g) * 0.2
+    res = torch.randn(M, N, generator=g).to(torch.bfloat16)
+    eps = 1e-5
+    norm = LayerNorm("ln", K, eps)
+    norm.bind({"ln.weight": gain.cuda(), "ln.bias": nbias.cuda()}, torch.bfloat16, "cuda")
+    lin = Linear("fc", K, N)
+    lin.bind({"fc.weight": w.cuda(), "fc.bias": b.cuda()}, torch.bfloat16, "cuda")
+    assert lin.fold_norm(norm)
+    ws = {}
+    def get(tag, rows, cols, dtype):
+        return ws.setdefault(tag, torch.zeros(rows, cols, dtype=dtype, device="cuda"))
+    ctx = SimpleNamespace(stream=stream(), status=torch.zeros(1, dtype=torch.int32, device="cuda"),
+                          ws=SimpleNamespace(get=get))
+    normed = R.layernorm(x, gain, nbias, eps)
+    for act, residual in ((None, None), ("gelu_new", None), (None, res)):
+        out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+        r_dev = None
+        if residual is not None:
+            out.copy_(residual)          # in place, as the blocks use it
+            r_dev = out
+        lin.forward(ctx, norm.deferred(ctx, x.cuda()), out, activation=act, residual=r_dev)
+        ref = R.linear(normed, w, b, act, residual)
+        assert rel_err(out, ref) <= 8e-3, (act, residual is not None)
+    assert int(ctx.status.item()) == 0
+    with pytest.raises(ops.KernelError):     # the folded layer no longer takes the normed tensor itself
+        lin.forward(ctx, normed.to(torch.bfloat16).cuda(), torch.zeros(M, N, dtype=torch.bfloat16, device="cuda"))
+
+
 def test_layernorm_constant_row_and_large_mean(ops):
     # a row with a large mean and tiny spread: a one-pass variance (E[x^2]-E[x]^2) would lose it
     x = (1000.0 + torch.arange(256).float().remainder(2) * 0.5).repeat(2, 1).cuda()
