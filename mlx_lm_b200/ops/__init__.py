@@ -26,7 +26,8 @@ EPI_NONE, EPI_GELU_NEW = 0, 1
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 # kernel sources that only a bfloat16 run launches from: a float32 run neither compiles nor loads them
-BF16_ONLY_LIBS = frozenset({"gemm_smallm", "gemm_smallm_fold", "gemm_tcgen05", "attention_prefill"})
+BF16_ONLY_LIBS = frozenset({"gemm_smallm", "gemm_smallm_fold", "gemm_tcgen05", "attention_prefill",
+                            "attention_prefill_tc"})
 
 # status word bits set by kernels (csrc/common.cuh)
 ST_TOKEN_RANGE, ST_POSITION_RANGE, ST_PAGE_RANGE, ST_WAIT_TIMEOUT = 1, 2, 4, 8
@@ -428,7 +429,11 @@ _PRE_ARGS = [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_
 
 import os as _os
 
-PREFILL_TILE = int(_os.environ.get("MLXB_PREFILL_TILE", "64"))   # queries per CTA of the attention kernel for portions
+PREFILL_TILE = int(_os.environ.get("MLXB_PREFILL_TILE", "128"))   # queries per CTA of the attention kernels for portions
+PREFILL_TC = _os.environ.get("MLXB_PREFILL_TC", "1") != "0"         # heads of 64 in tiles of 128 on the tcgen05 kernel
+
+_PRE_TC_ARGS = [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
 
 
 def attention_portions_supported(dtype, head_dim: int) -> bool:
@@ -446,6 +451,13 @@ def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out,
     if tiles.numel() < 4 * n_tiles:
         raise KernelError(f"attention_portions: {tiles.numel()} integers for {n_tiles} tiles")
     tile_rows = tile_rows or PREFILL_TILE
+    ldq, ldo = _rows(q, "attention q"), _rows(out, "attention out")
+    if (PREFILL_TC and Dh == 64 and tile_rows == 128 and 8 <= page <= 128 and page & (page - 1) == 0
+            and ldq % 8 == 0 and ldo % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
+        _call("attention_prefill_tc", "mlxb_attention_prefill_tc", _PRE_TC_ARGS, _p(q), ldq, q.shape[0], _p(tiles),
+              n_tiles, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale,
+              _p(k_pool), _p(v_pool), _p(out), ldo, _p(status), stream)
+        return
     _call("attention_prefill", "mlxb_attention_prefill", _PRE_ARGS, _p(q), _rows(q, "attention q"), _p(tiles), n_tiles,
           tile_rows, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
           _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream)

@@ -23,7 +23,7 @@ from .linear import Linear
 
 class Attention(Mixer):
     replayable = True
-    kernel_libs = ("attention", "attention_prefill")
+    kernel_libs = ("attention", "attention_prefill", "attention_prefill_tc")
 
     def __init__(self, name: str, width: int, n_heads: int, head_dim: int, n_kv_heads: Optional[int] = None,
                  window: Optional[int] = None, bias: bool = True, stored: str = "out_in",
