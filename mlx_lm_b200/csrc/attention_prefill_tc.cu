@@ -215,11 +215,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     constexpr uint32_t idesc_s = umma_idesc(TQ, TK, false);
     constexpr uint32_t idesc_o = umma_idesc(TQ, HD, true);
     const uint32_t tmem_s = tmem_base, tmem_o = tmem_base + 128;
-    bool ok = mbar_wait(&sm.q_full, 0, abort_flag);
-    for (int i = 0; i < n_blocks && ok; ++i) {
-      const uint32_t ph = (uint32_t)(i & 1);
-      if (!(ok = mbar_wait(&sm.k_full, ph, abort_flag))) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    // S of a block needs only its keys and the S columns, which the softmax threads give back with P; so
+    // S(i + 1) is issued right behind P V(i) and is ready when the softmax threads come back from accumulating O.
+    auto issue_s = [&]() {
       if (lane == 0) {
         const uint64_t da = umma_desc(smem_u32(sm.q), 16), db = umma_desc(smem_u32(sm.k), 16);
 #pragma unroll
@@ -228,10 +226,19 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         umma_commit(&sm.s_full);
       }
       __syncwarp();
-      if (!(ok = mbar_wait(&sm.s_full, ph, abort_flag))) break;    // S is there: the K block is free
-      if (i + 1 < n_blocks) load_pages(&map_k, sm.k, &sm.k_full, pg_next);
+    };
+    bool ok = mbar_wait(&sm.q_full, 0, abort_flag) && mbar_wait(&sm.k_full, 0, abort_flag);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      issue_s();
+    }
+    for (int i = 0; i < n_blocks && ok; ++i) {
+      const uint32_t ph = (uint32_t)(i & 1);
+      const bool more = i + 1 < n_blocks;
+      if (!(ok = mbar_wait(&sm.s_full, ph, abort_flag))) break;    // S(i) is there: the K block is free
+      if (more) load_pages(&map_k, sm.k, &sm.k_full, pg_next);
       if (!(ok = mbar_wait(&sm.v_full, ph, abort_flag))) break;
-      if (!(ok = mbar_wait(&sm.p_full, ph, abort_flag))) break;
+      if (!(ok = mbar_wait(&sm.p_full, ph, abort_flag))) break;    // P(i) is written, S(i) has been read
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (lane == 0) {
 #pragma unroll
@@ -244,9 +251,15 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         umma_commit(&sm.o_full);
       }
       __syncwarp();
-      if (!(ok = mbar_wait(&sm.o_full, ph, abort_flag))) break;    // O_b is there: V and P are free
-      if (i + 1 < n_blocks) load_pages(&map_v, sm.v, &sm.v_full, pg_next);
-      pg_next = page_of(kb_lo + i + 2);
+      if (more) {
+        if (!(ok = mbar_wait(&sm.k_full, ph ^ 1u, abort_flag))) break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        issue_s();
+      }
+      const int pg_after = page_of(kb_lo + i + 2);                 // its latency hides behind the wait below
+      if (!(ok = mbar_wait(&sm.o_full, ph, abort_flag))) break;    // O_b(i) is there: V and P are free
+      if (more) load_pages(&map_v, sm.v, &sm.v_full, pg_next);
+      pg_next = pg_after;
     }
   } else {
     // softmax: thread (half, r) owns keys [64 half, 64 half + 64) of every block and output dims

@@ -436,7 +436,8 @@ def make_tiles(lens, new, tile=64):
 @pytest.mark.parametrize("tile", [64, 128])
 @pytest.mark.parametrize("Hq,Hkv,Dh,page,window", [(4, 4, 16, 16, 0), (3, 3, 32, 16, 0), (6, 2, 48, 32, 0),
                                                     (5, 1, 80, 64, 0), (2, 2, 128, 16, 40), (8, 4, 64, 16, 17),
-                                                    (16, 16, 64, 16, 0), (2, 1, 96, 16, 100), (1, 1, 112, 32, 0)])
+                                                    (16, 16, 64, 16, 0), (2, 1, 96, 16, 100), (1, 1, 112, 32, 0),
+                                                    (4, 2, 64, 32, 0), (2, 2, 64, 128, 50), (3, 1, 64, 8, 0)])
 def test_attention_portions(ops, Hq, Hkv, Dh, page, window, tile):
     """The tensor-core kernel on the portions of a mixed step (single-token requests are left to the other
     kernel): portions that start at position 0, that continue long contexts, that end inside a tile, of two tokens."""
@@ -460,9 +461,11 @@ def test_attention_portions(ops, Hq, Hkv, Dh, page, window, tile):
     assert float(out[single].float().abs().max()) == 0.0
 
 
-def test_attention_portions_sees_each_key_once(ops):
+@pytest.mark.parametrize("tile", [64, 128])
+def test_attention_portions_sees_each_key_once(ops, tile):
     """Values that encode their own position and sharp queries: query i picks key (i * 7) % (i + 1) exactly, at
-    every offset inside tiles, blocks and pages; a key counted twice, skipped or taken from the wrong page shows."""
+    every offset inside tiles, blocks and pages; a key counted twice, skipped or taken from the wrong page shows.
+    (Tiles of 64: the mma.sync kernel; tiles of 128 with heads of 64: the tcgen05 kernel.)"""
     Hq = Hkv = 1
     Dh, page, n = 64, 16, 333
     c = paged_case(torch.bfloat16, lens=[0], new=[n], Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=0)
@@ -476,10 +479,10 @@ def test_attention_portions_sees_each_key_once(ops):
     c["qkv"][:, :Dh] = (code[target] * 2.0).to(torch.bfloat16)        # score 4*64*scale=32 on the target, ~0 elsewhere
     dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    tiles = make_tiles([0], [n]).cuda()
+    tiles = make_tiles([0], [n], tile).cuda()
     out = torch.zeros(n, Dh, dtype=torch.bfloat16, device="cuda")
     ops.attention_portions(dev["qkv"][:, :Dh], tiles, tiles.numel() // 4, dev["bt"], dev["k_pool"], dev["v_pool"], out,
-                           Hq, Dh ** -0.5, 0, status, stream(), tile_rows=64)
+                           Hq, Dh ** -0.5, 0, status, stream(), tile_rows=tile)
     got = out.float().cpu()
     for i in range(n):
         j = target[i]
