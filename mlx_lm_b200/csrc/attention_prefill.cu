@@ -21,8 +21,8 @@
 // The order in which a query's keys are added depends only on its position: blocks of 64 positions
 // from block 0 (or the window's first block) upward, even and odd blocks apart, then the two merged.
 //
-// (tcgen05 has no place here yet: with 64-wide heads the softmax, not the products, is the long pole
-// of this kernel; the linear layers, which carry 92 % of a prompt's flops, use tcgen05.)
+// (Heads of 64 in tiles of 128 queries run on the tcgen05 kernel of attention_prefill_tc.cu instead; this one
+// serves every other head size that is a multiple of 16, and tiles of 64.)
 #include "common.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
