@@ -229,27 +229,30 @@ def run_ours(args):
         print(json.dumps({"only": "decode", "batch": B, "ms_per_step": round(ms, 4), "launches_per_step": launches}))
         return
 
-    # ---- prefill: 2 x 1024 tokens in one step
+    # ---- prefill: 2 x 1024 tokens in one step (more prompts only with --only prefill --prefill-prompts N)
+    n_pf = args.prefill_prompts if args.only == "prefill" else 2
+    if not 1 <= n_pf <= max_b:
+        raise SystemExit(f"--prefill-prompts {n_pf}: 1 to {max_b}")
     g = torch.Generator().manual_seed(1)
-    prompts = [torch.randint(0, vocab, (1024,), generator=g).tolist() for _ in range(2)]
+    prompts = [torch.randint(0, vocab, (1024,), generator=g).tolist() for _ in range(n_pf)]
     times = []
     for it in range(4):
-        for i in range(2):
+        for i in range(n_pf):
             engine.add_request(("pf", i))
         torch.cuda.synchronize()
         s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         s.record()
-        engine.step([StepEntry(("pf", i), prompts[i], [1023]) for i in range(2)])
+        engine.step([StepEntry(("pf", i), prompts[i], [1023]) for i in range(n_pf)])
         e.record()
         torch.cuda.synchronize()
         times.append(s.elapsed_time(e))
-        for i in range(2):
+        for i in range(n_pf):
             engine.finish(("pf", i))
     pf_ms = min(times[1:])
     D, L = cfg["n_embd"], cfg["n_layer"]
-    attn_flops = 2 * L * 4 * D * (1024 * 1025 // 2)          # QK^T and PV over the causal half, two prompts
-    pf_flops = 2048 * lin_flops + attn_flops + 2 * 2 * D * vocab
-    prefill = {"value": round(2048 / (pf_ms / 1e3), 1), "tokens": 2048, "ms": round(pf_ms, 4),
+    attn_flops = n_pf * L * 4 * D * (1024 * 1025 // 2)       # QK^T and PV over the causal half of every prompt
+    pf_flops = n_pf * 1024 * lin_flops + attn_flops + n_pf * 2 * D * vocab
+    prefill = {"value": round(n_pf * 1024 / (pf_ms / 1e3), 1), "tokens": n_pf * 1024, "ms": round(pf_ms, 4),
                "frac": round(pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
     if args.only == "prefill":
         print(json.dumps({"only": "prefill", **prefill}))
@@ -321,6 +324,8 @@ def main():
                     help="run just this part and print its figures (decode / prefill: short runs for profiling; "
                          "mixed: 64 requests with prompts of 16..1024 tokens through the scheduler, 256-token portions "
                          "beside decoding requests)")
+    ap.add_argument("--prefill-prompts", type=int, default=2,
+                    help="with --only prefill: 1024-token prompts in the one step (the contract's figure is 2)")
     ap.add_argument("--size", default="medium", choices=sorted(SIZES), help="layer sizes: GPT-2 medium, large or XL")
     a = ap.parse_args()
     if a.impl == "reference":
