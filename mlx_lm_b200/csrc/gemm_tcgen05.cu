@@ -137,6 +137,14 @@ struct NormFoldRows {
 
 __device__ __forceinline__ void unfold8(float (&v)[8], int n8, int N, const float* __restrict__ colsum, float mean,
                                         float rstd) {
+  if (n8 + 8 <= N && (((uintptr_t)(colsum + n8)) & 15) == 0) {   // the same 32 bytes for every lane: two broadcast loads
+    const float4 c0 = *reinterpret_cast<const float4*>(colsum + n8), c1 = *reinterpret_cast<const float4*>(colsum + n8 + 4);
+    const float cs[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+    const float nm = -mean * rstd;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = fmaf(nm, cs[i], rstd * v[i]);
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < 8; ++i)
     if (n8 + i < N) v[i] = rstd * (v[i] - mean * colsum[n8 + i]);
