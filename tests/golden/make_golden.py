@@ -143,7 +143,9 @@ CFG = dict(model_type="gpt2", n_ctx=64, n_embd=48, n_head=3, n_layer=2, n_positi
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py <checkout of ml-explore/mlx-lm>")
+    ref_root = sys.argv[1]
     install_stand_in(ref_root)
     gpt2 = importlib.import_module("mlx_lm.models.gpt2")
     cache_mod = importlib.import_module("mlx_lm.models.cache")
