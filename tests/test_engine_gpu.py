@@ -141,6 +141,36 @@ def test_long_decoding_and_first_tokens(dtype, config, seed, tmp_path):
     assert eng.cache.pages_in_use() == [0]
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width,heads", [(1600, 25), (1280, 20)])
+def test_layer_sizes_of_the_larger_models(dtype, width, heads, tmp_path):
+    """One layer at the widths of GPT-2 XL and large (heads of 64, a width that is no multiple of 256, an inner
+    width of four times that), small vocabulary: a prompt in one step (the tcgen05 linear and attention kernels,
+    row statistics for the folded norms), then portions and single tokens (the few-rows kernels with norms folded
+    over 50 or 40 blocks of 32), against the plain implementation."""
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.weights import load_model
+    config = dict(CONFIG_A, n_embd=width, n_head=heads, n_layer=1, n_inner=4 * width, vocab_size=777, n_positions=512,
+                  ln_gain_std=0.2)
+    weights = make_model_dir(str(tmp_path), config, 31, peaky=4.0)
+    model, _ = load_model(str(tmp_path), dtype=dtype)
+    toks = random_tokens(300, 777, 5)
+    ref = plain.logits(toks, weights, config)
+    eng = Engine(model, page_size=16, n_pages=64, max_requests=2)
+    eng.add_request("a")
+    lg = eng.step([StepEntry("a", toks[:200], [0, 127, 128, 199])])
+    for row, pos in enumerate([0, 127, 128, 199]):
+        assert rel(lg[row], ref[pos]) <= TOL[dtype], pos
+    lg = eng.step([StepEntry("a", toks[200:260], [59])])          # a portion of 60: few rows
+    assert rel(lg[0], ref[259]) <= TOL[dtype]
+    worst = 0.0
+    for t in range(260, 300):                                     # single tokens
+        lg = eng.step([StepEntry("a", toks[t:t + 1], [0])])
+        worst = max(worst, rel(lg[0], ref[t]))
+    assert worst <= TOL[dtype], worst
+    eng.check_status()
+
+
 def test_step_refuses_bad_input(tmp_path):
     from mlx_lm_b200.cache import OutOfPages
     from mlx_lm_b200.engine import Engine, StepEntry
