@@ -66,6 +66,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   *abort_flag = 1;
   return false;
 }
+// The same for a whole warp, with one answer for all its lanes: the warp stays together whatever happens, so
+// that it can meet in __syncwarp afterwards.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  return __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag));
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -145,9 +150,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     mbar_init(&sm.k_full, 1);
     mbar_init(&sm.v_full, 1);
     mbar_init(&sm.s_full, 1);
-    mbar_init(&sm.p_full, AT_SOFTMAX);
+    mbar_init(&sm.p_full, AT_SOFTMAX / 32);   // one arrival per softmax warp
     mbar_init(&sm.o_full, 1);
-    mbar_init(&sm.x_full, AT_SOFTMAX);
+    mbar_init(&sm.x_full, AT_SOFTMAX / 32);
     sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
@@ -178,7 +183,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   if (warp == MMA_WARP) {
     // The whole warp takes part in the loads: lane s looks up the page of slot s of a block (one round of
     // global loads for all pages at once, a block ahead of its use) and issues that page's TMA copy; lane 0
-    // alone arms the barriers and issues the MMAs.  Waits are done by every lane, so the warp stays together.
+    // alone arms the barriers and issues the MMAs.  Waits are done by every lane with one answer for the warp.
     const int* bt = block_table + (size_t)req * max_pages;
     const int shift = __ffs(page) - 1;
     const int pages_per_block = TK / page;
@@ -227,7 +232,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       __syncwarp();
     };
-    bool ok = mbar_wait(&sm.q_full, 0, abort_flag) && mbar_wait(&sm.k_full, 0, abort_flag);
+    bool ok = mbar_wait_warp(&sm.q_full, 0, abort_flag) && mbar_wait_warp(&sm.k_full, 0, abort_flag);
     if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       issue_s();
@@ -235,10 +240,10 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int i = 0; i < n_blocks && ok; ++i) {
       const uint32_t ph = (uint32_t)(i & 1);
       const bool more = i + 1 < n_blocks;
-      if (!(ok = mbar_wait(&sm.s_full, ph, abort_flag))) break;    // S(i) is there: the K block is free
+      if (!(ok = mbar_wait_warp(&sm.s_full, ph, abort_flag))) break;    // S(i) is there: the K block is free
       if (more) load_pages(&map_k, sm.k, &sm.k_full, pg_next);
-      if (!(ok = mbar_wait(&sm.v_full, ph, abort_flag))) break;
-      if (!(ok = mbar_wait(&sm.p_full, ph, abort_flag))) break;    // P(i) is written, S(i) has been read
+      if (!(ok = mbar_wait_warp(&sm.v_full, ph, abort_flag))) break;
+      if (!(ok = mbar_wait_warp(&sm.p_full, ph, abort_flag))) break;    // P(i) is written, S(i) has been read
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       if (lane == 0) {
 #pragma unroll
@@ -252,12 +257,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       }
       __syncwarp();
       if (more) {
-        if (!(ok = mbar_wait(&sm.k_full, ph ^ 1u, abort_flag))) break;
+        if (!(ok = mbar_wait_warp(&sm.k_full, ph ^ 1u, abort_flag))) break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         issue_s();
       }
       const int pg_after = page_of(kb_lo + i + 2);                 // its latency hides behind the wait below
-      if (!(ok = mbar_wait(&sm.o_full, ph, abort_flag))) break;    // O_b(i) is there: V and P are free
+      if (!(ok = mbar_wait_warp(&sm.o_full, ph, abort_flag))) break;    // O_b(i) is there: V and P are free
       if (more) load_pages(&map_v, sm.v, &sm.v_full, pg_next);
       pg_next = pg_after;
     }
@@ -279,7 +284,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     for (int i = 0; i < n_blocks && ok; ++i) {
       const uint32_t ph = (uint32_t)(i & 1);
       const int key_base = (kb_lo + i) * TK + half * 64;
-      if (!(ok = mbar_wait(&sm.s_full, ph, abort_flag))) break;
+      if (!(ok = mbar_wait_warp(&sm.s_full, ph, abort_flag))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // blocks that lie wholly before the tile's first query and after every row's window floor need no mask
       const bool open = (kb_lo + i) * TK + TK - 1 <= pos0 && (window <= 0 || (kb_lo + i) * TK >= last_pos - window + 1);
@@ -301,8 +306,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         }
       }
       sm.row_max[half][r] = mx;                         // a bounded wait, not bar.sync: a role may have given up
-      mbar_arrive(&sm.x_full);
-      if (!(ok = mbar_wait(&sm.x_full, ph, abort_flag))) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.x_full);
+      if (!(ok = mbar_wait_warp(&sm.x_full, ph, abort_flag))) break;
       mx = fmaxf(mx, sm.row_max[half ^ 1][r]);
       const float m_new = fmaxf(m, mx * scale_log2e);   // scale > 0
       const float base = m_new == -INFINITY ? 0.f : m_new;
@@ -331,8 +337,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       l = l * corr + sum;
       asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P was written by ordinary stores; the MMA reads it
-      mbar_arrive(&sm.p_full);
-      if (!(ok = mbar_wait(&sm.o_full, ph, abort_flag))) break;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.p_full);
+      if (!(ok = mbar_wait_warp(&sm.o_full, ph, abort_flag))) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       {
         uint32_t ob[32];
@@ -346,8 +353,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // the row's sum is the two halves' sums
     if (ok) {
       sm.row_max[half][r] = l;
-      mbar_arrive(&sm.x_full);
-      ok = mbar_wait(&sm.x_full, (uint32_t)(n_blocks & 1), abort_flag);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&sm.x_full);
+      ok = mbar_wait_warp(&sm.x_full, (uint32_t)(n_blocks & 1), abort_flag);
       l += sm.row_max[half ^ 1][r];
     }
     if (ok && r < n_rows) {
