@@ -526,7 +526,8 @@ static int launch_decode(const void* q, int ldq, const int* rows, const int* pos
     cudaGetDevice(&dev);
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
   }
-  const bool many = (long long)n_rows * Hq > sms;   // more (row, head) pairs than SMs: several smaller CTAs per SM
+  // more (row, head, chunk) CTAs than SMs: several smaller CTAs per SM
+  const bool many = (long long)n_rows * Hq * n_chunks_max > sms;
 #define DEC2(TPK_, TH_)                                                                                              \
   {                                                                                                                  \
     const size_t smem = (size_t)(TH_ / 32) * (Dh + 2) * sizeof(float);                                               \
