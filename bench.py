@@ -161,6 +161,43 @@ def decode_loop(engine, sampler_cls, model, batch, prompt_len, steps, warmup, vo
     return ms, launches, mean_ctx
 
 
+def decode_timeline(engine, sampler_cls, model, batch, vocab):
+    """Where a decode step's time goes, kernel by kernel: a few steps under torch.profiler (CUPTI), then for the
+    kernels of the last step their start, their end and the time from the end of the kernel before to their own
+    end (`chain`: what the kernel adds to the step, since each waits for the one before).  Kernels start before
+    their predecessor ends (programmatic dependent launch), so durations overlap and only `chain` adds up.
+    Times under a profiler are for shares, not for the record."""
+    import collections
+
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        _, launches, _ = decode_loop(engine, sampler_cls, model, batch, PROMPT_LEN, 3, 8, vocab)
+        torch.cuda.synchronize()
+    ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
+          and "Memcpy" not in e.name and "Memset" not in e.name]
+    ev.sort(key=lambda e: e.time_range.start)
+    step = ev[-int(launches):]
+    t0 = step[0].time_range.start
+    rows, prev_end = [], t0
+    for e in step:
+        rows.append((e.name.replace("void ", "")[:60], e.time_range.start - t0, e.time_range.end - t0,
+                     e.time_range.end - prev_end))
+        prev_end = e.time_range.end
+    print(f"one decode step, batch {batch}: {len(rows)} kernels, {rows[-1][2]:.1f} us from the first start to the last end")
+    mid = len(rows) // 2
+    for name, a, b, chain in rows[mid:mid + 11]:
+        print(f"  {name:60s} start {a:8.1f}  end {b:8.1f}  chain {chain:5.1f}")
+    agg = collections.OrderedDict()
+    for name, a, b, chain in rows:
+        n, c, d = agg.get(name, (0, 0.0, 0.0))
+        agg[name] = (n + 1, c + chain, d + b - a)
+    for name, (n, c, d) in agg.items():
+        print(f"  {n:3d} x {name:60s} chain {c / n:5.2f} us each ({100 * c / rows[-1][2]:4.1f} % of the step), "
+              f"start to end {d / n:5.2f}")
+
+
 def mixed_workload(model, engine, vocab, args, n_requests=64, new_tokens=128, seed=3):
     """Continuous batching: 64 requests, prompt lengths uniform in [16, 1024 - new_tokens], portions of 256 tokens
     beside decoding requests, everything through the scheduler; wall-clock tokens per second."""
@@ -223,6 +260,9 @@ def run_ours(args):
 
     if args.only == "mixed":
         print(json.dumps(mixed_workload(model, engine, vocab, args)))
+        return
+    if args.only == "timeline":
+        decode_timeline(engine, DeviceSampler, model, B, vocab)
         return
     if args.only == "decode":
         ms, launches, mean_ctx = decode_loop(engine, DeviceSampler, model, B, PROMPT_LEN, K, W, vocab)
@@ -320,7 +360,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 24 (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "timeline"],
                     help="run just this part and print its figures (decode / prefill: short runs for profiling; "
                          "mixed: 64 requests with prompts of 16..1024 tokens through the scheduler, 256-token portions "
                          "beside decoding requests)")

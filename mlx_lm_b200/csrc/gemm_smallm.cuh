@@ -171,6 +171,11 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
       if (SCATTER && in && n >= kv.q_width) e_dst[x] = kv_slot(kv, m, n);
     }
   }
+  // With more elements per thread only the rows' part of the cache addresses is looked up here (one thread per
+  // row walks request -> position -> page); the epilogue adds the column's part.
+  __shared__ long long s_row_base[(SCATTER && !HOIST) ? 16 * MT : 1];
+  if (SCATTER && !HOIST && threadIdx.x < 16 * MT)
+    s_row_base[threadIdx.x] = (int)threadIdx.x < M ? kv_row_base(kv, threadIdx.x) : -1;
   pdl_wait();
   A = after_wait(A);
   residual = after_wait(residual);
@@ -312,19 +317,34 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
       }
     }
   } else {
-    for (int e = threadIdx.x; e < PER * 32; e += WARPS * 32) {
+    // the same, with the loads of all the thread's elements asked for together, after the products
+    float l_bias[EPT], l_colsum[EPT], l_res[EPT];
+#pragma unroll
+    for (int x = 0; x < EPT; ++x) {
+      const int e = threadIdx.x + x * WARPS * 32;
+      int m, n;
+      elem_mn(e, m, n);
+      const bool in = e < PER * 32 && m < M && n < N;
+      l_bias[x] = (in && bias) ? bias[n] : 0.f;
+      l_colsum[x] = (FOLD && in) ? fold.colsum[n] : 0.f;
+      l_res[x] = (in && residual) ? __bfloat162float(residual[(size_t)m * ldc + n]) : 0.f;
+    }
+#pragma unroll
+    for (int x = 0; x < EPT; ++x) {
+      const int e = threadIdx.x + x * WARPS * 32;
+      if (e >= PER * 32) break;
       float v = 0.f;
 #pragma unroll
       for (int w = 0; w < WARPS; ++w) v += part[w * PER * 32 + e];
       int m, n;
       elem_mn(e, m, n);
       if (m < M && n < N) {
-        if (FOLD) v = unfold(v, m, n, fold.colsum[n]);
-        if (bias) v += bias[n];
+        if (FOLD) v = unfold(v, m, n, l_colsum[x]);
+        v += l_bias[x];
         if (EPI == EPI_GELU_NEW) v = gelu_new_fast(v);
-        if (residual) v += __bfloat162float(residual[(size_t)m * ldc + n]);
+        v += l_res[x];
         if (SCATTER && n >= kv.q_width) {
-          __nv_bfloat16* dst = kv_slot(kv, m, n);
+          __nv_bfloat16* dst = kv_slot_at(kv, s_row_base[m], n);
           if (dst) *dst = __float2bfloat16_rn(v);
         } else {
           C[(size_t)m * ldc + n] = from_f<TO>(v);

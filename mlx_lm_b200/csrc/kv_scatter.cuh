@@ -39,3 +39,35 @@ __device__ __forceinline__ __nv_bfloat16* kv_slot(const KvScatter& kv, int m, in
   return pool + (((size_t)pg * kv.Hkv + hh) * kv.page + (pos % kv.page)) * kv.Dh + d;
 }
 
+
+// The same in two steps, for kernels that write many elements of a row: the row's part of the address once
+// (element offset of head 0, dim 0 of the token's slot; -1 for a padding row or an index out of range, which
+// sets the status bit) ...
+__device__ __forceinline__ long long kv_row_base(const KvScatter& kv, int m) {
+  const int r = kv.token_req[m];
+  if (r < 0) return -1;
+  const int pos = kv.positions[m];
+  const int lp = pos / kv.page;
+  const int pg = (pos >= 0 && lp < kv.max_pages) ? kv.block_table[(size_t)r * kv.max_pages + lp] : -2;
+  if (pg == -2) {
+    atomicOr(kv.status, MLXB_ST_POSITION_RANGE);
+    return -1;
+  }
+  if (pg >= kv.n_pages) {
+    atomicOr(kv.status, MLXB_ST_PAGE_RANGE);
+    return -1;
+  }
+  if (pg < 0) return -1;
+  return ((long long)pg * kv.Hkv * kv.page + (pos % kv.page)) * kv.Dh;
+}
+
+// ... and the column's part: where output column n (>= q_width) of that row goes.
+__device__ __forceinline__ __nv_bfloat16* kv_slot_at(const KvScatter& kv, long long row_base, int n) {
+  if (row_base < 0) return nullptr;
+  const int kvw = kv.Hkv * kv.Dh;
+  int c2 = n - kv.q_width;
+  __nv_bfloat16* pool = kv.k_pool;
+  if (c2 >= kvw) { c2 -= kvw; pool = kv.v_pool; }
+  const int hh = c2 / kv.Dh, d = c2 - hh * kv.Dh;
+  return pool + row_base + (long long)hh * kv.page * kv.Dh + d;
+}
