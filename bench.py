@@ -161,41 +161,71 @@ def decode_loop(engine, sampler_cls, model, batch, prompt_len, steps, warmup, vo
     return ms, launches, mean_ctx
 
 
-def decode_timeline(engine, sampler_cls, model, batch, vocab):
-    """Where a decode step's time goes, kernel by kernel: a few steps under torch.profiler (CUPTI), then for the
-    kernels of the last step their start, their end and the time from the end of the kernel before to their own
-    end (`chain`: what the kernel adds to the step, since each waits for the one before).  Kernels start before
-    their predecessor ends (programmatic dependent launch), so durations overlap and only `chain` adds up.
-    Times under a profiler are for shares, not for the record."""
+def print_timeline(prof, n_kernels, title):
+    """The last `n_kernels` kernels of a torch.profiler capture: their start, their end and the time from the end
+    of the kernel before to their own end (`chain`: what the kernel adds to the step, since each waits for the one
+    before).  Kernels start before their predecessor ends (programmatic dependent launch), so durations overlap
+    and only `chain` adds up.  Times under a profiler are for shares, not for the record."""
     import collections
 
     import torch
-    from torch.profiler import ProfilerActivity, profile
 
-    with profile(activities=[ProfilerActivity.CUDA]) as prof:
-        _, launches, _ = decode_loop(engine, sampler_cls, model, batch, PROMPT_LEN, 3, 8, vocab)
-        torch.cuda.synchronize()
     ev = [e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA
           and "Memcpy" not in e.name and "Memset" not in e.name]
     ev.sort(key=lambda e: e.time_range.start)
-    step = ev[-int(launches):]
+    step = ev[-int(n_kernels):]
     t0 = step[0].time_range.start
     rows, prev_end = [], t0
     for e in step:
         rows.append((e.name.replace("void ", "")[:60], e.time_range.start - t0, e.time_range.end - t0,
                      e.time_range.end - prev_end))
         prev_end = e.time_range.end
-    print(f"one decode step, batch {batch}: {len(rows)} kernels, {rows[-1][2]:.1f} us from the first start to the last end")
+    print(f"{title}: {len(rows)} kernels, {rows[-1][2]:.1f} us from the first start to the last end")
     mid = len(rows) // 2
-    for name, a, b, chain in rows[mid:mid + 11]:
+    for name, a, b, chain in rows[mid:mid + 15]:
         print(f"  {name:60s} start {a:8.1f}  end {b:8.1f}  chain {chain:5.1f}")
     agg = collections.OrderedDict()
     for name, a, b, chain in rows:
         n, c, d = agg.get(name, (0, 0.0, 0.0))
         agg[name] = (n + 1, c + chain, d + b - a)
     for name, (n, c, d) in agg.items():
-        print(f"  {n:3d} x {name:60s} chain {c / n:5.2f} us each ({100 * c / rows[-1][2]:4.1f} % of the step), "
-              f"start to end {d / n:5.2f}")
+        print(f"  {n:3d} x {name:60s} chain {c / n:6.2f} us each ({100 * c / rows[-1][2]:4.1f} % of the step), "
+              f"start to end {d / n:6.2f}")
+
+
+def decode_timeline(engine, sampler_cls, model, batch, vocab):
+    """Where a decode step's time goes, kernel by kernel: a few steps under torch.profiler (CUPTI)."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        _, launches, _ = decode_loop(engine, sampler_cls, model, batch, PROMPT_LEN, 3, 8, vocab)
+        torch.cuda.synchronize()
+    print_timeline(prof, launches, f"one decode step, batch {batch}")
+
+
+def prefill_timeline(engine, n_prompts, vocab):
+    """The same for one step of `n_prompts` whole prompts of 1024 tokens."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+
+    from mlx_lm_b200 import ops
+    from mlx_lm_b200.engine import StepEntry
+
+    g = torch.Generator().manual_seed(1)
+    prompts = [torch.randint(0, vocab, (1024,), generator=g).tolist() for _ in range(n_prompts)]
+    launches = 0
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for it in range(3):
+            for i in range(n_prompts):
+                engine.add_request(("pf", i))
+            ops.launch_count = 0
+            engine.step([StepEntry(("pf", i), prompts[i], [1023]) for i in range(n_prompts)])
+            launches = ops.launch_count
+            torch.cuda.synchronize()
+            for i in range(n_prompts):
+                engine.finish(("pf", i))
+    print_timeline(prof, launches, f"one prefill step, {n_prompts} x 1024 tokens")
 
 
 def mixed_workload(model, engine, vocab, args, n_requests=64, new_tokens=128, seed=3):
@@ -262,7 +292,10 @@ def run_ours(args):
         print(json.dumps(mixed_workload(model, engine, vocab, args)))
         return
     if args.only == "timeline":
-        decode_timeline(engine, DeviceSampler, model, B, vocab)
+        if args.prefill_prompts:
+            prefill_timeline(engine, args.prefill_prompts, vocab)
+        else:
+            decode_timeline(engine, DeviceSampler, model, B, vocab)
         return
     if args.only == "decode":
         ms, launches, mean_ctx = decode_loop(engine, DeviceSampler, model, B, PROMPT_LEN, K, W, vocab)
@@ -270,7 +303,7 @@ def run_ours(args):
         return
 
     # ---- prefill: 2 x 1024 tokens in one step (more prompts only with --only prefill --prefill-prompts N)
-    n_pf = args.prefill_prompts if args.only == "prefill" else 2
+    n_pf = (args.prefill_prompts or 2) if args.only == "prefill" else 2
     if not 1 <= n_pf <= max_b:
         raise SystemExit(f"--prefill-prompts {n_pf}: 1 to {max_b}")
     g = torch.Generator().manual_seed(1)
@@ -363,9 +396,11 @@ def main():
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "timeline"],
                     help="run just this part and print its figures (decode / prefill: short runs for profiling; "
                          "mixed: 64 requests with prompts of 16..1024 tokens through the scheduler, 256-token portions "
-                         "beside decoding requests)")
-    ap.add_argument("--prefill-prompts", type=int, default=2,
-                    help="with --only prefill: 1024-token prompts in the one step (the contract's figure is 2)")
+                         "beside decoding requests; timeline: every kernel of one step with its start and end, "
+                         "from torch.profiler)")
+    ap.add_argument("--prefill-prompts", type=int, default=0,
+                    help="with --only prefill: 1024-token prompts in the one step (default and the contract's figure: "
+                         "2); with --only timeline: the timeline of such a step instead of a decode step")
     ap.add_argument("--size", default="medium", choices=sorted(SIZES), help="layer sizes: GPT-2 medium, large or XL")
     a = ap.parse_args()
     if a.impl == "reference":

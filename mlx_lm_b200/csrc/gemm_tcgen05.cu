@@ -282,6 +282,17 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   const uint32_t tmem_base = sm.tmem_base;
   volatile int* abort_flag = &sm.abort_flag;
   pdl_trigger();
+  // The weights do not come from the previous kernel: the W halves of the first tile's first stages are asked
+  // for before the wait, so that after it only the rows of A are missing.
+  int early = 0;
+  if (threadIdx.x == 0 && (int)blockIdx.x < n_tiles) {
+    const int n0 = ((int)blockIdx.x / tiles_m) * BN;
+    early = k_tiles < STAGES ? k_tiles : STAGES;
+    for (int s = 0; s < early; ++s) {
+      mbar_expect_tx(&sm.full[s], STAGE_BYTES);
+      tma_load_2d(sm.b[s], &map_w, s * BK, n0, &sm.full[s]);
+    }
+  }
   pdl_wait();   // A (and the residual) come from the previous kernel
   residual = after_wait(residual);
 
@@ -294,6 +305,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         for (int kt = 0; kt < k_tiles; ++kt, ++issued) {
           const int s = issued % STAGES;
           const uint32_t ph = (issued / STAGES) & 1;
+          if (issued < early) {   // a fresh stage whose W half is on its way already
+            tma_load_2d(sm.a[s], &map_a, kt * BK, m0, &sm.full[s]);
+            continue;
+          }
           if (!mbar_wait(&sm.empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
           mbar_expect_tx(&sm.full[s], STAGE_BYTES);
           tma_load_2d(sm.a[s], &map_a, kt * BK, m0, &sm.full[s]);
