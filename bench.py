@@ -298,8 +298,15 @@ def run_ours(args):
             decode_timeline(engine, DeviceSampler, model, B, vocab)
         return
     if args.only == "decode":
-        ms, launches, mean_ctx = decode_loop(engine, DeviceSampler, model, B, PROMPT_LEN, K, W, vocab)
-        print(json.dumps({"only": "decode", "batch": B, "ms_per_step": round(ms, 4), "launches_per_step": launches}))
+        plen = args.prompt_len or PROMPT_LEN
+        if plen + 1 + W + K > CONTEXT:
+            raise SystemExit(f"--prompt-len {plen}: {W} + {K} decode steps after it exceed the context of {CONTEXT}")
+        ms, launches, mean_ctx = decode_loop(engine, DeviceSampler, model, B, plen, K, W, vocab)
+        step_bytes = weight_bytes + B * mean_ctx * kv_per_token
+        print(json.dumps({"only": "decode", "batch": B, "prompt_len": plen, "mean_context": round(mean_ctx, 1),
+                          "ms_per_step": round(ms, 4), "tokens_per_s": round(B / (ms / 1e3), 1),
+                          "hbm_frac": round(step_bytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                          "launches_per_step": launches}))
         return
 
     # ---- prefill: 2 x 1024 tokens in one step (more prompts only with --only prefill --prefill-prompts N)
@@ -401,6 +408,8 @@ def main():
     ap.add_argument("--prefill-prompts", type=int, default=0,
                     help="with --only prefill: 1024-token prompts in the one step (default and the contract's figure: "
                          "2); with --only timeline: the timeline of such a step instead of a decode step")
+    ap.add_argument("--prompt-len", type=int, default=0,
+                    help="with --only decode: prompt length before the timed steps (default 512, the contract's)")
     ap.add_argument("--size", default="medium", choices=sorted(SIZES), help="layer sizes: GPT-2 medium, large or XL")
     a = ap.parse_args()
     if a.impl == "reference":
