@@ -75,8 +75,12 @@ struct NormFold {
 };
 
 // MT: 16-row token tiles (M <= 16*MT); NW: 8-row weight tiles per CTA; WARPS: warps that share the K blocks.
+// The second launch bound (at least one CTA per SM, which says nothing new) is there for the register
+// allocator: without it the compiler keeps these kernels at 76 registers for the sake of occupancy; with it they
+// get 116 and run a decode step of 124 kernels 2-7 % faster (fewer, faster CTAs per SM, and room beside them for
+// the CTAs of the next kernel, which fetch their weights while they wait).
 template <int MT, int NW, int WARPS, typename TO, int EPI, bool SCATTER, bool FOLD>
-__global__ void __launch_bounds__(WARPS * 32)
+__global__ void __launch_bounds__(WARPS * 32, 1)
 gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                    const float* __restrict__ bias, const __nv_bfloat16* residual, TO* C, int M, int N, int K,
                    int lda, int ldc, KvScatter kv, NormFold fold) {
