@@ -173,6 +173,55 @@ def test_request_that_can_never_fit_is_refused():
     assert out[u] == expected(u, 60, 5)
 
 
+@pytest.mark.parametrize("seed", range(12))
+def test_random_workloads_give_every_request_its_own_tokens(seed):
+    """Random prompt lengths, budgets, pool sizes and arrival times: whatever the scheduler decides (portions,
+    admissions, preemptions), every request gets the tokens it would get alone, no step exceeds its budgets, no
+    page is left behind, and the oldest running request is never the one that starts over."""
+    import random
+
+    rng = random.Random(seed)
+    page = rng.choice([8, 16])
+    n_pages = rng.randint(6, 24)
+    max_requests = rng.randint(2, 5)
+    step_size = rng.choice([8, 16, 48, 200])
+    budget = rng.choice([16, 64, 256])
+    eng = FakeEngine(n_pages=n_pages, page_size=page, max_requests=8, max_len=256)
+    s = Scheduler(eng, fake_sample, max_requests=max_requests, max_prefilling=rng.randint(1, max_requests),
+                  prefill_step_size=step_size, max_tokens_per_step=budget)
+    capacity = min(n_pages * page, 256)
+    todo = []
+    for _ in range(rng.randint(3, 9)):
+        plen = rng.randint(1, max(1, min(120, capacity - 2)))
+        new = rng.randint(1, max(1, min(40, capacity - plen)))
+        todo.append((plen, new))
+    info, out, reasons = {}, {}, {}
+    n = 0
+    while todo or s.has_work():
+        while todo and (not s.has_work() or rng.random() < 0.3):
+            plen, new = todo.pop()
+            u = s.insert([rng.randrange(1000) for _ in range(plen)], max_tokens=new)
+            info[u] = (plen, new)
+        before = len(eng.steps)
+        _, gens = s.next()
+        for r in gens:
+            out.setdefault(r.uid, []).append(r.token)
+            if r.finish_reason:
+                reasons[r.uid] = r.finish_reason
+        for st in eng.steps[before:]:
+            assert sum(cnt for _, _, cnt, _ in st) <= max(budget, 1)
+            assert len(st) <= max_requests
+            assert all(cnt <= step_size for _, start, cnt, _ in st if cnt > 1)
+        assert sum(eng.cache.pages_in_use()) <= n_pages
+        n += 1
+        assert n < 20000, "the scheduler does not finish"
+    for u, (plen, new) in info.items():
+        assert out[u] == expected(u, plen, new), (seed, u)
+        assert reasons[u] == "length"
+    assert eng.cache.pages_in_use() == [0]
+    eng.cache.check()
+
+
 def test_stop_matcher():
     m = StopSequenceMatcher([[1, 2, 3], [7]])
     assert not m.matches([1, 2]) and m.matches([0, 1, 2, 3]) and m.matches([7]) and not m.matches([7, 1])
