@@ -1,13 +1,14 @@
 """A GPT-2 inference engine for one NVIDIA B200, in the manner of mlx-lm.
 
-``load``, ``generate``, ``stream_generate`` and ``batch_generate`` are the entry points
+``load``, ``generate``, ``stream_generate``, ``generate_step`` and ``batch_generate`` are the entry points
 (mlx_lm/__init__.py:9-20); they are imported on first use so that configuration, weights and the
 cache manager can be used without a CUDA device.
 """
 
 __version__ = "0.1.0"
 
-_API = {"load", "generate", "stream_generate", "batch_generate", "BatchGenerator", "GenerationResponse"}
+_API = {"load", "generate", "stream_generate", "generate_step", "batch_generate", "BatchGenerator",
+        "GenerationResponse"}
 
 
 def __getattr__(name):

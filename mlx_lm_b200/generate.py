@@ -140,6 +140,32 @@ def stream_generate(model, tokenizer: TokenizerWrapper, prompt: Union[str, List[
         sched.remove([uid])
 
 
+def generate_step(prompt: Union[List[int], torch.Tensor], model, *, max_tokens: int = 256,
+                  sampler: Optional[Sampler] = None, logits_processors: Optional[Sequence] = None,
+                  prefill_step_size: int = 2048,
+                  prompt_progress_callback: Optional[Callable[[int, int], None]] = None, seed: int = 0,
+                  engine: Optional[Engine] = None) -> Generator[Tuple[int, torch.Tensor], None, None]:
+    """Token ids in, ``(token, log-probabilities)`` out, one pair per generated token
+    (mlx_lm/generate.py:298-462): the log-probabilities are the float32 ``[vocab]`` vector the token was drawn
+    from, on the device.  No tokenizer and no end-of-sequence token: it stops after ``max_tokens``."""
+    tokens = [int(t) for t in (prompt.flatten().tolist() if isinstance(prompt, torch.Tensor) else prompt)]
+    engine = engine or get_engine(model)
+    dev_sampler = DeviceSampler(model.device, seed=seed, return_logprobs=True)
+    sched = Scheduler(engine, dev_sampler, max_requests=1, max_prefilling=1, prefill_step_size=prefill_step_size,
+                      max_tokens_per_step=max(prefill_step_size, 1))
+    uid = sched.insert(tokens, max_tokens, sampler or GREEDY, logits_processors or ())
+    try:
+        while sched.has_work():
+            progress, responses = sched.next()
+            if prompt_progress_callback is not None:
+                for p in progress:
+                    prompt_progress_callback(*p.progress)
+            for r in responses:
+                yield r.token, dev_sampler.last_logprobs[0].clone()
+    finally:
+        sched.remove([uid])
+
+
 def generate(model, tokenizer, prompt: Union[str, List[int]], verbose: bool = False, **kwargs) -> str:
     """The whole response as one string; ``verbose`` prints it as it comes, then speeds and memory."""
     if verbose:

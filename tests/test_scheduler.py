@@ -226,3 +226,48 @@ def test_stop_matcher():
     m = StopSequenceMatcher([[1, 2, 3], [7]])
     assert not m.matches([1, 2]) and m.matches([0, 1, 2, 3]) and m.matches([7]) and not m.matches([7, 1])
     assert not StopSequenceMatcher().matches([1])
+
+
+def test_generate_step_drives_the_scheduler_for_one_request(monkeypatch):
+    """The host side of ``generate_step`` with the fake engine and a stand-in for the device sampler: one pair
+    per generated token, the vector that belongs to it, progress for every portion of the prompt, no
+    end-of-sequence stop, and the request is gone afterwards."""
+    import importlib
+    from types import SimpleNamespace
+
+    G = importlib.import_module("mlx_lm_b200.generate")
+    eng = FakeEngine(n_pages=8)
+
+    class Vector:
+        def __init__(self, token):
+            self.token = token
+
+        def clone(self):
+            return ("log-probabilities of", self.token)
+
+    class StandInSampler:
+        def __init__(self, device, seed=0, return_logprobs=False):
+            assert return_logprobs
+            self.last_logprobs = None
+
+        def __call__(self, rows, requests):
+            tokens, logprobs = fake_sample(rows, requests)
+            self.last_logprobs = [Vector(t) for t in tokens]
+            return tokens, logprobs
+
+    monkeypatch.setattr(G, "DeviceSampler", StandInSampler)
+    monkeypatch.setattr(G, "get_engine", lambda model: eng)
+    seen = []
+    pairs = list(G.generate_step(list(range(11)), SimpleNamespace(device="cpu"), max_tokens=5, prefill_step_size=4,
+                                 prompt_progress_callback=lambda done, total: seen.append((done, total))))
+    want = expected(0, 11, 5)
+    assert [t for t, _ in pairs] == want
+    assert [v for _, v in pairs] == [("log-probabilities of", t) for t in want]
+    assert seen == [(4, 11), (8, 11), (11, 11)]
+    assert [sum(cnt for _, _, cnt, _ in st) for st in eng.steps] == [4, 4, 3, 1, 1, 1, 1]
+    assert eng.cache.pages_in_use() == [0]
+    # a generator that is dropped half way gives its pages back as well
+    gen = G.generate_step(list(range(20)), SimpleNamespace(device="cpu"), max_tokens=50)
+    next(gen), next(gen)
+    gen.close()
+    assert eng.cache.pages_in_use() == [0]
