@@ -68,6 +68,8 @@ def _split(name: str):
 
 def _digest(name: str) -> str:
     src, defines = _split(name)
+    if not os.path.exists(os.path.join(CSRC, src + ".cu")):
+        raise KernelBuildError(f"no kernel source {os.path.join(CSRC, src + '.cu')}")
     h = hashlib.sha1()
     for path in [os.path.join(CSRC, src + ".cu")] + _headers():
         with open(path, "rb") as f:
