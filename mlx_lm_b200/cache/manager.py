@@ -17,7 +17,8 @@ means row ``i`` of every cache's pool in that group.
 Life of a request: ``add_request`` takes a state slot; before a step
 ``reserve(rid, n)`` takes the pages positions ``length .. length+n-1`` need
 (all groups, or nothing if one runs out: ``OutOfPages``); after the step
-``commit(rid)`` advances the length and gives back pages a window has passed;
+``commit(rid)`` advances the length and gives back pages a window has passed
+(``rollback(rid)`` instead, if the step failed: the reservation is undone);
 ``truncate`` rewinds; ``release`` gives everything back.  Freed pages go on
 top of the free list (LIFO), so a small pool re-uses pages at once.
 
@@ -254,6 +255,19 @@ class CacheManager:
                 if r.pages[gi][lp] >= 0:
                     g.pool.free(r.pages[gi][lp])
                     r.pages[gi][lp] = -1
+
+    def rollback(self, rid: Hashable) -> None:
+        """The step that held the reservation did not run: forget the reserved positions and give back the
+        pages that were taken for them.  (State of fixed size that the failed step may have touched is not
+        restored: a request with such state has to be released and run again.)"""
+        r = self.requests[rid]
+        r.reserved = 0
+        keep = (r.length + self.page_size - 1) // self.page_size
+        for gi, g in enumerate(self.kv_groups):
+            while len(r.pages[gi]) > keep:
+                p = r.pages[gi].pop()
+                if p >= 0:
+                    g.pool.free(p)
 
     def truncate(self, rid: Hashable, new_len: int) -> None:
         """Forget positions ``new_len ..``; whole pages beyond are given back

@@ -308,6 +308,13 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
   const int r = token_req[t];
   const int p = positions[t];
   if (r < 0) return;
+  // A position the chunks do not cover has no CTA for its last chunk: the merge below would wait for a
+  // ticket that never comes.  Every CTA of such a row reports it and leaves before any ticket is taken, so
+  // the row's counter stays zero (the row's output is not written).
+  if (p < 0 || p / chunk >= n_chunks_max) {
+    if (threadIdx.x == 0) atomicOr(status, MLXB_ST_POSITION_RANGE);
+    return;
+  }
   const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
   const int k_begin = max(lo, c * chunk), k_end = min(p + 1, (c + 1) * chunk);
   if (k_begin >= k_end) return;
@@ -548,7 +555,8 @@ MLXB_EXPORT long long mlxb_attention_decode_scratch(int n_rows, int Hq, int Dh, 
 }
 
 // Rows with one query each.  rows: int32[n_rows] token indices or null (tokens 0..n_rows-1).
-// n_chunks_max * chunk must cover every position a row may have; partial: float32 scratch of
+// n_chunks_max * chunk should cover every position a row may have: a row whose position lies beyond gets no
+// output and sets MLXB_ST_POSITION_RANGE in *status (its counter stays zero).  partial: float32 scratch of
 // mlxb_attention_decode_scratch() floats, contents need not be initialised; counters: int32[n_rows * Hq]
 // that must be ZERO before the first call and are left zero by every call.
 // Dh must be a multiple of 8 (16 for bfloat16 alignment is implied by pages); q rows 16-byte aligned.

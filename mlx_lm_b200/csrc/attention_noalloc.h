@@ -38,6 +38,12 @@
 // replayed concurrently) would overwrite each other's partial results: run calls
 // on one device one after the other, i.e. on one stream.
 //
+// Positions.  n_chunks_max * chunk has to cover the largest position among the
+// rows.  A row whose position lies at or beyond that product (or is negative) is
+// left out: its output row is not written, MLXB_ST_POSITION_RANGE (2) is set in
+// *status, and it takes no ticket, so the counters stay zero and later calls are
+// not disturbed.  Read *status after the call if positions come from outside.
+//
 // It calls no cudaMalloc, cudaFree or any other allocating routine.  Inputs and
 // the output are the caller's, exactly as for mlxb_attention_decode(); only the
 // `partial` argument is gone.

@@ -8,11 +8,9 @@
 // the bfloat16 engine for shapes its tensor-core kernels refuse.
 //
 // Tile 64x64, K step 16, 256 threads with a 4x4 micro-tile each.  Any M, N, K.
-#include "common.cuh"
+#include "activations.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
-
-enum { EPI_NONE = 0, EPI_GELU_NEW = 1 };
 
 constexpr int BM = 64, BN = 64, BK = 16;
 
@@ -72,7 +70,7 @@ gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, const float* 
       if (n >= N) continue;
       float v = acc[i][j];
       if (bias) v += bias[n];
-      if (EPI == EPI_GELU_NEW) v = gelu_new_f(v);
+      v = activate<EPI, false>(v);
       if (residual) v += to_f(residual[(size_t)m * ldc + n]);
       C[(size_t)m * ldc + n] = from_f<TO>(v);
     }
@@ -83,15 +81,11 @@ template <typename T, typename TO>
 static int launch(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N,
                   int K, int lda, int ldc, int epi, cudaStream_t stream) {
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
-  if (epi == EPI_NONE)
-    launch_pdl(gemm_simt_kernel<T, TO, EPI_NONE>, grid, dim3(256), 0, stream, (const T*)A, (const T*)W, bias,
+  return dispatch_activation(epi, [&](auto e) {
+    launch_pdl(gemm_simt_kernel<T, TO, decltype(e)::value>, grid, dim3(256), 0, stream, (const T*)A, (const T*)W, bias,
                (const T*)residual, (TO*)C, M, N, K, lda, ldc);
-  else if (epi == EPI_GELU_NEW)
-    launch_pdl(gemm_simt_kernel<T, TO, EPI_GELU_NEW>, grid, dim3(256), 0, stream, (const T*)A, (const T*)W, bias,
-               (const T*)residual, (TO*)C, M, N, K, lda, ldc);
-  else
-    return mlxb_fail(MLXB_BAD_ARG, "linear: epilogue code %d", epi);
-  return mlxb_check_launch("linear (generic)");
+    return mlxb_check_launch("linear (generic)");
+  });
 }
 
 // dtype: dtype of A, W, residual.  out_f32 != 0: C is float32 whatever dtype is.

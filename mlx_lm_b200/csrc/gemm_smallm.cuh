@@ -30,10 +30,7 @@
 // pos % page), which saves the separate cache-write kernel of a decode step.
 #pragma once
 
-#include "common.cuh"
-
-
-enum { EPI_NONE = 0, EPI_GELU_NEW = 1 };
+#include "activations.cuh"
 
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
@@ -311,7 +308,7 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
       if (m < M && n < N) {
         if (FOLD) v = unfold(v, m, n, e_colsum[x]);
         v += e_bias[x];
-        if (EPI == EPI_GELU_NEW) v = gelu_new_fast(v);
+        v = activate<EPI, true>(v);
         v += e_res[x];
         if (SCATTER && n >= kv.q_width) {
           if (e_dst[x]) *e_dst[x] = __float2bfloat16_rn(v);
@@ -345,7 +342,7 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
       if (m < M && n < N) {
         if (FOLD) v = unfold(v, m, n, l_colsum[x]);
         v += l_bias[x];
-        if (EPI == EPI_GELU_NEW) v = gelu_new_fast(v);
+        v = activate<EPI, true>(v);
         v += l_res[x];
         if (SCATTER && n >= kv.q_width) {
           __nv_bfloat16* dst = kv_slot_at(kv, s_row_base[m], n);
@@ -364,17 +361,19 @@ static int launch_epi(const void* A, const void* W, const float* bias, const voi
                       cudaStream_t stream) {
   const dim3 grid((N + 8 * NW - 1) / (8 * NW));
   const size_t smem = ((size_t)WARPS * MT * NW * 4 * 32 + (FOLD ? (size_t)WARPS * 16 * MT * 2 : 0)) * sizeof(float);
-  auto k0 = gemm_smallm_kernel<MT, NW, WARPS, TO, EPI_NONE, SCATTER, FOLD>;
-  auto k1 = gemm_smallm_kernel<MT, NW, WARPS, TO, EPI_GELU_NEW, SCATTER, FOLD>;
-  auto kern = epi == EPI_GELU_NEW ? k1 : k0;
-  static bool raised[2] = {false, false};   // once per instantiation, and never for the first time inside a stream capture
-  if (smem > 48 * 1024 && !raised[epi == EPI_GELU_NEW]) {
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    raised[epi == EPI_GELU_NEW] = true;
-  }
-  launch_pdl(kern, grid, dim3(WARPS * 32), smem, stream, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias,
-             (const __nv_bfloat16*)residual, (TO*)C, M, N, K, lda, ldc, kv, fold);
-  return mlxb_check_launch("linear (few rows)");
+  // The fused cache write has no activation: only the plain epilogue is built for it.
+  return dispatch_activation(SCATTER ? (int)EPI_NONE : epi, [&](auto e) {
+    constexpr int EPI = SCATTER ? (int)EPI_NONE : (int)decltype(e)::value;
+    auto kern = gemm_smallm_kernel<MT, NW, WARPS, TO, EPI, SCATTER, FOLD>;
+    static bool raised = false;   // once per instantiation, and never for the first time inside a stream capture
+    if (smem > 48 * 1024 && !raised) {
+      cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      raised = true;
+    }
+    launch_pdl(kern, grid, dim3(WARPS * 32), smem, stream, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias,
+               (const __nv_bfloat16*)residual, (TO*)C, M, N, K, lda, ldc, kv, fold);
+    return mlxb_check_launch("linear (few rows)");
+  });
 }
 
 template <typename TO, bool SCATTER, bool FOLD>
@@ -414,7 +413,7 @@ static int check_args(int M, int N, int K, int lda, int ldc, int epi, const void
                      K, lda, ldc, N);
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15))
     return mlxb_fail(MLXB_BAD_ARG, "linear (few rows): operands must be 16-byte aligned");
-  if (epi != EPI_NONE && epi != EPI_GELU_NEW) return mlxb_fail(MLXB_BAD_ARG, "linear: epilogue code %d", epi);
+  if (!activation_known(epi)) return mlxb_fail(MLXB_BAD_ARG, "linear: epilogue code %d", epi);
   return 0;
 }
 

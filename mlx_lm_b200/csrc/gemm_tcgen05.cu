@@ -23,12 +23,10 @@
 // The accumulation order over K is fixed (stage by stage, four steps per stage), independent of M.
 #include <cuda.h>
 
-#include "common.cuh"
+#include "activations.cuh"
 #include "kv_scatter.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
-
-enum { EPI_NONE = 0, EPI_GELU_NEW = 1 };
 
 constexpr int BM = 128, BK = 64;
 constexpr int EPI_WARPS = 16;                     // four per quadrant of TMEM lanes, each a quarter of the columns
@@ -172,9 +170,9 @@ __device__ __forceinline__ void store8(const uint32_t* r, int n8, int N, size_t 
         if (n8 + i < N) v[i] += bias[n8 + i];
     }
   }
-  if (EPI == EPI_GELU_NEW) {
+  if (EPI != EPI_NONE) {
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = gelu_new_fast(v[i]);
+    for (int i = 0; i < 8; ++i) v[i] = activate<EPI, true>(v[i]);
   }
   if (residual) {
     if (have_fetched || (whole && ((row + n8) & 7) == 0)) {
@@ -494,21 +492,23 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
   if (int e = make_map(&ma, A, M, K, lda, BM)) return e;
   if (int e = make_map(&mw, W, N, K, K, BN)) return e;
   const size_t smem = sizeof(Smem<BN, STAGES>) + 1024;
-  auto k0 = gemm_tcgen05_kernel<BN, STAGES, TO, EPI_NONE, SCATTER>;
-  auto k1 = gemm_tcgen05_kernel<BN, STAGES, TO, SCATTER ? EPI_NONE : EPI_GELU_NEW, SCATTER>;
-  auto kern = epi == EPI_GELU_NEW ? k1 : k0;
-  static bool raised[2] = {false, false};
-  if (!raised[epi == EPI_GELU_NEW]) {
-    cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e != cudaSuccess) return mlxb_fail((int)e, "linear (tensor cores): %zu bytes of shared memory: %s", smem,
-                                           cudaGetErrorString(e));
-    raised[epi == EPI_GELU_NEW] = true;
-  }
   const int n_tiles = ((M + BM - 1) / BM) * ((N + BN - 1) / BN);
   const dim3 grid(n_tiles < sm_count() ? n_tiles : sm_count());
-  launch_pdl(kern, grid, dim3(THREADS), smem, stream, ma, mw, bias, (const __nv_bfloat16*)residual, (TO*)C, M, N, K,
-             ldc, status, kv, fold);
-  return mlxb_check_launch("linear (tensor cores)");
+  // The fused cache write has no activation: only the plain epilogue is built for it.
+  return dispatch_activation(SCATTER ? (int)EPI_NONE : epi, [&](auto e) {
+    constexpr int EPI = SCATTER ? (int)EPI_NONE : (int)decltype(e)::value;
+    auto kern = gemm_tcgen05_kernel<BN, STAGES, TO, EPI, SCATTER>;
+    static bool raised = false;   // once per instantiation, and never for the first time inside a stream capture
+    if (!raised) {
+      cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (err != cudaSuccess) return mlxb_fail((int)err, "linear (tensor cores): %zu bytes of shared memory: %s", smem,
+                                               cudaGetErrorString(err));
+      raised = true;
+    }
+    launch_pdl(kern, grid, dim3(THREADS), smem, stream, ma, mw, bias, (const __nv_bfloat16*)residual, (TO*)C, M, N, K,
+               ldc, status, kv, fold);
+    return mlxb_check_launch("linear (tensor cores)");
+  });
 }
 
 // Tile width: the one whose waves of tiles over the SMs cost least, a tile's cost being the bytes it streams
@@ -559,7 +559,7 @@ static int linear_tcgen05(int out_f32, const void* A, const void* W, const float
                      K, lda, ldc, N);
   if (((uintptr_t)A & 15) || ((uintptr_t)W & 15))
     return mlxb_fail(MLXB_BAD_ARG, "linear (tensor cores): operands must be 16-byte aligned");
-  if (epi != EPI_NONE && epi != EPI_GELU_NEW) return mlxb_fail(MLXB_BAD_ARG, "linear: epilogue code %d", epi);
+  if (!activation_known(epi)) return mlxb_fail(MLXB_BAD_ARG, "linear: epilogue code %d", epi);
   const int best = tile_width(M, N);
 #define GO(BN_, ST_)                                                                                              \
   {                                                                                                               \

@@ -215,3 +215,37 @@ MLXB_EXPORT int mlxb_row_stats(const void* x, void* stats, int R, int D, int ld,
              ld, eps);
   return mlxb_check_launch("row_stats");
 }
+
+// Row gather without a norm: y[r] = x[rows[r]], for a model whose output head reads the residual stream as
+// it is.  One block per output row; any width, any element type of 2 or 4 bytes.
+template <typename T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ y, int D,
+                                   int n_in) {
+  pdl_trigger();
+  pdl_wait();
+  const int r = blockIdx.x;
+  const int src = rows[r];
+  T* yo = y + (size_t)r * D;
+  if (src < 0 || src >= n_in) {     // never read outside x: a bad index gives a row of zeros
+    for (int d = threadIdx.x; d < D; d += blockDim.x) yo[d] = from_f<T>(0.f);
+    return;
+  }
+  const T* xi = after_wait(x) + (size_t)src * D;
+  for (int d = threadIdx.x; d < D; d += blockDim.x) yo[d] = xi[d];
+}
+
+// x: [n_in, D] contiguous; rows: int32 [R]; y: [R, D] contiguous.
+MLXB_EXPORT int mlxb_gather_rows(int dtype, const void* x, const int* rows, void* y, int R, int D, int n_in,
+                                 cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (D <= 0 || n_in <= 0 || rows == nullptr) return mlxb_fail(MLXB_BAD_ARG, "gather_rows: width %d, %d input rows", D, n_in);
+  const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : 64);
+  if (dtype == MLXB_F32)
+    launch_pdl(gather_rows_kernel<float>, dim3(R), dim3(threads), 0, stream, (const float*)x, rows, (float*)y, D, n_in);
+  else if (dtype == MLXB_BF16)
+    launch_pdl(gather_rows_kernel<__nv_bfloat16>, dim3(R), dim3(threads), 0, stream, (const __nv_bfloat16*)x, rows,
+               (__nv_bfloat16*)y, D, n_in);
+  else
+    return mlxb_fail(MLXB_BAD_DTYPE, "gather_rows: dtype code %d", dtype);
+  return mlxb_check_launch("gather_rows");
+}

@@ -16,6 +16,8 @@
 //     min-p  keeps logprob >= max logprob + log(min_p), and at least min_tokens_to_keep (:154-201);
 //     XTC    with probability xtc_probability removes every token whose renormalised probability is
 //            above the smallest probability that exceeds xtc_threshold, special tokens excepted (:240-276);
+//            the special tokens are the row's own: words `special_offset`, `special_count` of its record
+//            name a range of the list the launcher is given;
 //     top-k  keeps the k largest of what is left (:129-151).
 //   Tokens of equal logit are kept or dropped together.
 //
@@ -29,7 +31,8 @@ struct SampleParams {   // 16 x 32-bit words per row
   float temp, top_p, min_p, xtc_probability, xtc_threshold;
   int top_k, min_tokens_to_keep;
   unsigned seed_lo, seed_hi, request, position;
-  int pad[5];
+  int special_offset, special_count;   // this row's XTC special tokens: xtc_special[offset .. offset + count)
+  int pad[3];
 };
 
 __device__ __forceinline__ unsigned fkey(float f) {
@@ -123,13 +126,16 @@ struct Keep {          // which vocabulary entries are still candidates
 __global__ void __launch_bounds__(1024)
 sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleParams* __restrict__ params,
               const int* __restrict__ xtc_special, int n_special, int* __restrict__ out_token,
-              float* __restrict__ out_logprob, float* __restrict__ out_logprobs, int ldo) {
+              float* __restrict__ out_logprob, float* __restrict__ out_logprobs, int ldo,
+              const int* status_in, int* __restrict__ status_out) {
   __shared__ float redf[40];
   __shared__ int redi[40];
   pdl_trigger();
   pdl_wait();
   logits = after_wait(logits);
   const int row = blockIdx.x;
+  // The step's status word rides along with the tokens: one copy to the host brings both.
+  if (status_out && row == 0 && threadIdx.x == 0) *status_out = __ldcg(after_wait(status_in));
   const float* lg = logits + (size_t)row * ld;
   const SampleParams P = params[row];
   const int tid = threadIdx.x, nt = blockDim.x;
@@ -154,7 +160,10 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleParam
     return;
   }
 
-  Keep keep{0u, false, 0.f, lse, xtc_special, n_special};
+  const bool has_special = xtc_special && P.special_count > 0 && P.special_offset >= 0 &&
+                           P.special_offset + P.special_count <= n_special;
+  Keep keep{0u, false, 0.f, lse, has_special ? xtc_special + P.special_offset : nullptr,
+            has_special ? P.special_count : 0};
 
   if (P.top_p > 0.f && P.top_p < 1.f) {
     // smallest key u with  sum_{key_i <= u} p_i  >  1 - top_p
@@ -248,16 +257,21 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleParam
 }
 
 // logits: float32 [R, V] at row stride ld.  params: R records of 16 words (SampleParams).
+// xtc_special: int32 [n_special], the rows' XTC special tokens one list after the other; each record names its range.
 // out_logprobs (optional): float32 [R, V] at row stride ldo receives logits - logsumexp.
+// status_in / status_out (optional, both or neither): the word at status_in is copied to status_out.
 MLXB_EXPORT int mlxb_sample(const float* logits, int ld, int R, int V, const void* params, const int* xtc_special,
                             int n_special, int* out_token, float* out_logprob, float* out_logprobs, int ldo,
-                            cudaStream_t stream) {
+                            const int* status_in, int* status_out, cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0 || ld < V) return mlxb_fail(MLXB_BAD_ARG, "sample: vocabulary %d, row stride %d", V, ld);
-  if (n_special < 0 || n_special > 64) return mlxb_fail(MLXB_BAD_ARG, "sample: %d special tokens (at most 64)", n_special);
+  if (n_special < 0 || (n_special > 0 && !xtc_special))
+    return mlxb_fail(MLXB_BAD_ARG, "sample: %d special tokens without a list", n_special);
+  if ((status_in == nullptr) != (status_out == nullptr))
+    return mlxb_fail(MLXB_BAD_ARG, "sample: the status word needs both a source and a destination");
   const int threads = V >= 16384 ? 1024 : (V >= 2048 ? 512 : 256);
   launch_pdl(sample_kernel, dim3(R), dim3(threads), 0, stream, logits, ld, V, (const SampleParams*)params,
-             xtc_special, n_special, out_token, out_logprob, out_logprobs, ldo);
+             xtc_special, n_special, out_token, out_logprob, out_logprobs, ldo, status_in, status_out);
   return mlxb_check_launch("sample");
 }
 

@@ -48,8 +48,8 @@ class DecodeGraph:
         self.total = total
         self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
         self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
-        self.out = torch.zeros(2 * B, dtype=torch.int32, device=dev)      # tokens | log-probability bits
-        self.out_host = torch.zeros(2 * B, dtype=torch.int32).pin_memory()
+        self.out = torch.zeros(2 * B + 1, dtype=torch.int32, device=dev)  # tokens | log-probability bits | status word
+        self.out_host = torch.zeros(2 * B + 1, dtype=torch.int32).pin_memory()
         h = self.host.numpy()
         h[self.off["logit_rows"]: self.off["logit_rows"] + B] = np.arange(B)
         h[self.off["req_first_token"]: self.off["req_first_token"] + B + 1] = np.arange(B + 1)
@@ -74,21 +74,10 @@ class DecodeGraph:
 
         # once eagerly on a side stream (loads libraries, sizes the workspace), then capture
         self.dev.copy_(self.host)
-        self.program = None
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
-            ops.start_recording()
-            try:
-                self._launch()
-            finally:
-                calls = ops.stop_recording()
-            if engine.use_program and engine.model.dtype == torch.bfloat16:
-                # the model's launches (all but the sampler's) as one persistent kernel, where each has a phase
-                from ..ops import program
-                self.program = program.compile_program(calls[:-1], dev)
-                if self.program is not None:
-                    self._launch()
+            self._launch()
         side.synchronize()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph, stream=side):
@@ -100,12 +89,9 @@ class DecodeGraph:
         ctx = self.ctx
         ctx.stream = ops.current_stream()
         before = ops.launch_count
-        if self.program is not None:
-            from ..ops import program
-            program.launch(self.program, self.engine.status, ctx.stream)
-        else:
-            self.logits = self.engine.model.run(ctx)
-        ops.sample(self.logits, self.params, self.tok, self.lp, ctx.stream)
+        self.logits = self.engine.model.run(ctx)
+        ops.sample(self.logits, self.params, self.tok, self.lp, ctx.stream, status=self.engine.status,
+                   status_out=self.out[2 * self.B:])
         self._count = ops.launch_count - before
 
     def run(self, entries: Sequence[StepEntry], requests: Sequence, seed: int) -> Tuple[List[int], List[float]]:
@@ -114,31 +100,36 @@ class DecodeGraph:
         n = len(entries)
         h, off, W = self.host.numpy(), self.off, mgr.table_width
         h[off["token_req"] + n: off["token_req"] + B] = -1
-        by_rid = {r.uid: r for r in requests}
         words = []
-        for i, e in enumerate(entries):
-            start = mgr.reserve(e.rid, 1)
-            h[off["tokens"] + i] = e.tokens[0]
-            h[off["positions"] + i] = start
-            h[off["token_req"] + i] = i
-            h[off["slots"] + i] = mgr.requests[e.rid].slot
-            h[off["req_first_position"] + i] = start
-            r = requests[i]
-            words.append(r.sampler.words(seed, r.uid, len(r.tokens)))
-        h[off["sample"]: off["sample"] + n * ops.SAMPLE_WORDS] = np.frombuffer(b"".join(words), dtype=np.int32)
-        h[off["sample"] + n * ops.SAMPLE_WORDS: off["sample"] + B * ops.SAMPLE_WORDS] = 0
-        rids = [e.rid for e in entries]
-        for g in range(len(mgr.kv_groups)):
-            o = off[f"table{g}"]
-            mgr.block_table(g, rids, out=h[o: o + n * W].reshape(n, W))
-            h[o + n * W: o + B * W] = -1
-        self.dev.copy_(self.host, non_blocking=True)
-        self.graph.replay()
-        ops.launch_count += self.n_kernels
-        self.out_host.copy_(self.out, non_blocking=True)
-        torch.cuda.current_stream().synchronize()
+        try:
+            for i, e in enumerate(entries):
+                start = mgr.reserve(e.rid, 1)
+                h[off["tokens"] + i] = e.tokens[0]
+                h[off["positions"] + i] = start
+                h[off["token_req"] + i] = i
+                h[off["slots"] + i] = mgr.requests[e.rid].slot
+                h[off["req_first_position"] + i] = start
+                r = requests[i]
+                words.append(r.sampler.words(seed, r.uid, len(r.tokens)))
+            h[off["sample"]: off["sample"] + n * ops.SAMPLE_WORDS] = np.frombuffer(b"".join(words), dtype=np.int32)
+            h[off["sample"] + n * ops.SAMPLE_WORDS: off["sample"] + B * ops.SAMPLE_WORDS] = 0
+            rids = [e.rid for e in entries]
+            for g in range(len(mgr.kv_groups)):
+                o = off[f"table{g}"]
+                mgr.block_table(g, rids, out=h[o: o + n * W].reshape(n, W))
+                h[o + n * W: o + B * W] = -1
+            self.dev.copy_(self.host, non_blocking=True)
+            self.graph.replay()
+            ops.launch_count += self.n_kernels
+            self.out_host.copy_(self.out, non_blocking=True)
+            torch.cuda.current_stream().synchronize()
+        except BaseException:
+            for e in entries:          # the step did not run to its end: undo the reservations
+                mgr.rollback(e.rid)
+            raise
         for e in entries:
             mgr.commit(e.rid)
         eng.n_steps += 1
         o = self.out_host.numpy()
+        eng.host_status = int(o[2 * B])
         return o[:n].tolist(), o[B:B + n].view(np.float32).tolist()

@@ -21,7 +21,12 @@ Decisions, all made in ``plan`` (plain Python, no device):
             far (recompute); tokens already handed out stay handed out.  A request that could never
             fit the pool alone is refused at ``insert``;
 * finishing ``"length"`` at ``max_tokens`` generated tokens, ``"stop"`` when a stop sequence matches
-            (mlx_lm/generate.py:1504-1514); pages and slot are given back at once.
+            (mlx_lm/generate.py:1504-1514), ``"cancelled"`` for a request taken out with ``remove``
+            (reported once, by the next ``next``); pages and slot are given back at once.
+
+After every step that hands out tokens the scheduler looks at the status word the kernels set instead of
+faulting (a token, position or page id out of range, a bounded wait that gave up), which the sampler brought
+back with the tokens, and raises ``KernelError`` rather than hand out tokens of a step that went wrong.
 
 The scheduler talks to an engine through five calls (``add_request``, ``finish``, ``step``,
 ``cache`` for page arithmetic, ``max_len``), and to a ``sample`` callable; tests drive it with fakes.
@@ -68,6 +73,11 @@ class Request:
     n_generated: int = 0
     admitted_at: int = -1             # admission counter; -1 while waiting
     preemptions: int = 0
+    rid: object = None                # the request's name in the engine (None: its uid)
+
+    def __post_init__(self):
+        if self.rid is None:
+            self.rid = self.uid
 
     @property
     def remaining(self) -> int:
@@ -126,6 +136,11 @@ class Scheduler:
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []
         self._uid = 0
+        # uids start at 0 in every scheduler (and key the random draws, so that a seed gives the same tokens
+        # again); in the engine a request is named by (scheduler, uid), so that two schedulers on one engine
+        # never collide
+        self._namespace = engine.new_namespace() if hasattr(engine, "new_namespace") else None
+        self._cancelled: List[Response] = []
         self._admissions = 0
         self.stats = SchedulerStats()
         self.last_step_tokens = self.last_step_prompt_tokens = 0
@@ -150,22 +165,30 @@ class Scheduler:
         uid = self._uid
         self._uid += 1
         self.waiting.append(Request(uid, prompt, len(prompt), max_tokens, sampler or GREEDY, tuple(processors),
-                                    stop or StopSequenceMatcher()))
+                                    stop or StopSequenceMatcher(),
+                                    rid=uid if self._namespace is None else (self._namespace, uid)))
         return uid
 
-    def remove(self, uids: Sequence[int]) -> None:
+    def remove(self, uids: Sequence[int]) -> List[Response]:
+        """Take requests out at any stage (mlx_lm/generate.py:1777-1802).  Each gets one last response with
+        ``finish_reason="cancelled"`` and no token (-1), returned here and once more by the next ``next``."""
         uids = set(uids)
-        for r in [r for r in self.running if r.uid in uids]:
-            self.engine.finish(r.uid)
+        gone = [r for r in self.running if r.uid in uids]
+        for r in gone:
+            self.engine.finish(r.rid)
             self.running.remove(r)
+        gone += [r for r in self.waiting if r.uid in uids]
         self.waiting = deque(r for r in self.waiting if r.uid not in uids)
+        out = [Response(r.uid, -1, 0.0, "cancelled", all_tokens=list(r.tokens)) for r in gone]
+        self._cancelled.extend(out)
+        return out
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running)
+        return bool(self.waiting or self.running or self._cancelled)
 
     # ------------------------------------------------------------------ decisions
     def _preempt(self, victim: Request) -> None:
-        self.engine.finish(victim.uid)
+        self.engine.finish(victim.rid)
         self.running.remove(victim)
         victim.n_cached = 0
         victim.admitted_at = -1
@@ -177,7 +200,7 @@ class Scheduler:
         """The pages per group that n more tokens of r take, if the pools still have them beside the ``taken``
         pages of the entries planned so far; else None."""
         cache = self.engine.cache
-        need = cache.pages_needed(r.uid, n)
+        need = cache.pages_needed(r.rid, n)
         for t, c, g in zip(taken, need, cache.kv_groups):
             if t + c > g.pool.n_free:
                 return None
@@ -197,7 +220,7 @@ class Scheduler:
         return lo
 
     def _take(self, taken: List[int], r: Request, n: int) -> None:
-        for g, c in enumerate(self.engine.cache.pages_needed(r.uid, n)):
+        for g, c in enumerate(self.engine.cache.pages_needed(r.rid, n)):
             taken[g] += c
 
     def plan(self) -> List[PlannedEntry]:
@@ -237,10 +260,10 @@ class Scheduler:
                    and sum(1 for r in self.running if r.remaining > 1) < self.max_prefilling
                    and self.engine.cache.has_free_slot()):
                 r = self.waiting[0]
-                self.engine.add_request(r.uid)
+                self.engine.add_request(r.rid)
                 n = self._largest_portion(taken, r, min(r.remaining, self.prefill_step_size, budget))
                 if n == 0:
-                    self.engine.finish(r.uid)
+                    self.engine.finish(r.rid)
                     break
                 self._take(taken, r, n)
                 self.waiting.popleft()
@@ -258,11 +281,12 @@ class Scheduler:
 
     # ------------------------------------------------------------------ one iteration
     def next(self) -> Tuple[List[PromptProgress], List[Response]]:
+        cancelled, self._cancelled = self._cancelled, []
         planned = self.plan()
         self.last_step_tokens = self.last_step_prompt_tokens = 0
         if not planned:
-            return [], []
-        entries = [StepEntry(p.request.uid, p.request.tokens[p.request.n_cached:p.request.n_cached + p.n_tokens],
+            return [], cancelled
+        entries = [StepEntry(p.request.rid, p.request.tokens[p.request.n_cached:p.request.n_cached + p.n_tokens],
                              [p.n_tokens - 1] if p.wants_logits else []) for p in planned]
         sampled = [p.request for p in planned if p.wants_logits]
         fused = (len(sampled) == len(planned) and hasattr(self.engine, "decode_sampled")
@@ -272,6 +296,8 @@ class Scheduler:
         else:
             logits = self.engine.step(entries)
             tokens, logprobs = self.sample(logits, sampled) if sampled else ([], [])
+        if sampled:
+            self._check_status()
         self.stats.steps += 1
         self.stats.most_running = max(self.stats.most_running, len(self.running))
         prompts: List[PromptProgress] = []
@@ -297,8 +323,18 @@ class Scheduler:
                 elif r.n_generated >= r.max_tokens:
                     reason = "length"
                 if reason is not None:
-                    self.engine.finish(r.uid)
+                    self.engine.finish(r.rid)
                     self.running.remove(r)
                 responses.append(Response(r.uid, int(tok), lp, reason,
                                           all_tokens=list(r.tokens) if reason is not None else None))
-        return prompts, responses
+        return prompts, cancelled + responses
+
+    def _check_status(self) -> None:
+        """Raise if a kernel of the steps since the last look reported something (``Engine.host_status``: the
+        status word as the sampler's copy of the tokens brought it to the host; no synchronisation here)."""
+        word = getattr(self.engine, "host_status", 0)
+        if word:
+            from ..ops import KernelError, describe_status
+            self.engine.clear_status()
+            raise KernelError("a kernel reported: " + describe_status(word) + "; the tokens of this step are not "
+                              "handed out")

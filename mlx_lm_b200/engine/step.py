@@ -18,8 +18,6 @@ into one pinned host buffer and reach the device in one copy.
 
 from __future__ import annotations
 
-import os
-
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Optional, Sequence
 
@@ -139,7 +137,11 @@ class StepContext:
         return LayerCacheView("state", entry.write, state=g.data[g.index_of(entry.cache_id)], slots=self._slots)
 
     def gather_rows(self, x: torch.Tensor) -> torch.Tensor:
-        raise NotImplementedError("a model without a final norm needs a row-gather kernel")
+        """The rows of ``x`` whose logits are wanted, as a tensor of their own (what a final norm does on the
+        way for a model that has one)."""
+        out = self.ws.get("wanted_rows", self.n_logit_rows, x.shape[1], x.dtype)
+        ops.gather_rows(x, self.logit_rows, out, self.stream)
+        return out
 
 
 class Engine:
@@ -157,20 +159,13 @@ class Engine:
                 max_tokens = max_requests * self.max_len
             n_pages = (max_tokens + page_size - 1) // page_size
         libs = [n for n in d.kernel_libs() if model.dtype == torch.bfloat16 or n not in ops.BF16_ONLY_LIBS]
-        # Steps of single tokens can run as one persistent kernel over a table of phases where every launch of the
-        # step has a phase (ops/program.py): MLXB_DECODE_PROGRAM=1.  The default is the chain of kernels.
-        self.use_program = os.environ.get("MLXB_DECODE_PROGRAM", "0") == "1"
-        head_dims = {spec.head_dim for spec in d.cache_specs().values() if hasattr(spec, "head_dim")}
-        if self.use_program and model.dtype == torch.bfloat16 and len(head_dims) == 1:
-            tpk = 2
-            while tpk * 8 < next(iter(head_dims)):
-                tpk *= 2
-            libs.append(f"decode_program:MLXB_DP_TPK={tpk}")
         kernel_build.ensure_built(libs)      # compiled now, in parallel, if this is their first use
         self.cache = CacheManager(d.cache_specs(), page_size=page_size, n_pages=n_pages, max_requests=max_requests,
                                   max_len=self.max_len, dtype=model.dtype, device=model.device)
         self.ws = Workspace(model.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=model.device)
+        self.host_status = 0      # the status word as a sampler's copy of a step's tokens last brought it to the host
+        self._namespaces = 0
         self._host = [None, None]
         self._host_events = [None, None]
         self._dev: Optional[torch.Tensor] = None
@@ -194,6 +189,12 @@ class Engine:
 
     def has_request(self, rid: Hashable) -> bool:
         return rid in self.cache.requests
+
+    def new_namespace(self) -> int:
+        """A number no earlier caller got: schedulers that share this engine name their requests
+        ``(namespace, uid)`` and so never collide."""
+        self._namespaces += 1
+        return self._namespaces
 
     # ------------------------------------------------------------------ the step
     def _int_buffers(self, n: int):
@@ -256,13 +257,20 @@ class Engine:
         n_single = sum(1 for e in entries if len(e.tokens) == 1)
         n_portions = n_real - n_single
         # Shapes are rounded up so that few distinct step shapes occur (each shape's launches are recorded once
-        # and re-issued): every portion gets a span of rows that is a multiple of the attention tile, and the
-        # number of single-token entries goes up to the next power of two (multiples of 64 above 64).  The extra
-        # rows carry request index -1: the cache write and the attention kernels skip them, the other kernels
-        # compute rows nobody reads.  Models with parts that loop over the step's entries on the host keep exact shapes.
+        # and re-issued): every portion gets a span of rows that is a multiple of the attention tile (of 16 rows
+        # for a portion of up to 64 tokens, so that a short tail beside decoding requests stays a step of few
+        # rows), and the number of single-token entries goes up to the next power of two (multiples of 64 above
+        # 64).  The extra rows carry request index -1: the cache write and the attention kernels skip them, the
+        # other kernels compute rows nobody reads.  Models with parts that loop over the step's entries on the
+        # host keep exact shapes.
         rounding = self.use_replay
-        span = [len(e.tokens) if len(e.tokens) == 1 or not rounding else (len(e.tokens) + TQ - 1) // TQ * TQ
-                for e in entries]
+
+        def rows_of(n: int) -> int:
+            if n == 1 or not rounding:
+                return n
+            return (n + 15) // 16 * 16 if n <= 64 else (n + TQ - 1) // TQ * TQ
+
+        span = [rows_of(len(e.tokens)) for e in entries]
         n_fake = 0
         if rounding and n_single:
             bucket = 1
@@ -291,73 +299,78 @@ class Engine:
         h[off["tokens"]: off["tokens"] + T] = 0
         h[off["positions"]: off["positions"] + T] = 0
         h[off["token_req"]: off["token_req"] + T] = -1
-        t0 = 0
-        rows: List[int] = []
-        single_rows: List[int] = []
-        portion_rows: List[int] = []
-        tiles: List[tuple] = []
-        for r, e in enumerate(entries):
-            n = len(e.tokens)
-            start = mgr.reserve(e.rid, n)
-            slot = mgr.requests[e.rid].slot
-            h[off["tokens"] + t0: off["tokens"] + t0 + n] = e.tokens
-            h[off["positions"] + t0: off["positions"] + t0 + n] = np.arange(start, start + n, dtype=np.int32)
-            h[off["token_req"] + t0: off["token_req"] + t0 + n] = r
-            h[off["slots"] + r] = slot
-            h[off["req_first_token"] + r] = t0
-            h[off["req_first_position"] + r] = start
-            rows.extend(t0 + w for w in e.want)
-            if mixed:
-                (single_rows if n == 1 else portion_rows).extend(range(t0, t0 + span[r]))
-            if n > 1:
-                tiles.extend((t0 + a, min(TQ, n - a), r, start + a) for a in range(0, n, TQ))
-            ctx.spans.append(RequestSpan(e.rid, slot, t0, n, start))
-            ctx.max_q_len = max(ctx.max_q_len, n)
-            t0 += span[r]
-        for f in range(n_fake):                      # filler single-token entries
-            r = n_real + f
-            h[off["slots"] + r] = 0
-            h[off["req_first_token"] + r] = t0
-            h[off["req_first_position"] + r] = 0
-            if mixed:
-                single_rows.append(t0)
-            t0 += 1
-        h[off["req_first_token"] + R] = T
-        if L_rows:
-            rows.extend([rows[0]] * (L_rows - L))
-            h[off["logit_rows"]: off["logit_rows"] + L_rows] = rows
-        if mixed:
-            h[off["single_rows"]: off["single_rows"] + n_single_rows] = single_rows
-            h[off["portion_rows"]: off["portion_rows"] + T - n_single_rows] = portion_rows
-        if n_tiles:
-            tiles.sort(key=lambda t: -(t[3] + t[1]))     # tiles with the most keys start first
-            h[off["tiles"]: off["tiles"] + 4 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
-        rids = [e.rid for e in entries]
-        for g in range(len(mgr.kv_groups)):
-            o = off[f"table{g}"]
-            h[o: o + R * W] = -1
-            mgr.block_table(g, rids, out=h[o: o + n_real * W].reshape(n_real, W))
-        self._upload(hi, total)
-
-        view = lambda name, n: dev[off[name]: off[name] + n]
-        ctx.stream = ops.current_stream()
-        ctx.n_tokens, ctx.n_requests, ctx.n_logit_rows = T, R, L_rows
-        ctx.tokens, ctx.positions, ctx.token_req = view("tokens", T), view("positions", T), view("token_req", T)
-        ctx.logit_rows = view("logit_rows", L_rows)
-        ctx.req_first_token, ctx.req_first_position = view("req_first_token", R + 1), view("req_first_position", R)
-        ctx._slots = view("slots", R)
-        ctx.n_single, ctx.n_portion = n_single_rows, T - n_single_rows
-        if mixed:
-            ctx.single_rows = view("single_rows", n_single_rows)
-            ctx.portion_rows = view("portion_rows", T - n_single_rows)
-        if n_tiles:
-            ctx.portion_tiles, ctx.n_portion_tiles = view("tiles", 4 * n_tiles), n_tiles
-        ctx._tables = [view(f"table{g}", R * W).view(R, W) for g in range(len(mgr.kv_groups))]
         try:
+            t0 = 0
+            rows: List[int] = []
+            single_rows: List[int] = []
+            portion_rows: List[int] = []
+            tiles: List[tuple] = []
+            for r, e in enumerate(entries):
+                n = len(e.tokens)
+                start = mgr.reserve(e.rid, n)
+                slot = mgr.requests[e.rid].slot
+                h[off["tokens"] + t0: off["tokens"] + t0 + n] = e.tokens
+                h[off["positions"] + t0: off["positions"] + t0 + n] = np.arange(start, start + n, dtype=np.int32)
+                h[off["token_req"] + t0: off["token_req"] + t0 + n] = r
+                h[off["slots"] + r] = slot
+                h[off["req_first_token"] + r] = t0
+                h[off["req_first_position"] + r] = start
+                rows.extend(t0 + w for w in e.want)
+                if mixed:
+                    (single_rows if n == 1 else portion_rows).extend(range(t0, t0 + span[r]))
+                if n > 1:
+                    tiles.extend((t0 + a, min(TQ, n - a), r, start + a) for a in range(0, n, TQ))
+                ctx.spans.append(RequestSpan(e.rid, slot, t0, n, start))
+                ctx.max_q_len = max(ctx.max_q_len, n)
+                t0 += span[r]
+            for f in range(n_fake):                      # filler single-token entries
+                r = n_real + f
+                h[off["slots"] + r] = 0
+                h[off["req_first_token"] + r] = t0
+                h[off["req_first_position"] + r] = 0
+                if mixed:
+                    single_rows.append(t0)
+                t0 += 1
+            h[off["req_first_token"] + R] = T
+            if L_rows:
+                rows.extend([rows[0]] * (L_rows - L))
+                h[off["logit_rows"]: off["logit_rows"] + L_rows] = rows
+            if mixed:
+                h[off["single_rows"]: off["single_rows"] + n_single_rows] = single_rows
+                h[off["portion_rows"]: off["portion_rows"] + T - n_single_rows] = portion_rows
+            if n_tiles:
+                tiles.sort(key=lambda t: -(t[3] + t[1]))     # tiles with the most keys start first
+                h[off["tiles"]: off["tiles"] + 4 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
+            rids = [e.rid for e in entries]
+            for g in range(len(mgr.kv_groups)):
+                o = off[f"table{g}"]
+                h[o: o + R * W] = -1
+                mgr.block_table(g, rids, out=h[o: o + n_real * W].reshape(n_real, W))
+            self._upload(hi, total)
+
+            view = lambda name, n: dev[off[name]: off[name] + n]
+            ctx.stream = ops.current_stream()
+            ctx.n_tokens, ctx.n_requests, ctx.n_logit_rows = T, R, L_rows
+            ctx.tokens, ctx.positions, ctx.token_req = view("tokens", T), view("positions", T), view("token_req", T)
+            ctx.logit_rows = view("logit_rows", L_rows)
+            ctx.req_first_token, ctx.req_first_position = view("req_first_token", R + 1), view("req_first_position", R)
+            ctx._slots = view("slots", R)
+            ctx.n_single, ctx.n_portion = n_single_rows, T - n_single_rows
+            if mixed:
+                ctx.single_rows = view("single_rows", n_single_rows)
+                ctx.portion_rows = view("portion_rows", T - n_single_rows)
+            if n_tiles:
+                ctx.portion_tiles, ctx.n_portion_tiles = view("tiles", 4 * n_tiles), n_tiles
+            ctx._tables = [view(f"table{g}", R * W).view(R, W) for g in range(len(mgr.kv_groups))]
             logits = self._run(ctx, (T, R, L_rows, n_single_rows, n_tiles, ctx.stream, dev.data_ptr()))
-        finally:
+        except BaseException:
+            # The step did not run to its end: its positions are not part of the requests.  The pages taken for
+            # them go back, and the requests continue from where they were.
             for e in entries:
-                mgr.commit(e.rid)
+                mgr.rollback(e.rid)
+            raise
+        for e in entries:
+            mgr.commit(e.rid)
         self.n_steps += 1
         return logits if logits is None or L_rows == L else logits[:L]
 
@@ -402,22 +415,18 @@ class Engine:
         return graph.run(entries, requests, sampler.seed)
 
     def read_status(self) -> int:
-        """Bits kernels set instead of faulting (token, position or page id out of range).
-        Reading synchronises with the device and clears the word."""
+        """Bits kernels set instead of faulting (token, position or page id out of range, a bounded wait that
+        gave up).  Reading synchronises with the device and clears the word."""
         s = int(self.status.item())
         if s:
-            self.status.zero_()
-        if s & ops.ST_WAIT_TIMEOUT:
-            for g in self._graphs.values():    # a persistent kernel that gave up left its barrier words behind
-                if g.program is not None:
-                    g.program.reset()
+            self.clear_status()
         return s
+
+    def clear_status(self) -> None:
+        self.status.zero_()
+        self.host_status = 0
 
     def check_status(self) -> None:
         s = self.read_status()
         if s:
-            names = [n for b, n in ((ops.ST_TOKEN_RANGE, "token id out of range"),
-                                    (ops.ST_POSITION_RANGE, "position without a page or out of range"),
-                                    (ops.ST_PAGE_RANGE, "page id outside the pool"),
-                                    (ops.ST_WAIT_TIMEOUT, "a bounded wait in a kernel gave up")) if s & b]
-            raise ops.KernelError("a kernel reported: " + "; ".join(names))
+            raise ops.KernelError("a kernel reported: " + ops.describe_status(s))

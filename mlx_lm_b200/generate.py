@@ -35,7 +35,7 @@ DEFAULT_TOP_P = 1.0
 DEFAULT_MIN_P = 0.0
 DEFAULT_TOP_K = 0
 DEFAULT_XTC_PROBABILITY = 0.0
-DEFAULT_XTC_THRESHOLD = 0.0
+DEFAULT_XTC_THRESHOLD = 0.1    # the command line's default (mlx_lm/generate.py:124-128)
 DEFAULT_MIN_TOKENS_TO_KEEP = 1
 DEFAULT_SEED = None
 
@@ -100,15 +100,15 @@ def _encode(tokenizer: TokenizerWrapper, prompt) -> List[int]:
 def stream_generate(model, tokenizer: TokenizerWrapper, prompt: Union[str, List[int], torch.Tensor],
                     max_tokens: int = 256, sampler: Optional[Sampler] = None,
                     logits_processors: Optional[Sequence] = None, prefill_step_size: int = 2048,
-                    prompt_progress_callback: Optional[Callable[[int, int], None]] = None, seed: int = 0,
-                    return_logprobs: bool = False, engine: Optional[Engine] = None,
+                    prompt_progress_callback: Optional[Callable[[int, int], None]] = None,
+                    seed: Optional[int] = None, return_logprobs: bool = False, engine: Optional[Engine] = None,
                     ) -> Generator[GenerationResponse, None, None]:
     """Yield the generated text segment by segment.  Stops at an end-of-sequence token
     (``finish_reason="stop"``, the token is not part of the text) or after ``max_tokens``
-    (``"length"``); the last response carries the reason."""
+    (``"length"``); the last response carries the reason.  ``seed=None``: a fresh seed for every call."""
     tokens = _encode(tokenizer, prompt)
     engine = engine or get_engine(model)
-    dev_sampler = DeviceSampler(model.device, seed=seed, return_logprobs=return_logprobs)
+    dev_sampler = DeviceSampler(model.device, seed=seed, return_logprobs=return_logprobs, engine=engine)
     sched = Scheduler(engine, dev_sampler, max_requests=1, max_prefilling=1, prefill_step_size=prefill_step_size,
                       max_tokens_per_step=max(prefill_step_size, 1))
     stop = StopSequenceMatcher([[t] for t in tokenizer.eos_token_ids])
@@ -124,6 +124,8 @@ def stream_generate(model, tokenizer: TokenizerWrapper, prompt: Union[str, List[
                 for p in progress:
                     prompt_progress_callback(*p.progress)
             for r in responses:
+                if r.finish_reason == "cancelled":
+                    continue
                 if n == 0:
                     prompt_tps = len(tokens) / max(time.perf_counter() - tic, 1e-9)
                     tic = time.perf_counter()
@@ -143,14 +145,15 @@ def stream_generate(model, tokenizer: TokenizerWrapper, prompt: Union[str, List[
 def generate_step(prompt: Union[List[int], torch.Tensor], model, *, max_tokens: int = 256,
                   sampler: Optional[Sampler] = None, logits_processors: Optional[Sequence] = None,
                   prefill_step_size: int = 2048,
-                  prompt_progress_callback: Optional[Callable[[int, int], None]] = None, seed: int = 0,
+                  prompt_progress_callback: Optional[Callable[[int, int], None]] = None,
+                  seed: Optional[int] = None,
                   engine: Optional[Engine] = None) -> Generator[Tuple[int, torch.Tensor], None, None]:
     """Token ids in, ``(token, log-probabilities)`` out, one pair per generated token
     (mlx_lm/generate.py:298-462): the log-probabilities are the float32 ``[vocab]`` vector the token was drawn
     from, on the device.  No tokenizer and no end-of-sequence token: it stops after ``max_tokens``."""
     tokens = [int(t) for t in (prompt.flatten().tolist() if isinstance(prompt, torch.Tensor) else prompt)]
     engine = engine or get_engine(model)
-    dev_sampler = DeviceSampler(model.device, seed=seed, return_logprobs=True)
+    dev_sampler = DeviceSampler(model.device, seed=seed, return_logprobs=True, engine=engine)
     sched = Scheduler(engine, dev_sampler, max_requests=1, max_prefilling=1, prefill_step_size=prefill_step_size,
                       max_tokens_per_step=max(prefill_step_size, 1))
     uid = sched.insert(tokens, max_tokens, sampler or GREEDY, logits_processors or ())
@@ -161,7 +164,8 @@ def generate_step(prompt: Union[List[int], torch.Tensor], model, *, max_tokens: 
                 for p in progress:
                     prompt_progress_callback(*p.progress)
             for r in responses:
-                yield r.token, dev_sampler.last_logprobs[0].clone()
+                if r.finish_reason != "cancelled":
+                    yield r.token, dev_sampler.last_logprobs[0].clone()
     finally:
         sched.remove([uid])
 
@@ -224,10 +228,11 @@ class BatchGenerator:
                  sampler: Optional[Sampler] = None, logits_processors: Optional[Sequence] = None,
                  completion_batch_size: int = 32, prefill_batch_size: int = 8, prefill_step_size: int = 2048,
                  max_kv_size: Optional[int] = None, stream=None, max_tokens_per_step: Optional[int] = None,
-                 seed: int = 0, page_size: int = 16, num_pages: Optional[int] = None,
+                 seed: Optional[int] = None, page_size: int = 16, num_pages: Optional[int] = None,
                  engine: Optional[Engine] = None, return_logprobs: bool = False):
         if max_kv_size is not None:
-            raise ValueError("max_kv_size (a rotating cache) is not offered: GPT-2 attends all its positions")
+            raise ValueError("max_kv_size (a rotating cache for the whole run) is not offered: which keys a layer "
+                             "keeps is a property of its mixer (a window), not an option of a run")
         self.model = model
         self.max_tokens = max_tokens
         self.sampler = sampler or GREEDY
@@ -236,7 +241,7 @@ class BatchGenerator:
         self.prefill_batch_size, self.prefill_step_size = prefill_batch_size, prefill_step_size
         self.engine = engine or get_engine(model, page_size=page_size, num_pages=num_pages,
                                            max_requests=max(64, self.completion_batch_size))
-        self._sampler = DeviceSampler(model.device, seed=seed, return_logprobs=return_logprobs)
+        self._sampler = DeviceSampler(model.device, seed=seed, return_logprobs=return_logprobs, engine=self.engine)
         self._sched = Scheduler(self.engine, self._sampler, max_requests=self.completion_batch_size,
                                 max_prefilling=prefill_batch_size, prefill_step_size=prefill_step_size,
                                 max_tokens_per_step=max_tokens_per_step or max(prefill_step_size, 1))
@@ -282,6 +287,7 @@ class BatchGenerator:
                 for p, m, s, lp, sm in zip(prompts, max_tokens, samplers, logits_processors, stop_matchers)]
 
     def remove(self, uids: Sequence[int], return_prompt_caches: bool = False):
+        """Cancel requests at any stage; the next ``next()`` reports each once with ``finish_reason="cancelled"``."""
         self._sched.remove(uids)
         return {} if return_prompt_caches else None
 
@@ -334,7 +340,7 @@ def batch_generate(model, tokenizer, prompts: List[List[int]], prompt_caches=Non
                 if r.finish_reason is not None and verbose:
                     fin += 1
                     print(f"[batch_generate] Finished processing {fin}/{n} ...", end="\r")
-                if r.finish_reason != "stop":
+                if r.finish_reason not in ("stop", "cancelled"):
                     results[r.uid].append(r.token)
                     lps[r.uid].append(float(r.logprobs))
     gen.close()
@@ -352,46 +358,53 @@ def batch_generate(model, tokenizer, prompts: List[List[int]], prompt_caches=Non
 # ---------------------------------------------------------------------- command line
 
 def str2bool(string: str) -> bool:
+    """'F' and 'False' in any case are false, everything else is true (mlx_lm/generate.py:48-49)."""
     return string.lower() not in ["false", "f"]
 
 
 def setup_arg_parser() -> argparse.ArgumentParser:
-    p = argparse.ArgumentParser(prog="mlx_lm_b200.generate", description="LLM inference script")
+    """Options with mlx-lm's names, meanings and defaults (mlx_lm/generate.py:54-213) where this engine has
+    the feature; the help texts are this package's own."""
+    p = argparse.ArgumentParser(prog="mlx_lm_b200.generate",
+                                description="Generate text (or token ids) from a model folder on one GPU")
     p.add_argument("--model", type=str, default=None,
-                   help="The path to the local model directory (config.json, model.safetensors).")
+                   help="model folder holding config.json and model*.safetensors")
     p.add_argument("--random-weights", type=int, default=None, metavar="SEED",
-                   help="Instead of --model: make a model with seeded random weights from --config")
-    p.add_argument("--config", type=str, default=None, help="config.json for --random-weights")
+                   help="no --model: build a model with random weights drawn from this seed, sized by --config")
+    p.add_argument("--config", type=str, default=None, help="the config.json that --random-weights reads")
     p.add_argument("--prompt-tokens", type=str, default=None,
-                   help="The prompt as token ids separated by commas or blanks (instead of --prompt)")
-    p.add_argument("--fp32", action="store_true", help="Same as --dtype float32")
+                   help="prompt given as token ids (commas or blanks between them); replaces --prompt")
+    p.add_argument("--fp32", action="store_true", help="shorthand for --dtype float32")
     p.add_argument("--extra-eos-token", type=str, default=(), nargs="+",
-                   help="Add tokens in the list of eos tokens that stop generation.")
+                   help="further tokens at which generation ends")
     p.add_argument("--prompt", "-p", default=DEFAULT_PROMPT,
-                   help="Message to be processed by the model ('-' reads from stdin). A folder without a "
-                        "tokenizer takes token ids separated by blanks.")
+                   help="text to continue; '-' takes it from standard input; for a folder without a tokenizer, "
+                        "token ids with blanks between them")
     p.add_argument("--max-tokens", "-m", type=int, default=DEFAULT_MAX_TOKENS,
-                   help="Maximum number of tokens to generate")
-    p.add_argument("--temp", type=float, default=DEFAULT_TEMP, help="Sampling temperature")
-    p.add_argument("--top-p", type=float, default=DEFAULT_TOP_P, help="Sampling top-p")
-    p.add_argument("--min-p", type=float, default=DEFAULT_MIN_P, help="Sampling min-p")
-    p.add_argument("--top-k", type=int, default=DEFAULT_TOP_K, help="Sampling top-k")
+                   help="stop after this many new tokens")
+    p.add_argument("--temp", type=float, default=DEFAULT_TEMP, help="temperature; 0 picks the likeliest token")
+    p.add_argument("--top-p", type=float, default=DEFAULT_TOP_P,
+                   help="nucleus sampling: keep the likeliest tokens whose probabilities add up to this")
+    p.add_argument("--min-p", type=float, default=DEFAULT_MIN_P,
+                   help="drop tokens less likely than this fraction of the likeliest one")
+    p.add_argument("--top-k", type=int, default=DEFAULT_TOP_K, help="keep the k likeliest tokens (0: all)")
     p.add_argument("--xtc-probability", type=float, default=DEFAULT_XTC_PROBABILITY,
-                   help="Probability of XTC sampling to happen each next token")
+                   help="chance, per token, that XTC removes the top choices")
     p.add_argument("--xtc-threshold", type=float, default=DEFAULT_XTC_THRESHOLD,
-                   help="Thresold the probs of each next token candidate to be sampled by XTC")
+                   help="XTC removes every candidate above this probability except the least likely of them")
     p.add_argument("--min-tokens-to-keep", type=int, default=DEFAULT_MIN_TOKENS_TO_KEEP,
-                   help="Minimum tokens to keep for min-p sampling.")
-    p.add_argument("--seed", type=int, default=DEFAULT_SEED, help="PRNG seed")
+                   help="candidates that --min-p always leaves")
+    p.add_argument("--seed", type=int, default=DEFAULT_SEED,
+                   help="seed of the random draws (default: a new one every run)")
     p.add_argument("--ignore-chat-template", action="store_true",
-                   help="Accepted for compatibility: prompts are always used as they are.")
+                   help="has no effect: a prompt is always used exactly as given")
     p.add_argument("--verbose", type=str2bool, default=True,
-                   help="Log verbose output when 'True' or 'T' or only print the response when 'False' or 'F'")
-    p.add_argument("--prefill-step-size", type=int, default=2048, help="Tokens of the prompt run per step")
+                   help="'T'/'True': also print separators, speeds and memory; 'F'/'False': the response alone")
+    p.add_argument("--prefill-step-size", type=int, default=2048, help="prompt tokens run in one step")
     p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16",
-                   help="bfloat16: the serving kernels; float32: everything in true 32-bit")
-    p.add_argument("--page-size", type=int, default=16, help="Tokens per page of the key/value cache")
-    p.add_argument("--num-pages", type=int, default=None, help="Pages in the pool (default: room for 64 requests)")
+                   help="bfloat16: the serving kernels; float32: the whole model in true 32-bit arithmetic")
+    p.add_argument("--page-size", type=int, default=16, help="tokens in one page of the key/value cache")
+    p.add_argument("--num-pages", type=int, default=None, help="pages in the pool (default: enough for 64 requests)")
     return p
 
 
@@ -427,7 +440,7 @@ def main(argv: Optional[Sequence[str]] = None) -> None:
     engine = get_engine(model, page_size=args.page_size, num_pages=args.num_pages, max_requests=1 if args.num_pages
                         else 64)
     response = generate(model, tokenizer, prompt, verbose=args.verbose, max_tokens=args.max_tokens, sampler=sampler,
-                        prefill_step_size=args.prefill_step_size, seed=args.seed or 0, engine=engine)
+                        prefill_step_size=args.prefill_step_size, seed=args.seed, engine=engine)
     if not args.verbose:
         print(response)
 

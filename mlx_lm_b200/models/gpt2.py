@@ -17,6 +17,7 @@ from typing import Optional
 
 from ..config.base import BaseModelArgs, ConfigError, _positive_int
 from ..config.registry import register_architecture
+from ..parts.linear import ACTIVATIONS
 from ..parts import (MLP, Attention, Init, LayerNorm, LearnedAbsolute, ModelDescription, OutputHead, PreNormBlock,
                      TokenEmbedding)
 
@@ -54,8 +55,9 @@ class ModelArgs(BaseModelArgs):
                               "for GPT-2: its fused c_attn has 3*n_embd outputs")
         if not isinstance(self.layer_norm_epsilon, (int, float)) or self.layer_norm_epsilon <= 0:
             raise ConfigError(f"layer_norm_epsilon must be a positive number, got {self.layer_norm_epsilon!r}")
-        if self.activation_function != "gelu_new":
-            raise ConfigError(f"activation_function {self.activation_function!r}: GPT-2 here runs 'gelu_new' only")
+        if self.activation_function not in ACTIVATION_NAMES:
+            raise ConfigError(f"activation_function {self.activation_function!r} is not one of "
+                              f"{sorted(ACTIVATION_NAMES)}")
         if self.n_ctx is None:
             self.n_ctx = self.n_positions
 
@@ -92,5 +94,8 @@ def build(args: ModelArgs) -> ModelDescription:
         ignored_tensors=(r"h\.\d+\.attn\.bias", r"h\.\d+\.attn\.masked_bias"),
         args=args)
 
+
+# the activations the feed-forward's kernels know (csrc/activations.cuh), less the identity
+ACTIVATION_NAMES = frozenset(n for n in ACTIVATIONS if n not in (None, "none"))
 
 register_architecture("gpt2", ModelArgs, build)

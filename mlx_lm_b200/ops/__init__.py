@@ -21,7 +21,27 @@ import torch
 from . import build
 
 F32, BF16 = 0, 1
-EPI_NONE, EPI_GELU_NEW = 0, 1
+
+
+def _read_activations():
+    """``{name: code}`` from the one list of epilogue activations, csrc/activations.cuh, which every linear
+    kernel includes: lines ``X(IDENTIFIER, code, name)``."""
+    import os
+    import re
+
+    with open(os.path.join(build.CSRC, "activations.cuh")) as f:
+        text = f.read()
+    body = text[text.index("#define MLXB_ACTIVATION_LIST"):]
+    body = body[:body.index("\n\n")]
+    found = {m.group(3): int(m.group(2)) for m in re.finditer(r"X\((\w+),\s*(\d+),\s*(\w+)\)", body)}
+    if "none" not in found or sorted(found.values()) != list(range(len(found))):
+        raise RuntimeError(f"csrc/activations.cuh: cannot read the list of activations ({found})")
+    return found
+
+
+ACTIVATION_CODES = _read_activations()
+EPI_NONE = ACTIVATION_CODES["none"]
+EPI_GELU_NEW = ACTIVATION_CODES["gelu_new"]
 
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
@@ -35,6 +55,15 @@ ST_TOKEN_RANGE, ST_POSITION_RANGE, ST_PAGE_RANGE, ST_WAIT_TIMEOUT = 1, 2, 4, 8
 
 class KernelError(RuntimeError):
     pass
+
+
+def describe_status(word: int) -> str:
+    """The bits of a status word in words."""
+    names = [n for b, n in ((ST_TOKEN_RANGE, "token id out of range"),
+                            (ST_POSITION_RANGE, "position without a page or out of range"),
+                            (ST_PAGE_RANGE, "page id outside the pool"),
+                            (ST_WAIT_TIMEOUT, "a bounded wait in a kernel gave up")) if word & b]
+    return "; ".join(names) or f"status {word}"
 
 
 def require_cuda() -> None:
@@ -189,6 +218,20 @@ def row_stats(x, stats, eps: float, stream) -> None:
     if stats.shape != (R, 2) or not stats.is_contiguous():
         raise KernelError(f"row_stats: statistics {tuple(stats.shape)} for {R} rows")
     _call("norm", "mlxb_row_stats", _STATS_ARGS, _p(x), _p(stats), R, D, _rows(x, "row_stats x"), eps, stream)
+
+
+_GATHER_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+
+
+def gather_rows(x, rows, out, stream) -> None:
+    """``out[r] = x[rows[r]]`` (a row index outside ``x`` gives a row of zeros)."""
+    _need(x, out.dtype, "gather_rows x")
+    _need(rows, torch.int32, "gather_rows rows")
+    R, D = out.shape
+    if x.dim() != 2 or x.shape[1] != D or rows.numel() != R or not x.is_contiguous() or not out.is_contiguous():
+        raise KernelError(f"gather_rows: x {tuple(x.shape)}, {rows.numel()} indices, out {tuple(out.shape)}")
+    _call("norm", "mlxb_gather_rows", _GATHER_ARGS, dtype_code(out.dtype), _p(x), _p(rows), _p(out), R, D, x.shape[0],
+          stream)
 
 
 # --------------------------------------------------------------------------
@@ -502,16 +545,19 @@ def attention_decode(q, positions, token_req, block_table, k_pool, v_pool, out, 
 SAMPLE_WORDS, PROCESS_WORDS = 16, 8
 
 _SAMPLE_ARGS = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                c_void_p]
+                c_void_p, c_void_p, c_void_p]
 
 
-def sample(logits, params, out_token, out_logprob, stream, xtc_special=None, out_logprobs=None) -> None:
+def sample(logits, params, out_token, out_logprob, stream, xtc_special=None, out_logprobs=None, status=None,
+           status_out=None) -> None:
     """One token per row of float32 ``logits [R, V]``.
 
     ``params``: int32 ``[R, 16]`` holding the bit patterns of csrc/sampling.cu's ``SampleParams``;
     ``out_token`` int32 ``[R]``, ``out_logprob`` float32 ``[R]`` (log-probability of the chosen token
     under the unfiltered distribution); ``out_logprobs`` (optional) float32 ``[R, V]`` receives
-    ``logits - logsumexp(logits)``."""
+    ``logits - logsumexp(logits)``.  ``xtc_special``: int32 list of the rows' XTC special tokens, each
+    row's record naming its range.  ``status`` / ``status_out`` (int32, one word each): the kernel copies
+    the step's status word next to its results, so that the host reads both with one copy."""
     _need(logits, torch.float32, "sample logits")
     _need(params, torch.int32, "sample params")
     _need(out_token, torch.int32, "sample out_token")
@@ -529,8 +575,14 @@ def sample(logits, params, out_token, out_logprob, stream, xtc_special=None, out
     if xtc_special is not None:
         _need(xtc_special, torch.int32, "sample xtc_special")
         n_special = xtc_special.numel()
+    if (status is None) != (status_out is None):
+        raise KernelError("sample: status and status_out go together")
+    if status is not None:
+        _need(status, torch.int32, "sample status")
+        _need(status_out, torch.int32, "sample status_out")
     _call("sampling", "mlxb_sample", _SAMPLE_ARGS, _p(logits), _rows(logits, "sample logits"), R, V, _p(params),
-          _p(xtc_special), n_special, _p(out_token), _p(out_logprob), _p(out_logprobs), ldo, stream)
+          _p(xtc_special), n_special, _p(out_token), _p(out_logprob), _p(out_logprobs), ldo, _p(status),
+          _p(status_out), stream)
 
 
 _PROCESS_ARGS = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]

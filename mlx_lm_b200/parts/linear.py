@@ -17,7 +17,8 @@ import torch
 from .. import ops
 from .base import MATRIX, VECTOR, Init, Normed, ParamSpec, Part
 
-ACTIVATIONS = {None: ops.EPI_NONE, "none": ops.EPI_NONE, "gelu_new": ops.EPI_GELU_NEW}
+# name -> epilogue code, read from the list the kernels are compiled from (csrc/activations.cuh)
+ACTIVATIONS = {None: ops.EPI_NONE, **ops.ACTIVATION_CODES}
 
 
 class Linear(Part):
@@ -25,12 +26,14 @@ class Linear(Part):
     kernel_libs = ("gemm_simt", "gemm_smallm", "gemm_smallm_fold", "gemm_tcgen05")
 
     def __init__(self, name: str, n_in: int, n_out: int, bias: bool = True, stored: str = "out_in",
-                 weight_suffix: str = ".weight", init: Init = Init(), bias_init: Init = Init()):
+                 weight_suffix: str = ".weight", init: Init = Init(), bias_init: Init = Init(),
+                 tensor_core_from: Optional[int] = None):
         if stored not in ("out_in", "in_out"):
             raise ValueError(f"stored layout {stored!r}: 'out_in' or 'in_out'")
         self.name, self.n_in, self.n_out, self.has_bias, self.stored = name, n_in, n_out, bias, stored
         self.weight_name = name + weight_suffix
         self.init, self.bias_init = init, bias_init
+        self.tensor_core_from = self.TENSOR_CORE_FROM if tensor_core_from is None else int(tensor_core_from)
         self.weight: Optional[torch.Tensor] = None
         self.bias: Optional[torch.Tensor] = None
         self.folded = None        # see fold_norm
@@ -75,14 +78,27 @@ class Linear(Part):
         self.weight, self.bias = folded, bias.contiguous()
         return True
 
-    def fold_of(self, ctx, x: Normed):
-        """The ``fold`` argument of the kernels for this step's rows."""
+    # From this many output features on, steps of 33 to 64 rows run on the tcgen05 kernel rather than on the
+    # few-rows kernel (measured with a vocabulary-sized output: each of the few-rows kernel's many CTAs reads
+    # all the rows again).  An option of the layer, not of a model: ``Linear(..., tensor_core_from=n)``.
+    TENSOR_CORE_FROM = 16384
+
+    def few_rows(self, n_rows: int) -> bool:
+        """Whether a step of ``n_rows`` rows runs on the few-rows kernel (else: the tcgen05 kernel)."""
+        if n_rows > ops.SMALL_M:
+            return False
+        return not (n_rows > 32 and self.n_out >= self.tensor_core_from)
+
+    def fold_of(self, ctx, x: Normed, few: Optional[bool] = None):
+        """The ``fold`` argument of the kernels for this step's rows: ``(colsum, eps)`` for the few-rows
+        kernel, which finds the rows' statistics itself, ``(colsum, stats)`` with the statistics from
+        ``ops.row_stats`` for the tcgen05 kernel.  ``few``: which of the two runs (default: ``few_rows``)."""
         f, src = self.folded, x.source
         if (f is None or f.norm is not x.norm or x.rows is not None or src.stride(1) != 1 or src.stride(0) % 8
                 or src.data_ptr() % 16):
             raise ops.KernelError(f"{self.name}: the norm before this layer is folded into its weights; it takes "
                                   f"the rows before that norm, contiguous and 16-byte aligned")
-        if x.shape[0] <= ops.SMALL_M:
+        if self.few_rows(x.shape[0]) if few is None else few:
             return (f.colsum, f.eps)
         stats = ctx.ws.get("row_stats", x.shape[0], 2, torch.float32)
         ops.row_stats(src, stats, f.eps, ctx.stream)
@@ -93,18 +109,16 @@ class Linear(Part):
         to 64 rows, the tcgen05 kernel for more; an inner size that is no multiple of 8 (no 16-byte rows)
         goes to the generic kernel."""
         epi = ACTIVATIONS[activation]
+        few = self.few_rows(x.shape[0])      # decided once, before the fold's argument is made for that kernel
         fold = None
         if isinstance(x, Normed):
-            fold = self.fold_of(ctx, x)
+            fold = self.fold_of(ctx, x, few)
             x = x.source
         elif self.folded is not None:
             raise ops.KernelError(f"{self.name}: the norm before this layer is folded into its weights; it takes a "
                                   f"Normed, not a tensor")
         fast = (x.dtype == torch.bfloat16 and self.n_in % 8 == 0 and x.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0)
-        few = x.shape[0] <= ops.SMALL_M
-        if few and x.shape[0] > 32 and self.n_out >= 16384:
-            few = False       # a vocabulary-sized output at 33-64 rows: measured faster on the tcgen05 kernel
         if fast and few:
             ops.linear_few_rows(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual, fold=fold)
         elif fast:

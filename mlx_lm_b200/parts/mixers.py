@@ -61,7 +61,7 @@ class Attention(Mixer):
                 and src.stride(0) % 8 == 0 and src.data_ptr() % 16 == 0):
             # nothing to do to q and k before the cache: the projection's epilogue puts keys and values
             # into the pages itself
-            fold = self.qkv.fold_of(ctx, x) if isinstance(x, Normed) else None
+            fold = self.qkv.fold_of(ctx, x, few=T <= ops.SMALL_M) if isinstance(x, Normed) else None
             ops.linear_qkv_to_cache(src, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, ctx.token_req,
                                     cache.block_table, cache.k, cache.v, self.q_width, ctx.status, ctx.stream,
                                     fold=fold)

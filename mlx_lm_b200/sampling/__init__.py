@@ -33,12 +33,14 @@ class Sampler:
     xtc_special_tokens: tuple = ()
     seed: Optional[int] = None     # None: the scheduler's seed
 
-    def words(self, seed: int, request: int, position: int) -> bytes:
-        """The 16 words of csrc/sampling.cu's SampleParams for one row."""
+    def words(self, seed: int, request: int, position: int, special_offset: int = 0) -> bytes:
+        """The 16 words of csrc/sampling.cu's SampleParams for one row.  ``special_offset``: where this
+        row's XTC special tokens begin in the list the kernel is given."""
         s = self.seed if self.seed is not None else seed
         return struct.pack("<5f2i4I5i", self.temp, self.top_p, self.min_p, self.xtc_probability, self.xtc_threshold,
                            self.top_k, self.min_tokens_to_keep, s & 0xFFFFFFFF, (s >> 32) & 0xFFFFFFFF,
-                           request & 0xFFFFFFFF, position & 0xFFFFFFFF, 0, 0, 0, 0, 0)
+                           request & 0xFFFFFFFF, position & 0xFFFFFFFF, special_offset,
+                           len(self.xtc_special_tokens), 0, 0, 0)
 
     def __call__(self, logprobs, seed: int = 0, request: int = 0, position: int = 0):
         import torch

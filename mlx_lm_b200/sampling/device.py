@@ -3,7 +3,8 @@ chosen tokens back to the host in one copy."""
 
 from __future__ import annotations
 
-from typing import List, Sequence, Tuple
+import os
+from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -17,10 +18,16 @@ class DeviceSampler:
 
     Row ``i`` of ``logits`` belongs to ``requests[i]``, which carries its ``Sampler``, its
     processors, its token history and its uid; the position of the token being drawn is the
-    length of that history, so the random draw is a function of (seed, uid, position) alone."""
+    length of that history, so the random draw is a function of (seed, uid, position) alone.
 
-    def __init__(self, device, seed: int = 0, return_logprobs: bool = False):
-        self.device, self.seed, self.return_logprobs = device, int(seed), return_logprobs
+    ``seed=None`` draws a seed from the operating system, so that two unseeded runs differ, as they do in
+    mlx-lm, whose generator is seeded only by ``--seed`` (mlx_lm/generate.py:2067-2068).  With an ``engine``
+    the kernel brings the engine's status word back together with the tokens (``engine.host_status``)."""
+
+    def __init__(self, device, seed: Optional[int] = 0, return_logprobs: bool = False, engine=None):
+        if seed is None:
+            seed = int.from_bytes(os.urandom(8), "little")
+        self.device, self.seed, self.return_logprobs, self.engine = device, int(seed), return_logprobs, engine
         self._cap = 0
         self._host = self._dev_params = self._out = self._out_host = None
         self.last_logprobs = None
@@ -31,8 +38,8 @@ class DeviceSampler:
         cap = max(64, 2 * R)
         self._host = torch.empty(cap * ops.SAMPLE_WORDS, dtype=torch.int32).pin_memory()
         self._dev_params = torch.empty(cap * ops.SAMPLE_WORDS, dtype=torch.int32, device=self.device)
-        self._out = torch.empty(2 * cap, dtype=torch.int32, device=self.device)   # tokens | logprob bits
-        self._out_host = torch.empty(2 * cap, dtype=torch.int32).pin_memory()
+        self._out = torch.zeros(2 * cap + 1, dtype=torch.int32, device=self.device)   # tokens | logprob bits | status
+        self._out_host = torch.zeros(2 * cap + 1, dtype=torch.int32).pin_memory()
         self._cap = cap
 
     def __call__(self, logits: torch.Tensor, requests: Sequence) -> Tuple[List[int], List[float]]:
@@ -40,40 +47,52 @@ class DeviceSampler:
         stream = ops.current_stream()
         self._ensure(R)
         self._process(logits, requests, stream)
-        rec = b"".join(r.sampler.words(self.seed, r.uid, len(r.tokens)) for r in requests)
-        self._host.numpy()[:R * ops.SAMPLE_WORDS] = np.frombuffer(rec, dtype=np.int32)
+        special: List[int] = []          # every row's own XTC special tokens, one list after the other
+        recs = []
+        for r in requests:
+            recs.append(r.sampler.words(self.seed, r.uid, len(r.tokens), special_offset=len(special)))
+            special.extend(r.sampler.xtc_special_tokens)
+        self._host.numpy()[:R * ops.SAMPLE_WORDS] = np.frombuffer(b"".join(recs), dtype=np.int32)
         self._dev_params[:R * ops.SAMPLE_WORDS].copy_(self._host[:R * ops.SAMPLE_WORDS], non_blocking=True)
-        special = {t for r in requests for t in r.sampler.xtc_special_tokens}
-        xs = torch.tensor(sorted(special), dtype=torch.int32, device=self.device) if special else None
+        xs = torch.tensor(special, dtype=torch.int32, device=self.device) if special else None
         cap = self._cap
         tok = self._out[:R]
         lp = self._out[cap:cap + R].view(torch.float32)
         full = None
         if self.return_logprobs:
             full = torch.empty_like(logits)
-        ops.sample(logits, self._dev_params, tok, lp, stream, xtc_special=xs, out_logprobs=full)
+        status = self.engine.status if self.engine is not None else None
+        ops.sample(logits, self._dev_params, tok, lp, stream, xtc_special=xs, out_logprobs=full, status=status,
+                   status_out=self._out[2 * cap:] if status is not None else None)
         self.last_logprobs = full
-        self._out_host[:cap + R].copy_(self._out[:cap + R], non_blocking=True)
+        self._out_host.copy_(self._out, non_blocking=True)
         torch.cuda.current_stream().synchronize()
         h = self._out_host.numpy()
+        if self.engine is not None:
+            self.engine.host_status = int(h[2 * cap])
         return h[:R].tolist(), h[cap:cap + R].view(np.float32).tolist()
 
     def _process(self, logits, requests, stream) -> None:
-        procs = []
-        for r in requests:
-            mine = [p for p in r.processors if isinstance(p, LogitsProcessors)]
-            if len(mine) > 1:
-                raise ValueError("give one LogitsProcessors record per request (make_logits_processors returns one)")
-            procs.append(mine[0] if mine else None)
-        for i, r in enumerate(requests):   # user callables, as mlx-lm runs them: f(tokens, logits) -> logits
-            for p in r.processors:
-                if not isinstance(p, LogitsProcessors):
+        """Each request's processors in the order of its list.  The lists are walked in rounds: in round j the
+        rows whose j-th processor is a ``LogitsProcessors`` record go through the kernel together (the other
+        rows get a record that does nothing), and a row whose j-th processor is a callable is given to it as
+        mlx-lm does: ``f(tokens, logits[1, V]) -> logits`` (mlx_lm/generate.py:402-404)."""
+        rounds = max((len(r.processors) for r in requests), default=0)
+        for j in range(rounds):
+            procs = []
+            for i, r in enumerate(requests):
+                p = r.processors[j] if j < len(r.processors) else None
+                if p is not None and not isinstance(p, LogitsProcessors):
                     row = logits[i:i + 1]
                     new = p(torch.tensor(r.tokens, device=logits.device), row)
                     if new is not row:
                         row.copy_(new)
-        if not any(procs):
-            return
+                    p = None
+                procs.append(p)
+            if any(procs):
+                self._run_records(logits, requests, procs, stream)
+
+    def _run_records(self, logits, requests, procs, stream) -> None:
         R = len(requests)
         C = max(max((p.context_size for p in procs if p), default=0), 1)
         B = max(max((len(p.logit_bias) for p in procs if p), default=0), 1)

@@ -34,6 +34,10 @@ def linear(x, w, bias=None, activation=None, residual=None):
         y = y + bias.float()
     if activation == "gelu_new":
         y = gelu_new(y)
+    elif activation == "relu":
+        y = torch.relu(y)
+    elif activation not in (None, "none"):
+        raise ValueError(activation)
     if residual is not None:
         y = y + residual.float()
     return y

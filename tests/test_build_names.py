@@ -10,11 +10,11 @@ from mlx_lm_b200.ops import build
 
 def test_names_of_plain_libraries_and_variants():
     assert build._split("attention") == ("attention", [])
-    assert build._split("decode_program:MLXB_DP_TPK=8,OTHER=1") == ("decode_program", ["MLXB_DP_TPK=8", "OTHER=1"])
-    plain, variant = build.lib_path("decode_program"), build.lib_path("decode_program:MLXB_DP_TPK=8")
-    other = build.lib_path("decode_program:MLXB_DP_TPK=4")
+    assert build._split("attention:MLXB_X=8,OTHER=1") == ("attention", ["MLXB_X=8", "OTHER=1"])
+    plain, variant = build.lib_path("attention"), build.lib_path("attention:MLXB_X=8")
+    other = build.lib_path("attention:MLXB_X=4")
     assert len({plain, variant, other}) == 3
-    assert os.path.basename(variant).startswith("decode_program.MLXB_DP_TPK_8-") and variant.endswith(".so")
+    assert os.path.basename(variant).startswith("attention.MLXB_X_8-") and variant.endswith(".so")
     assert os.path.dirname(plain) == build.build_dir()
     assert build.lib_path("attention") == build.lib_path("attention")        # a pure function of the sources
 

@@ -129,3 +129,26 @@ def test_random_orders_never_lose_or_double_book(seed, page, n_pages):
         m.release(rid)
     m.check()
     assert m.pages_in_use() == [0, 0] and m.pages_free() == [n_pages, n_pages]
+
+
+def test_rollback_undoes_a_reservation():
+    """A step that failed gives its pages back and leaves the lengths where they were."""
+    m = CacheManager({0: FULL, 1: WIN}, page_size=16, n_pages=8, max_requests=3, max_len=256)
+    m.add_request("a")
+    m.add_request("b")
+    m.reserve("a", 20)
+    m.commit("a")
+    before = (m.pages_in_use(), m.length("a"), m.length("b"), list(m.requests["a"].pages[0]))
+    m.reserve("a", 30)                     # crosses two page edges
+    m.reserve("b", 5)
+    assert m.pages_in_use() != before[0]
+    m.rollback("a")
+    m.rollback("b")
+    m.check()
+    assert (m.pages_in_use(), m.length("a"), m.length("b"), list(m.requests["a"].pages[0])) == before
+    assert m.requests["a"].reserved == 0 and m.requests["b"].pages == [[], []]
+    m.rollback("b")                        # nothing reserved: nothing happens
+    assert m.reserve("a", 30) == 20        # and the request goes on from where it was
+    m.commit("a")
+    m.check()
+    assert m.length("a") == 50

@@ -30,7 +30,7 @@ def test_missing_keys_are_all_named():
 
 
 @pytest.mark.parametrize("key,value,word", [("n_embd", 65, "divisible"), ("n_layer", 0, "n_layer"),
-                                            ("activation_function", "relu", "gelu_new"),
+                                            ("activation_function", "swish", "gelu_new"),
                                             ("num_key_value_heads", 2, "num_key_value_heads"),
                                             ("layer_norm_epsilon", 0, "layer_norm_epsilon"), ("n_inner", -4, "n_inner")])
 def test_bad_values_name_the_key(key, value, word):

@@ -263,43 +263,159 @@ def test_decode_as_a_cuda_graph_equals_the_eager_step(dtype, tmp_path):
     engine.check_status()
 
 
-@pytest.mark.parametrize("config,seed,lens", [(CONFIG_A, 21, (5, 40, 17)), (CONFIG_B, 22, (90, 3, 33, 64, 12))])
-def test_decode_step_as_one_persistent_kernel(config, seed, lens, tmp_path, monkeypatch):
-    """The opt-in path that runs a whole decode step as one cooperative kernel over a table of phases
-    (csrc/decode_program.cu): its logits are those of the plain implementation, step after step, over page
-    edges, for a batch smaller than its bucket, and the barrier words survive many launches."""
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_failed_step_leaves_the_cache_as_it_was(dtype, tmp_path, monkeypatch):
+    """If the model raises in the middle of a step, the step's positions are not part of the requests: lengths
+    and pages are what they were, and the same tokens run again give the logits of an undisturbed run."""
     from mlx_lm_b200.engine import Engine, StepEntry
-    from mlx_lm_b200.engine.scheduler import Request
-    from mlx_lm_b200.sampling import Sampler
-    from mlx_lm_b200.sampling.device import DeviceSampler
     from mlx_lm_b200.weights import load_model
-    import mlx_lm_b200.parts.block as block
-    monkeypatch.setattr(block, "FOLD_NORMS", False)    # the program has phases for the plain kernels only
-    weights = make_model_dir(str(tmp_path), dict(config, ln_gain_std=0.3), seed, peaky=6.0)
-    model, _ = load_model(str(tmp_path), dtype="bfloat16")
-    n_steps = 36
-    seqs = [random_tokens(n + n_steps, config["vocab_size"], seed + n) for n in lens]
-    refs = [plain.logits(t, weights, config) for t in seqs]
-    eng = Engine(model, page_size=16, n_pages=sum((len(t) + 15) // 16 for t in seqs), max_requests=len(seqs))
-    eng.use_program = True
-    sampler = DeviceSampler(model.device, seed=0)
-    reqs = []
-    for i, (n, t) in enumerate(zip(lens, seqs)):
-        eng.add_request(i)
-        eng.step([StepEntry(i, t[:n], [])])
-        reqs.append(Request(i, list(t[:n + 1]), n + 1, 1000, Sampler()))
-    worst = 0.0
-    for s in range(n_steps):
-        entries = [StepEntry(r.uid, [r.tokens[-1]], [0]) for r in reqs]
-        eng.decode_sampled(entries, reqs, sampler)
-        graph = eng._graphs[next(b for b in eng.GRAPH_BUCKETS if b >= len(reqs))]
-        assert graph.program is not None, "the step has no program: the test would not test it"
-        for i, (r, n) in enumerate(zip(reqs, lens)):
-            worst = max(worst, rel(graph.logits[i], refs[i][n + s]))
-            if s + 1 < n_steps:
-                r.tokens.append(seqs[i][n + s + 1])        # the given sequence, not the sampled token
+    weights = make_model_dir(str(tmp_path), CONFIG_A, 2, peaky=6.0)
+    model, _ = load_model(str(tmp_path), dtype=dtype)
+    toks, other = random_tokens(60, 512, 1), random_tokens(20, 512, 2)
+    ref = plain.logits(toks, weights, CONFIG_A)
+    eng = Engine(model, page_size=16, n_pages=8, max_requests=2)
+    eng.add_request("a"); eng.add_request("b")
+    eng.step([StepEntry("a", toks[:30], []), StepEntry("b", other[:5], [])])
+    before = (eng.cache.length("a"), eng.cache.length("b"), eng.cache.pages_in_use())
+    real_run = model.run
+    blocks = model.description.blocks
+
+    def failing(ctx):          # the first block runs (and writes keys for the new positions), then the step dies
+        blocks[0].forward(ctx, model.description.embedding.forward(ctx, model.description.position),
+                          ctx.cache_view(model.description.order[0]))
+        raise RuntimeError("fault injected on the host")
+
+    monkeypatch.setattr(model, "run", failing)
+    with pytest.raises(RuntimeError, match="injected"):
+        eng.step([StepEntry("a", toks[30:50], [19]), StepEntry("b", other[5:6], [0])])     # crosses a page edge
+    eng.cache.check()
+    assert (eng.cache.length("a"), eng.cache.length("b"), eng.cache.pages_in_use()) == before
+    monkeypatch.setattr(model, "run", real_run)
+    lg = eng.step([StepEntry("a", toks[30:60], list(range(30))), StepEntry("b", other[5:6], [])])
+    assert rel(lg, ref[30:60]) <= TOL[dtype]
     eng.check_status()
-    assert worst <= TOL["bfloat16"], worst
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_trim_and_run_again(dtype, tmp_path):
+    """mlx-lm trims a prompt cache and generates again (tests/test_prompt_cache.py:266-294, ``KVCache.trim``,
+    mlx_lm/models/cache.py:378-381): here 70 tokens are run, the cache is cut back to 37 (across a page edge),
+    another request takes the freed pages, and the tail run again gives the rows of an uninterrupted run."""
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.weights import load_model
+    weights = make_model_dir(str(tmp_path), CONFIG_B, 9, peaky=8.0)
+    model, _ = load_model(str(tmp_path), dtype=dtype)
+    toks, other = random_tokens(70, 1000, 3), random_tokens(40, 1000, 4)
+    ref, ref_other = plain.logits(toks, weights, CONFIG_B), plain.logits(other, weights, CONFIG_B)
+    eng = Engine(model, page_size=16, n_pages=6, max_requests=2)        # 70 tokens hold 5 of the 6 pages
+    eng.add_request("a")
+    first = eng.step([StepEntry("a", toks, list(range(70)))]).clone()
+    assert rel(first, ref) <= TOL[dtype]
+    held = list(eng.cache.requests["a"].pages[0])
+    eng.cache.truncate("a", 37)
+    assert eng.cache.length("a") == 37 and eng.cache.pages_in_use() == [3]
+    eng.add_request("b")                                                 # takes the two pages just freed, and one more
+    lg = eng.step([StepEntry("b", other, [39])])
+    assert set(eng.cache.requests["b"].pages[0]) >= set(held[3:]) and rel(lg[0], ref_other[39]) <= TOL[dtype]
+    eng.finish("b")
+    again = [eng.step([StepEntry("a", toks[37:39], [0, 1])]).clone(),      # two tokens, then one, then the rest
+             eng.step([StepEntry("a", toks[39:40], [0])]).clone(),
+             eng.step([StepEntry("a", toks[40:70], list(range(30)))]).clone()]
+    assert rel(torch.cat(again), ref[37:]) <= TOL[dtype]
+    assert rel(torch.cat(again), first[37:]) <= TOL[dtype] * 0.5
+    eng.check_status()
+    eng.cache.check()
+
+
+def test_a_folded_norm_before_a_very_wide_layer(tmp_path):
+    """33 to 64 rows into a layer of 16384 or more outputs run on the tcgen05 kernel; with the norm before it
+    folded into its weights that kernel needs the rows' statistics, not the few-rows kernel's epsilon."""
+    from mlx_lm_b200.parts import LayerNorm, Linear
+    D, N = 64, 16384
+    ln, lin = LayerNorm("ln", D, 1e-5), Linear("wide", D, N, bias=True)
+    w = bind(ln, torch.bfloat16, seed=1)
+    w.update(bind(lin, torch.bfloat16, seed=2))
+    ref_w, ref_b = w["wide.weight"], w["wide.bias"]
+    assert lin.fold_norm(ln)
+    g = torch.Generator().manual_seed(5)
+    for rows in (40, 20, 130):
+        x = (torch.randn(rows, D, generator=g) * 2 + 0.5).to(torch.bfloat16)
+        ctx = part_ctx(rows)
+        out = torch.empty(rows, N, dtype=torch.bfloat16, device="cuda")
+        assert lin.few_rows(rows) == (rows <= 32)
+        lin.forward(ctx, ln.deferred(ctx, x.cuda()), out)
+        want = plain.layer_norm(x.float(), w["ln.weight"], w["ln.bias"], 1e-5) @ ref_w.T + ref_b
+        assert rel(out, want) <= 2e-2, rows
+
+
+def test_a_model_without_a_final_norm(tmp_path):
+    """``ModelDescription.final_norm`` may be None: the rows whose logits are wanted are then gathered as they
+    are and go to the output head (a toy model defined here)."""
+    from mlx_lm_b200.config import BaseModelArgs, register_architecture
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.parts import (MLP, Attention, Init, LayerNorm, ModelDescription, NoPosition, OutputHead,
+                                   PreNormBlock, TokenEmbedding)
+    from mlx_lm_b200.weights import load_model, write_random_model
+    from safetensors.torch import load_file
+    W, V = 48, 83
+
+    @dataclass
+    class Args(BaseModelArgs):
+        model_type: str
+        activation: str
+
+    def build(a):
+        emb = TokenEmbedding("emb", V, W, init=Init(0.0, 0.5))
+        blk = PreNormBlock(LayerNorm("n1", W, 1e-5), Attention("mix", W, 3, 16, qkv_name="qkv", out_name="out",
+                                                               init=Init(0.0, 0.3)),
+                           LayerNorm("n2", W, 1e-5), MLP("ff", W, 72, activation=a.activation, up_name="up",
+                                                         down_name="down", init=Init(0.0, 0.3)))
+        return ModelDescription("toy_no_final_norm", W, V, emb, NoPosition(), [blk], None,
+                                OutputHead(V, W, tied_to=None, name="head"), args=a)
+
+    register_architecture("toy_no_final_norm", Args, build, replace=True)
+    for dtype, tolerance in (("float32", 5e-5), ("bfloat16", 3e-2)):
+        write_random_model(str(tmp_path), dict(model_type="toy_no_final_norm", activation="relu"), seed=8)
+        w = {k: v.float() for k, v in load_file(str(tmp_path / "model.safetensors")).items()}
+        toks = random_tokens(30, V, 1)
+        x = w["emb.weight"][torch.tensor(toks)]
+        h = plain.layer_norm(x, w["n1.weight"], w["n1.bias"], 1e-5)
+        q, k, v = plain.split_heads(h @ w["mix.qkv.weight"].T + w["mix.qkv.bias"], 3)
+        x = x + plain.causal_attention(q, k, v) @ w["mix.out.weight"].T + w["mix.out.bias"]
+        h = plain.layer_norm(x, w["n2.weight"], w["n2.bias"], 1e-5)
+        x = x + torch.relu(h @ w["ff.up.weight"].T + w["ff.up.bias"]) @ w["ff.down.weight"].T + w["ff.down.bias"]
+        ref = x @ w["head.weight"].T
+        model, _ = load_model(str(tmp_path), dtype=dtype)
+        eng = Engine(model, page_size=16, n_pages=4, max_requests=1, max_len=64)
+        eng.add_request(0)
+        got = [eng.step([StepEntry(0, toks[:17], [3, 16, 0])]).clone(), eng.step([StepEntry(0, toks[17:18], [0])]).clone(),
+               eng.step([StepEntry(0, toks[18:], list(range(12)))]).clone()]
+        assert rel(torch.cat(got), ref[[3, 16, 0, 17] + list(range(18, 30))]) <= tolerance, dtype
+        eng.check_status()
+
+
+def test_benchmark_and_random_weights_sub_commands(tmp_path):
+    """``python -m mlx_lm_b200 random_weights`` writes a model folder and ``... benchmark`` times it with the
+    report lines of mlx-lm's benchmark (mlx_lm/benchmark.py:117-176), for a batch of one and of three."""
+    import json
+    import subprocess
+    import sys
+    from helpers import ROOT
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(dict(CONFIG_A, ln_gain_std=0.2)))
+    run = lambda *a: subprocess.run([sys.executable, "-m", "mlx_lm_b200", *a], cwd=ROOT, capture_output=True,
+                                    text=True, timeout=600)
+    r = run("random_weights", "--config", str(cfg), "--seed", "3", "--out", str(tmp_path / "m"))
+    assert r.returncode == 0, r.stderr
+    assert (tmp_path / "m" / "config.json").exists() and (tmp_path / "m" / "model.safetensors").exists()
+    for batch in (1, 3):
+        r = run("benchmark", "--model", str(tmp_path / "m"), "-p", "16", "-g", "8", "-n", "1", "-b", str(batch))
+        assert r.returncode == 0, r.stderr
+        lines = r.stdout.strip().splitlines()
+        assert lines[0] == "Running warmup.."
+        assert lines[1] == f"Timing with prompt_tokens=16, generation_tokens=8, batch_size={batch}."
+        assert lines[2].startswith("Trial 1:  prompt_tps=") and "generation_tps=" in lines[2] and "total_time=" in lines[2]
+        assert lines[3].startswith("Averages: prompt_tps=") and "peak_memory=" in lines[3]
 
 
 def test_command_line(tmp_path):

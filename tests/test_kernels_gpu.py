@@ -239,6 +239,48 @@ def test_linear_tensor_cores(ops, M, N, K):
     assert int(status.item()) == 0
 
 
+@pytest.mark.parametrize("M,N,K", [(3, 200, 96), (40, 1000, 320), (200, 320, 96)])
+def test_every_activation_of_the_list_in_every_linear_kernel(ops, M, N, K):
+    """The epilogue activations are one list (csrc/activations.cuh) that every linear kernel is compiled from
+    and the Python side reads: each name of the list runs in the generic (both dtypes), the few-rows and the
+    tcgen05 kernel and gives what the plain statement gives; a code outside the list is refused."""
+    from mlx_lm_b200.parts.linear import ACTIVATIONS
+    assert set(ops.ACTIVATION_CODES) == {"none", "gelu_new", "relu"} and ACTIVATIONS[None] == ops.EPI_NONE
+    g = torch.Generator().manual_seed(M + N)
+    x32 = torch.randn(M, K, generator=g).to(torch.bfloat16).float()
+    w32 = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).float()
+    b = torch.randn(N, generator=g).cuda()
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for name, code in ops.ACTIVATION_CODES.items():
+        ref = R.linear(x32, w32, b.cpu(), name)
+        if name == "relu":
+            assert float((ref == 0).float().mean()) > 0.2          # the clamp is exercised
+        for dtype in DTYPES:
+            x, w = x32.to(dtype).cuda(), w32.to(dtype).cuda()
+            out = torch.empty(M, N, dtype=dtype, device="cuda")
+            ops.linear_generic(x, w, b, out, stream(), epilogue=code)
+            assert rel_err(out, ref) <= tol(dtype, 2e-6, 6e-3), (name, dtype)
+        x, w = x32.to(torch.bfloat16).cuda(), w32.to(torch.bfloat16).cuda()
+        out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+        if M <= 64:
+            ops.linear_few_rows(x, w, b, out, stream(), epilogue=code)
+        else:
+            ops.linear_tensor_cores(x, w, b, out, status, stream(), epilogue=code)
+        assert rel_err(out, ref) <= 6e-3, name
+    with pytest.raises(ops.KernelError):
+        ops.linear_generic(x, w, b, out, stream(), epilogue=len(ops.ACTIVATION_CODES))
+    assert int(status.item()) == 0
+
+
+def test_gather_rows(ops):
+    for dtype in DTYPES:
+        x = torch.randn(37, 50).to(dtype).cuda()
+        rows = torch.tensor([5, 0, 36, 5, 99, -1], dtype=torch.int32).cuda()     # the last two lie outside
+        out = torch.full((6, 50), 7.0, dtype=dtype, device="cuda")
+        ops.gather_rows(x, rows, out, stream())
+        assert torch.equal(out[:4], x[[5, 0, 36, 5]]) and float(out[4:].abs().max()) == 0.0
+
+
 def test_linear_tensor_cores_finds_one_hot_entries(ops):
     """One-hot rows and columns: the output must be exactly the picked weight entry, which pins down the
     operand layouts (swizzle, K steps inside a stage, tile edges) far better than random data."""

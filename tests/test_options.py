@@ -14,7 +14,7 @@ def test_command_line_names_and_defaults():
     G = importlib.import_module("mlx_lm_b200.generate")
     a = G.setup_arg_parser().parse_args([])
     assert (a.prompt, a.max_tokens, a.temp, a.top_p, a.min_p, a.top_k) == ("hello", 100, 0.0, 1.0, 0.0, 0)
-    assert (a.xtc_probability, a.xtc_threshold, a.min_tokens_to_keep, a.seed) == (0.0, 0.0, 1, None)
+    assert (a.xtc_probability, a.xtc_threshold, a.min_tokens_to_keep, a.seed) == (0.0, 0.1, 1, None)   # mlx_lm/generate.py:124-128
     assert a.verbose is True and a.ignore_chat_template is False and a.model is None
     assert a.dtype == "bfloat16" and a.page_size == 16 and a.prefill_step_size == 2048
     b = G.setup_arg_parser().parse_args(["--model", "m", "-p", "5 6", "-m", "7", "--temp", "0.5", "--top-p", "0.9",

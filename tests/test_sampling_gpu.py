@@ -147,3 +147,43 @@ def test_logits_processors():
     for i, (kw, h) in enumerate(zip(settings, histories)):
         assert np.abs(dev[i].cpu().numpy() - S.process(x[i], h, **kw)).max() < 1e-5, i
     assert make_logits_processors() == []
+
+
+def test_device_sampler_rows_keep_their_own_options():
+    """Through ``DeviceSampler``, as the scheduler calls it: every row has its own XTC special tokens (one
+    request's exemptions protect nothing in another's row), processors run in the order of each request's list,
+    the engine's status word comes back with the tokens, and an unseeded sampler draws a seed of its own."""
+    from types import SimpleNamespace
+
+    from mlx_lm_b200.sampling import make_logits_processors, make_sampler
+    from mlx_lm_b200.sampling.device import DeviceSampler
+    probs = np.array([0.4, 0.3, 0.15, 0.15])
+    plain_xtc = make_sampler(1.0, xtc_probability=1.0, xtc_threshold=0.2)
+    keeps_0 = make_sampler(1.0, xtc_probability=1.0, xtc_threshold=0.2, xtc_special_tokens=(0,))
+    engine = SimpleNamespace(status=torch.zeros(1, dtype=torch.int32, device="cuda"), host_status=-1)
+    ds = DeviceSampler("cuda", seed=4, engine=engine)
+    seen = [set(), set(), set()]
+    for p in range(60):
+        reqs = [SimpleNamespace(uid=u, tokens=[0] * p, sampler=s, processors=())
+                for u, s in enumerate((keeps_0, plain_xtc, keeps_0))]
+        logits = torch.tensor(np.log(np.stack([probs] * 3)), dtype=torch.float32).cuda()
+        toks, _ = ds(logits, reqs)
+        for u, t in enumerate(toks):
+            seen[u].add(t)
+        assert engine.host_status == 0
+    assert seen[0] == seen[2] == {0, 1, 2, 3} and seen[1] == {1, 2, 3}
+    engine.status.fill_(6)
+    ds(logits, reqs)
+    assert engine.host_status == 6
+    # order of processors: a callable that doubles the logits and a bias of +1 on token 2 do not commute
+    (bias,) = make_logits_processors(logit_bias={2: 1.0})
+    double = lambda tokens, lg: lg * 2.0
+    base = torch.tensor([[0.0, 1.0, 1.2, -1.0]], dtype=torch.float32)
+    greedy = make_sampler(0.0)
+    out = []
+    for procs in ((double, bias), (bias, double)):
+        lg = base.clone().cuda()
+        ds([lg][0], [SimpleNamespace(uid=0, tokens=[1], sampler=greedy, processors=procs)])
+        out.append(lg[0].cpu().tolist())
+    assert out[0] == pytest.approx([0.0, 2.0, 3.4, -2.0]) and out[1] == pytest.approx([0.0, 2.0, 4.4, -2.0])
+    assert DeviceSampler("cuda", seed=None).seed != DeviceSampler("cuda", seed=None).seed

@@ -138,7 +138,8 @@ def test_stop_sequence_and_remove():
             out.setdefault(r.uid, []).append(r)
     assert [r.token for r in out[a]] == want[:5] and out[a][-1].finish_reason == "stop"
     assert out[a][-1].all_tokens == list(range(6)) + want[:5]
-    assert len(out[b]) == 3 and eng.cache.pages_in_use() == [0]
+    # three tokens, then the one response that says it was taken out
+    assert [r.finish_reason for r in out[b]] == [None, None, None, "cancelled"] and eng.cache.pages_in_use() == [0]
 
 
 def test_pages_run_out_newest_request_is_recomputed():
@@ -246,8 +247,8 @@ def test_generate_step_drives_the_scheduler_for_one_request(monkeypatch):
             return ("log-probabilities of", self.token)
 
     class StandInSampler:
-        def __init__(self, device, seed=0, return_logprobs=False):
-            assert return_logprobs
+        def __init__(self, device, seed=0, return_logprobs=False, engine=None):
+            assert return_logprobs and engine is eng
             self.last_logprobs = None
 
         def __call__(self, rows, requests):
@@ -271,3 +272,67 @@ def test_generate_step_drives_the_scheduler_for_one_request(monkeypatch):
     next(gen), next(gen)
     gen.close()
     assert eng.cache.pages_in_use() == [0]
+
+
+def test_a_status_word_from_the_kernels_stops_the_tokens():
+    """The sampler brings the kernels' status word back with the tokens; if it is not zero the scheduler raises
+    instead of handing the step's tokens out, and clears the word."""
+    from mlx_lm_b200.ops import ST_PAGE_RANGE, ST_WAIT_TIMEOUT, KernelError
+
+    class Reporting(FakeEngine):
+        host_status = 0
+        cleared = 0
+
+        def clear_status(self):
+            self.host_status = 0
+            self.cleared += 1
+
+    eng = Reporting(n_pages=8)
+    s = Scheduler(eng, fake_sample)
+    uid = s.insert(list(range(10)), max_tokens=4)
+    _, gens = s.next()
+    assert [r.uid for r in gens] == [uid]
+    eng.host_status = ST_PAGE_RANGE | ST_WAIT_TIMEOUT
+    with pytest.raises(KernelError) as err:
+        s.next()
+    assert "page id outside the pool" in str(err.value) and "bounded wait" in str(err.value)
+    assert eng.host_status == 0 and eng.cleared == 1
+
+
+def test_removed_requests_are_reported_as_cancelled_once():
+    eng = FakeEngine(n_pages=16)
+    s = Scheduler(eng, fake_sample, max_requests=1)
+    a = s.insert(list(range(20)), max_tokens=50)
+    b = s.insert(list(range(5)), max_tokens=50)          # still waiting: only one request runs
+    s.next()
+    gone = s.remove([a, b])
+    assert sorted(r.uid for r in gone) == [a, b] and all(r.finish_reason == "cancelled" and r.token == -1 for r in gone)
+    assert eng.cache.pages_in_use() == [0] and s.has_work()
+    _, gens = s.next()
+    assert sorted((r.uid, r.finish_reason) for r in gens) == [(a, "cancelled"), (b, "cancelled")]
+    assert not s.has_work() and s.next() == ([], [])
+
+
+def test_two_schedulers_on_one_engine_do_not_collide():
+    """Uids start at 0 in every scheduler (they key the random draws); in the engine a request is named with
+    the scheduler's namespace as well."""
+    class Spaces(FakeEngine):
+        n = 0
+
+        def new_namespace(self):
+            self.n += 1
+            return self.n
+
+    eng = Spaces(n_pages=16)
+    s1, s2 = Scheduler(eng, fake_rid_sample), Scheduler(eng, fake_rid_sample)
+    u1, u2 = s1.insert(list(range(9)), max_tokens=3), s2.insert(list(range(4)), max_tokens=3)
+    assert u1 == u2 == 0
+    s1.next(); s2.next(); s1.next(); s2.next()
+    assert set(eng.cache.requests) == {(1, 0), (2, 0)}
+    run(s1); run(s2)
+    assert eng.cache.pages_in_use() == [0]
+
+
+def fake_rid_sample(rows, requests):
+    assert [r.rid for r in requests] == [rid for rid, _ in rows]
+    return [token_fn(r.uid, pos + 1) for r, (_, pos) in zip(requests, rows)], [0.0] * len(rows)

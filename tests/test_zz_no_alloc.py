@@ -72,6 +72,30 @@ def test_no_alloc_entry_point_matches_the_ordinary_one(dtype):
         scale = max(1e-6, float(want.float().abs().max()))
         assert float((got.float() - want.float()).abs().max()) / scale <= tol
         assert float(got.float().abs().max()) > 0
+    # A position the chunks do not cover: that row is skipped and reported in the status word, it takes no
+    # ticket from the library's counters, and the next, valid call is as right as before.
+    c = _case(3, 3, Hq, Hkv, Dh, page, [40, 200, 90], dtype)
+    bad = c["positions"].clone()
+    bad[1] = n_chunks * chunk           # first position beyond the covered range
+    got = torch.zeros(3, Hq * Dh, dtype=dtype, device="cuda")
+    call = lambda positions: fn(ops.dtype_code(dtype), c["q"].data_ptr(), Hq * Dh, None, positions.data_ptr(),
+                                c["token_req"].data_ptr(), c["bt"].data_ptr(), c["width"], c["n_pages"], page, Hq, Hkv,
+                                Dh, 0, Dh ** -0.5, c["k"].data_ptr(), c["v"].data_ptr(), n_chunks, chunk,
+                                got.data_ptr(), Hq * Dh, 3, status.data_ptr(), stream)
+    assert call(bad) == 0, lib.mlxb_last_error()
+    torch.cuda.synchronize()
+    assert int(status.item()) == ops.ST_POSITION_RANGE
+    assert float(got[1].float().abs().max()) == 0.0 and float(got[0].float().abs().max()) > 0
+    status.zero_()
+    want = torch.zeros_like(got)
+    scratch = torch.empty(ops.attention_decode_scratch(3, Hq, Dh, max_len, chunk), device="cuda")
+    counters = torch.zeros(3 * Hq, dtype=torch.int32, device="cuda")
+    ops.attention_decode(c["q"], c["positions"], c["token_req"], c["bt"], c["k"], c["v"], want, Hq, Dh ** -0.5, 0,
+                         scratch, counters, max_len, status, stream, chunk=chunk)
+    assert call(c["positions"]) == 0, lib.mlxb_last_error()
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0
+    assert float((got.float() - want.float()).abs().max()) / max(1e-6, float(want.float().abs().max())) <= tol
     # beyond the built-in array: refused with a message, nothing launched
     rows_too_many = MAX_FLOATS // (Hq * n_chunks * (Dh + 2)) + 1
     rc = fn(ops.dtype_code(dtype), c["q"].data_ptr(), Hq * Dh, None, c["positions"].data_ptr(),
