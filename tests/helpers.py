@@ -20,6 +20,17 @@ CONFIG_B = dict(model_type="gpt2", n_layer=3, n_embd=96, n_head=3, n_inner=320, 
                 layer_norm_epsilon=1e-6, activation_function="gelu_new", ln_gain_std=0.1)
 
 
+# A third configuration: heads of 64 (the head size of the benchmarked models, which alone runs the tcgen05
+# attention kernel for portions), two heads, sizes that differ from A and B.
+CONFIG_C = dict(model_type="gpt2", n_layer=2, n_embd=128, n_head=2, n_inner=384, vocab_size=640, n_positions=512,
+                layer_norm_epsilon=3e-6, activation_function="gelu_new", ln_gain_std=0.2)
+
+# The layer sizes of GPT-2 medium (width 1024, 16 heads of 64, inner width 4096, vocabulary 50257, 1024
+# positions) with two of its 24 layers: the shapes of the benchmark's launches at a cost of seconds on the CPU.
+MEDIUM_2_LAYERS = dict(model_type="gpt2", n_layer=2, n_embd=1024, n_head=16, n_inner=4096, vocab_size=50257,
+                       n_positions=1024, layer_norm_epsilon=1e-5, activation_function="gelu_new", ln_gain_std=0.1)
+
+
 def make_model_dir(path, config, seed, peaky=0.0, dtype="bfloat16"):
     """Write a random model folder; ``peaky`` > 0 multiplies the query and key columns of every
     c_attn weight so that attention is sharp and a wrong or missing key changes the logits visibly."""

@@ -10,7 +10,7 @@ import pytest
 import torch
 
 import plain_gpt2 as plain
-from helpers import (CONFIG_A, CONFIG_B, Trace, make_model_dir, max_live_tokens, mixed_schedule, random_tokens,
+from helpers import (CONFIG_A, CONFIG_B, CONFIG_C, Trace, make_model_dir, max_live_tokens, mixed_schedule, random_tokens,
                      run_trace)
 
 pytestmark = pytest.mark.gpu
@@ -20,8 +20,12 @@ TOL = {"float32": 2e-5, "bfloat16": 3e-2}
 
 CASES = {
     "A": (CONFIG_A, 0, 0.0, [23, 29, 100, 128, 65]),
+    "A-sharp": (CONFIG_A, 3, 12.0, [128, 61, 97]),
     "B": (CONFIG_B, 1, 0.0, [29, 55, 88, 200, 256]),
     "B-sharp": (CONFIG_B, 2, 12.0, [88, 256, 130]),
+    # heads of 64: lengths that cross the 128-key blocks and the 128-query tiles of the tcgen05 attention kernel
+    "C": (CONFIG_C, 4, 0.0, [130, 257, 300, 512]),
+    "C-sharp": (CONFIG_C, 5, 8.0, [512, 129, 384]),
 }
 
 
@@ -32,11 +36,16 @@ def build_trace(lengths, vocab, seed):
         tr.whole(f"{name}:whole", toks)
     for name, toks in reqs.items():
         tr.bulk_then_single(f"{name}:tail", toks, tail=32)
+    long = max(len(t) for t in reqs.values()) > 256
     for name, toks in reqs.items():
-        tr.portions(f"{name}:portions", toks)
+        if long:     # also portions of more than one query tile, and one that ends on a tile's edge
+            tr.portions(f"{name}:portions", toks, sizes=(7, 2, 16, 3, 5, 2, 130, 33, 2, 1, 17, 200, 39))
+        else:
+            tr.portions(f"{name}:portions", toks)
     mixed_schedule(tr, [(f"{name}:mixed", toks) for name, toks in reqs.items()], seed=seed)
     mixed_schedule(tr, [(f"{name}:mixed2", toks) for name, toks in reversed(list(reqs.items()))], seed=seed + 7,
-                   sizes=(2, 1, 1, 1, 16, 1, 1, 48, 1, 2, 1, 1, 1, 9))
+                   sizes=(2, 1, 1, 1, 16, 1, 1, 48, 1, 2, 1, 1, 1, 9) if not long else
+                   (2, 1, 130, 1, 16, 1, 1, 257, 1, 2, 65, 1, 1, 128, 9))
     return reqs, tr
 
 
@@ -60,7 +69,9 @@ def test_replay_matches_plain(case, dtype, tmp_path):
             worst, worst_key = err, (rid, pos)
     # every position of every request in every cutting was written
     assert n_rows == 5 * sum(lengths)  # whole, tail, portions, mixed, mixed2
-    print(f"{case} {dtype}: worst relative difference {worst:.3e} at {worst_key} over {n_rows} rows")
+    biggest = max(float(np.abs(r).max()) for r in ref.values())
+    print(f"{case} {dtype}: worst relative difference {worst:.3e} at {worst_key} over {n_rows} rows "
+          f"(largest |logit| {biggest:.2f})")
     assert worst <= TOL[dtype], f"worst at {worst_key}: {worst}"
     # the same position gives the same logits however it was cut (tighter than against the reference)
     cut_tol = TOL[dtype] * 0.5
