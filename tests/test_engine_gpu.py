@@ -17,12 +17,29 @@ from helpers import CONFIG_A, CONFIG_B, make_model_dir, random_tokens
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+# Largest |difference| allowed as a fraction of max(1, largest |reference logit|): about twice the worst measured
+# on a B200 with the tiny configurations (float32 5e-7, bfloat16 5.6e-3; run with -s to see them) ...
+TOL = {"float32": 5e-6, "bfloat16": 1.2e-2}
+# ... and at the widths of the larger models (float32 7.5e-6, bfloat16 1.3e-2: more terms per sum)
+TOL_WIDE = {"float32": 2e-5, "bfloat16": 2.5e-2}
+
+
+SEEN = []      # every relative difference a test computed; its largest is printed after the test (pytest -s)
 
 
 def rel(got, ref):
     ref = torch.as_tensor(ref).float().cpu()
-    return float((torch.as_tensor(got).float().cpu() - ref).abs().max()) / max(1.0, float(ref.abs().max()))
+    r = float((torch.as_tensor(got).float().cpu() - ref).abs().max()) / max(1.0, float(ref.abs().max()))
+    SEEN.append(r)
+    return r
+
+
+@pytest.fixture(autouse=True)
+def report_largest_difference(request):
+    SEEN.clear()
+    yield
+    if SEEN:
+        print(f"\n{request.node.name}: largest relative difference {max(SEEN):.3e}")
 
 
 def part_ctx(T=0, positions=None, token_req=None):
@@ -152,7 +169,7 @@ def test_layer_sizes_of_the_larger_models(dtype, width, heads, tmp_path):
     from mlx_lm_b200.weights import load_model
     config = dict(CONFIG_A, n_embd=width, n_head=heads, n_layer=1, n_inner=4 * width, vocab_size=777, n_positions=512,
                   ln_gain_std=0.2)
-    weights = make_model_dir(str(tmp_path), config, 31, peaky=4.0)
+    weights = make_model_dir(str(tmp_path), config, 31, peaky=2.0)
     model, _ = load_model(str(tmp_path), dtype=dtype)
     toks = random_tokens(300, 777, 5)
     ref = plain.logits(toks, weights, config)
@@ -160,15 +177,40 @@ def test_layer_sizes_of_the_larger_models(dtype, width, heads, tmp_path):
     eng.add_request("a")
     lg = eng.step([StepEntry("a", toks[:200], [0, 127, 128, 199])])
     for row, pos in enumerate([0, 127, 128, 199]):
-        assert rel(lg[row], ref[pos]) <= TOL[dtype], pos
+        assert rel(lg[row], ref[pos]) <= TOL_WIDE[dtype], pos
     lg = eng.step([StepEntry("a", toks[200:260], [59])])          # a portion of 60: few rows
-    assert rel(lg[0], ref[259]) <= TOL[dtype]
+    assert rel(lg[0], ref[259]) <= TOL_WIDE[dtype]
     worst = 0.0
     for t in range(260, 300):                                     # single tokens
         lg = eng.step([StepEntry("a", toks[t:t + 1], [0])])
         worst = max(worst, rel(lg[0], ref[t]))
-    assert worst <= TOL[dtype], worst
+    assert worst <= TOL_WIDE[dtype], worst
     eng.check_status()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_wrong_page_is_seen(dtype, tmp_path):
+    """The comparison with the plain implementation must fail when a request reads one wrong page: after a
+    prompt is in the cache, two page ids of the request are exchanged in the host block table (nothing else
+    changes) and the next tokens are decoded.  At configuration A, without sharpened attention, in both
+    precisions: the limits of these tests are tight enough to see it."""
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.weights import load_model
+    weights = make_model_dir(str(tmp_path), CONFIG_A, 0)
+    model, _ = load_model(str(tmp_path), dtype=dtype)
+    toks = random_tokens(80, 512, 7)
+    ref = plain.logits(toks, weights, CONFIG_A)
+    eng = Engine(model, page_size=16, n_pages=8, max_requests=1)
+    eng.add_request("r")
+    right = eng.step([StepEntry("r", toks[:64], [40, 63])])
+    assert rel(right, ref[[40, 63]]) <= TOL[dtype]
+    pages = eng.cache.requests["r"].pages[0]
+    pages[0], pages[1] = pages[1], pages[0]            # positions 0-15 now read the keys of 16-31 and back
+    worst = 0.0
+    for t in range(64, 80):
+        worst = max(worst, rel(eng.step([StepEntry("r", toks[t:t + 1], [0])])[0], ref[t]))
+    assert worst > 2 * TOL[dtype], f"a wrong page moved the logits by only {worst}"
+    eng.check_status()                                  # every id is a page of the pool: no kernel can tell
 
 
 def test_step_refuses_bad_input(tmp_path):

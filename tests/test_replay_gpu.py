@@ -15,17 +15,22 @@ from helpers import (CONFIG_A, CONFIG_B, CONFIG_C, Trace, make_model_dir, max_li
 
 pytestmark = pytest.mark.gpu
 
-# largest |difference| allowed, as a fraction of max(1, largest |reference logit|)
-TOL = {"float32": 2e-5, "bfloat16": 3e-2}
+# Largest |difference| allowed, as a fraction of max(1, largest |reference logit| of the row).  float32: the
+# worst case measured on a B200 is 1.3e-6.  bfloat16: per case, about twice the worst difference measured there
+# (A 3.6e-3, A-sharp 4.4e-3, B 5.6e-3, B-sharp 1.5e-2, C 5.7e-3, C-sharp 1.7e-2; the test prints them): sharp
+# attention turns the rounding of the scores into larger differences, so those cases have a limit of their own.
+# A request reading one wrong page moves the logits of A by 0.035 or more
+# (tests/test_engine_gpu.py::test_a_wrong_page_is_seen).
+TOL_F32 = 5e-6
 
-CASES = {
-    "A": (CONFIG_A, 0, 0.0, [23, 29, 100, 128, 65]),
-    "A-sharp": (CONFIG_A, 3, 12.0, [128, 61, 97]),
-    "B": (CONFIG_B, 1, 0.0, [29, 55, 88, 200, 256]),
-    "B-sharp": (CONFIG_B, 2, 12.0, [88, 256, 130]),
+CASES = {   # configuration, seed, sharpness of attention, request lengths, bfloat16 limit
+    "A": (CONFIG_A, 0, 0.0, [23, 29, 100, 128, 65], 7.5e-3),
+    "A-sharp": (CONFIG_A, 3, 12.0, [128, 61, 97], 9e-3),
+    "B": (CONFIG_B, 1, 0.0, [29, 55, 88, 200, 256], 1.2e-2),
+    "B-sharp": (CONFIG_B, 2, 12.0, [88, 256, 130], 3e-2),
     # heads of 64: lengths that cross the 128-key blocks and the 128-query tiles of the tcgen05 attention kernel
-    "C": (CONFIG_C, 4, 0.0, [130, 257, 300, 512]),
-    "C-sharp": (CONFIG_C, 5, 8.0, [512, 129, 384]),
+    "C": (CONFIG_C, 4, 0.0, [130, 257, 300, 512], 1.2e-2),
+    "C-sharp": (CONFIG_C, 5, 8.0, [512, 129, 384], 3e-2),
 }
 
 
@@ -52,7 +57,8 @@ def build_trace(lengths, vocab, seed):
 @pytest.mark.parametrize("case", list(CASES))
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_matches_plain(case, dtype, tmp_path):
-    config, seed, sharp, lengths = CASES[case]
+    config, seed, sharp, lengths, tol_bf16 = CASES[case]
+    limit = TOL_F32 if dtype == "float32" else tol_bf16
     weights = make_model_dir(str(tmp_path / "model"), config, seed, peaky=sharp)
     reqs, tr = build_trace(lengths, config["vocab_size"], seed)
     # the pool holds exactly what the busiest moment needs, so freed pages are taken again
@@ -72,9 +78,9 @@ def test_replay_matches_plain(case, dtype, tmp_path):
     biggest = max(float(np.abs(r).max()) for r in ref.values())
     print(f"{case} {dtype}: worst relative difference {worst:.3e} at {worst_key} over {n_rows} rows "
           f"(largest |logit| {biggest:.2f})")
-    assert worst <= TOL[dtype], f"worst at {worst_key}: {worst}"
+    assert worst <= limit, f"worst at {worst_key}: {worst}"
     # the same position gives the same logits however it was cut (tighter than against the reference)
-    cut_tol = TOL[dtype] * 0.5
+    cut_tol = limit * 0.5
     for name, toks in reqs.items():
         for pos in range(len(toks)):
             base = got[(f"{name}:whole", pos)]
