@@ -124,19 +124,21 @@ def test_decoding_as_cuda_graphs_at_the_benchmarked_layer_sizes(dtype, batch, me
     assert eng.host_status == 0
     eng.check_status()
     if batch == 8:
-        # one more step with two pages of request 0 exchanged in the host block table: its row must be off by
-        # more than the limit (so the limit sees a wrong page at these sizes), the other rows must not move
+        # one more step with the first entry of request 0's host block table pointed at its second page: its row
+        # must be off by more than the limit (so the limit sees a wrong page at these sizes), the other rows
+        # must not move
         pages = eng.cache.requests[0].pages[0]
-        pages[0], pages[1] = pages[1], pages[0]
+        first, pages[0] = pages[0], pages[1]
         seqs = [t + random_tokens(1, V, 7) for t in seqs]
         for i, r in enumerate(reqs):
             r.tokens.append(seqs[i][-1])
         eng.decode_sampled([StepEntry(r.uid, [r.tokens[-1]], [0]) for r in reqs], reqs, sampler)
         off = eng._graphs[batch].logits[:batch].float().cpu()
         ref_last = torch.stack([plain.hidden_states(t, w32, CFG)[-1] for t in seqs]) @ w32["wte.weight"].T
-        assert rel_rows(off[:1], ref_last[:1]) > 2 * TOL[dtype], "a wrong page is not seen"
+        assert rel_rows(off[:1], ref_last[:1]) > 1.5 * TOL[dtype], "a wrong page is not seen"
         assert rel_rows(off[1:], ref_last[1:]) <= TOL[dtype]
         seqs = [t[:-1] for t in seqs]
+        pages[0] = first
     hidden = [plain.hidden_states(t, w32, CFG)[n:n + n_steps] for n, t in zip(lens, seqs)]
     ref = torch.cat(hidden) @ w32["wte.weight"].T
     worst = rel_rows(torch.cat([torch.stack(g) for g in got]), ref)
