@@ -31,7 +31,17 @@ MLXB_DEFINE_LAST_ERROR()
 constexpr int BM = 128, BK = 64;
 constexpr int EPI_WARPS = 16;                     // four per quadrant of TMEM lanes, each a quarter of the columns
 constexpr int THREADS = 64 + 32 * EPI_WARPS;
+// Polls of a barrier before a wait gives up (about a second).  A test builds this file with
+// MLXB_TEST_WAIT_TIMEOUT defined: the limit is then short, and mlxb_test_withhold_arrival(1) makes the MMA thread
+// leave out the arrival that tells the epilogue warps that a CTA's first accumulator is complete, so that their
+// wait runs out and the abort path below is taken: every role leaves its loop, the CTA waits (bounded) for
+// what it has in flight, reports MLXB_ST_WAIT_TIMEOUT, frees its tensor memory and returns.  Nothing else differs.
+#ifdef MLXB_TEST_WAIT_TIMEOUT
+constexpr uint32_t SPIN_LIMIT = 1u << 12;
+__device__ int g_test_withhold_arrival = 0;
+#else
 constexpr uint32_t SPIN_LIMIT = 1u << 22;
+#endif
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -118,6 +128,7 @@ struct Smem {
   uint64_t empty[STAGES];
   uint64_t acc_full[2];
   uint64_t acc_empty[2];
+  uint64_t drained;       // abort path only: every tensor-core operation issued so far has completed
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -264,6 +275,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&sm.full[s], 1); mbar_init(&sm.empty[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&sm.acc_full[b], 1); mbar_init(&sm.acc_empty[b], 32 * EPI_WARPS); }
+    mbar_init(&sm.drained, 1);
     sm.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("prefetch.tensormap [%0];" ::"l"(&map_a) : "memory");
@@ -350,6 +362,9 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             umma_bf16(tmem_acc, da + 2 * k, db + 2 * k, idesc, (kt > 0 || k > 0) ? 1u : 0u);
           umma_commit(&sm.empty[s]);   // the stage is free once these MMAs have read it
         }
+#ifdef MLXB_TEST_WAIT_TIMEOUT
+        if (g_test_withhold_arrival && it == 0) continue;   // the test's missing arrival
+#endif
         if (ok) umma_commit(&sm.acc_full[b]);   // arrives when every MMA of this tile has completed
       }
     }
@@ -449,12 +464,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
   __syncthreads();
   if (threadIdx.x == 0 && sm.abort_flag) atomicOr(status, MLXB_ST_WAIT_TIMEOUT);
   if (warp == 1) {
+    if (lane == 0 && sm.abort_flag) {
+      // Somebody gave up.  Products this thread issued may still be running on the tensor memory that is freed
+      // below: one more commit arrives when all of them have completed; wait for it, bounded.
+      umma_commit(&sm.drained);
+      const uint32_t addr = smem_u32(&sm.drained);
+      for (uint32_t p = 0; p < (1u << 20); ++p) {
+        uint32_t done;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}" : "=r"(done) : "r"(addr), "r"(0u) : "memory");
+        if (done) break;
+      }
+    }
+    __syncwarp();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
   }
 }
 
 // ---------------------------------------------------------------------------------------------- host side
+
+#ifdef MLXB_TEST_WAIT_TIMEOUT
+// Test builds only: switch the withheld arrival on or off for the launches that follow on this device.
+MLXB_EXPORT int mlxb_test_withhold_arrival(int on) {
+  const cudaError_t e = cudaMemcpyToSymbol(g_test_withhold_arrival, &on, sizeof(int));
+  if (e != cudaSuccess) return mlxb_fail((int)e, "withhold_arrival: %s", cudaGetErrorString(e));
+  return 0;
+}
+#endif
 
 static int make_map(CUtensorMap* map, const void* base, int rows, int cols, int ld, int box_rows) {
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};

@@ -216,6 +216,25 @@ def test_a_wrong_page_is_seen(dtype, tmp_path):
     pages[0] = first
 
 
+def test_status_bits_become_errors_and_are_cleared(tmp_path):
+    """What a kernel reports in the status word (here written by the test: a bounded wait that gave up, a page
+    id outside the pool) is raised by ``check_status`` in words and cleared, and the engine goes on."""
+    from mlx_lm_b200 import ops
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.weights import load_model
+    make_model_dir(str(tmp_path), CONFIG_A, 0)
+    model, _ = load_model(str(tmp_path), dtype="bfloat16")
+    eng = Engine(model, page_size=16, n_pages=4, max_requests=1)
+    eng.status.fill_(ops.ST_WAIT_TIMEOUT | ops.ST_PAGE_RANGE)
+    with pytest.raises(ops.KernelError) as err:
+        eng.check_status()
+    assert "bounded wait" in str(err.value) and "page id outside the pool" in str(err.value)
+    assert eng.read_status() == 0 and eng.host_status == 0
+    eng.add_request(0)
+    assert eng.step([StepEntry(0, [1, 2, 3], [2])]).shape == (1, 512)
+    eng.check_status()
+
+
 def test_step_refuses_bad_input(tmp_path):
     from mlx_lm_b200.cache import OutOfPages
     from mlx_lm_b200.engine import Engine, StepEntry

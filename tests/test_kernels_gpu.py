@@ -587,3 +587,42 @@ def test_attention_window_edge(ops, dtype):
                              dev["v_pool"], out, Hq, Dh ** -0.5, W, scratch, counters, 256, status, stream())
         close = float((out[0].float().cpu() - want).abs().max()) <= 3e-2
         assert close == expect_hit
+
+
+def test_a_bounded_wait_that_runs_out(ops):
+    """Failure detection without a fault: the tcgen05 linear kernel is built once more with a short limit on
+    its barrier waits and a switch that leaves out one arrival (the MMA thread never tells the epilogue warps
+    that the first accumulator is complete).  Their wait then runs out: the kernel must come back by itself with
+    MLXB_ST_WAIT_TIMEOUT in the status word (no trap, no hang, its tensor memory freed), and the next launch of
+    the same library, with the switch off, must be right.  The engine turns that status bit into a KernelError."""
+    from ctypes import c_int
+    from mlx_lm_b200.ops import build
+    name = "gemm_tcgen05:MLXB_TEST_WAIT_TIMEOUT=1"
+    lib = build.load(name)
+    lib.mlxb_test_withhold_arrival.argtypes, lib.mlxb_test_withhold_arrival.restype = [c_int], c_int
+    g = torch.Generator().manual_seed(3)
+    M, N, K = 256, 128, 128
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()
+    out = torch.zeros(M, N, dtype=torch.bfloat16, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+
+    def launch():
+        ops._call(name, "mlxb_linear_tcgen05", ops._TC_ARGS, 0, x.data_ptr(), w.data_ptr(), None, None, out.data_ptr(),
+                  M, N, K, K, N, ops.EPI_NONE, status.data_ptr(), stream())
+        torch.cuda.synchronize()
+
+    assert lib.mlxb_test_withhold_arrival(1) == 0
+    try:
+        launch()
+        assert int(status.item()) == ops.ST_WAIT_TIMEOUT
+        assert float(out.float().abs().max()) == 0.0          # the epilogue never ran
+    finally:
+        assert lib.mlxb_test_withhold_arrival(0) == 0
+    status.zero_()
+    launch()
+    assert int(status.item()) == 0
+    assert rel_err(out, R.linear(x.cpu(), w.cpu())) <= 6e-3
+    # and the ordinary library is untouched by all this
+    ops.linear_tensor_cores(x, w, None, out, status, stream())
+    assert int(status.item()) == 0 and rel_err(out, R.linear(x.cpu(), w.cpu())) <= 6e-3
