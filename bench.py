@@ -8,13 +8,19 @@ A step is one decode step of the whole batch.  The default run has the layer siz
 bfloat16 weights, a batch of 8 requests with 512-token prompts and a context of 1024: after the
 prompts are in the cache, W untimed and K timed decode steps follow.  One JSON line is printed:
 
-  value      decoded tokens per second, timed on the device (CUDA events around the K steps)
+  value      decoded tokens per second, timed on the device (CUDA events around the K steps): the median of
+             five trials of K steps, each on fresh requests (`trials_ms` lists them)
   e2e        the same through the Python entry point (BatchGenerator): host token ids in, host
              token ids out, every step's inputs copied from pinned host memory and its tokens read back
+             (bytes counted at the copies); median of three trials
   prefill    one step of 2 x 1024 prompt tokens: tokens/s, ms, flops / time / measured bf16 peak
   roofline   decode step: bytes it has to read (every weight once + the live requests' cache) / time,
              against the measured copy bandwidth
-  points     decode tokens/s at batch 1 and 64
+  points     decode tokens/s at batch 1 and 64, the same from 1000-token prompts, and the mixed workload
+             (64 requests, prompts of 16..1024 tokens, 256-token portions beside decoding requests)
+  kernels    the kernels a decode step and a prefill step spend their time in, each kind timed alone (a CUDA
+             graph of that kernel for every layer, L2 flushed between replays): microseconds per launch, the
+             bytes or flops it has to move, and the fraction of the measured peak
 
 With --gpus N > 1 it prints one line and exits with 2: the engine runs on one GPU.
 """
@@ -229,20 +235,22 @@ def prefill_timeline(engine, n_prompts, vocab):
 
 
 def mixed_workload(model, engine, vocab, args, n_requests=64, new_tokens=128, seed=3):
-    """Continuous batching: 64 requests, prompt lengths uniform in [16, 1024 - new_tokens], portions of 256 tokens
-    beside decoding requests, everything through the scheduler; wall-clock tokens per second."""
+    """Continuous batching: 64 requests, prompt lengths uniform in [16, 1024], up to 128 new tokens each (fewer
+    where the 1024 positions end first), portions of 256 tokens beside decoding requests, everything through the
+    scheduler; wall-clock tokens per second."""
     import torch
 
     from mlx_lm_b200.generate import BatchGenerator
 
     g = torch.Generator().manual_seed(seed)
-    lens = torch.randint(16, 1024 - new_tokens, (n_requests,), generator=g).tolist()
+    lens = torch.randint(16, 1025, (n_requests,), generator=g).tolist()
     prompts = [torch.randint(0, vocab, (n,), generator=g).tolist() for n in lens]
+    new = [max(1, min(new_tokens, 1024 + 1 - n)) for n in lens]     # the last new token needs no position
 
     def run():
         gen = BatchGenerator(model, max_tokens=new_tokens, engine=engine, completion_batch_size=64,
-                             prefill_batch_size=8, prefill_step_size=256, max_tokens_per_step=2048)
-        gen.insert(prompts)
+                             prefill_batch_size=8, prefill_step_size=256, max_tokens_per_step=2048, seed=0)
+        gen.insert(prompts, new)
         torch.cuda.synchronize()
         t0 = time.perf_counter()
         n_out = 0
@@ -254,13 +262,128 @@ def mixed_workload(model, engine, vocab, args, n_requests=64, new_tokens=128, se
         return dt, n_out, st
 
     run()                                   # warm-up: graphs, launch plans, workspaces
+    before = engine.n_replayed
     dt, n_out, st = run()
     engine.check_status()
     return {"only": "mixed", "size": args.size, "requests": n_requests, "prompt_tokens": sum(lens),
             "generated_tokens": n_out, "seconds": round(dt, 4), "steps": st.steps,
             "prompt_tokens_per_s": round(sum(lens) / dt, 1), "generated_tokens_per_s": round(n_out / dt, 1),
             "tokens_per_s": round((sum(lens) + n_out) / dt, 1), "preemptions": st.preemptions,
-            "replayed_steps": engine.n_replayed}
+            "replayed_steps": engine.n_replayed - before}
+
+
+def reference_arm():
+    """The reference is mlx-lm, installed without its dependencies under baseline/_ref.  It runs on MLX, for
+    which this machine has no wheel: try the imports a run would need and report what this box answers."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "mlx_lm")):
+        return {"impl": "reference", "unavailable": f"mlx-lm is not installed under baseline/_ref ({ref} has no mlx_lm)"}
+    sys.path.insert(0, ref)
+    tried = []
+    for name in ("mlx.core", "mlx_lm"):
+        try:
+            __import__(name)
+            tried.append(f"import {name}: ok")
+        except BaseException as e:      # whatever this box raises is the answer
+            tried.append(f"import {name}: {type(e).__name__}: {e}")
+            return {"impl": "reference", "unavailable": "; ".join(tried) + " (mlx-lm runs on MLX, which has no "
+                    "wheel for this machine and cannot be fetched: no network)"}
+    return {"impl": "reference", "unavailable": "; ".join(tried) + "; mlx imports here, but the reference arm was never "
+            "built because it never did before"}
+
+
+def flush_l2(buf):
+    buf.zero_()
+
+
+def kernel_table(calls, pk, mode, attention_bytes=0.0, attention_flops=0.0, reps=5):
+    """Each kind of kernel of a recorded step, timed alone: the launches of a kind (one per layer) are captured
+    into a CUDA graph with their recorded arguments and replayed `reps` times with an L2 flush before each; the
+    result is microseconds per launch, what the launch has to move (from the labels the parts gave, attention
+    from the caller) and the fraction of the measured peak: HBM bytes for a decode step, bf16 flops for prefill."""
+    import collections
+    import re
+
+    import torch
+
+    groups = collections.OrderedDict()
+    for c in calls:
+        lab = c[4] or ("?", 0.0, 0.0)
+        kind = re.sub(r"\.\d+\.", ".", lab[0])
+        kind = re.sub(r"^h\.", "", kind)
+        groups.setdefault(kind, []).append(c)
+    side = torch.cuda.Stream()
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+
+    def time_graph(launches):
+        """Median microseconds of a graph of these launches, L2 flushed before every replay."""
+        graph = torch.cuda.CUDAGraph()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            for f, lib, fname, args, _ in launches:            # once eagerly
+                f(*args[:-1], side.cuda_stream)
+        side.synchronize()
+        with torch.cuda.graph(graph, stream=side):
+            handle = torch.cuda.current_stream().cuda_stream
+            for f, lib, fname, args, _ in launches:
+                f(*args[:-1], handle)
+        times = []
+        for _ in range(reps + 1):
+            flush_l2(flush)
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            graph.replay()
+            e.record()
+            torch.cuda.synchronize()
+            times.append(s.elapsed_time(e) * 1e3)
+        return sorted(times[1:])[len(times[1:]) // 2]
+
+    # A kind with a launch or two per step (embedding, final norm, output head, sampler) is timed behind the
+    # launches of the kind with the most launches, as the difference to those alone: a graph of one kernel would
+    # mostly measure the graph's own launch.
+    lead_kind = max(groups, key=lambda k: len(groups[k]))
+    lead = groups[lead_kind] if len(groups[lead_kind]) >= 8 else []
+    lead_us = time_graph(lead) if lead else 0.0
+    out = collections.OrderedDict()
+    for kind, group in groups.items():
+        if len(group) >= 8 or not lead:
+            us = (lead_us if kind == lead_kind else time_graph(group)) / len(group)
+        else:
+            us = max(time_graph(lead + group) - lead_us, 0.0) / len(group)
+        flops = sum(c[4][1] for c in group if c[4]) / len(group)
+        nbytes = sum(c[4][2] for c in group if c[4]) / len(group)
+        if kind.endswith("attention"):
+            flops, nbytes = attention_flops, attention_bytes
+        rec = {"n": len(group), "us": round(us, 2)}
+        if nbytes:
+            rec["gbs"] = round(nbytes / us / 1e3, 1)
+        if flops:
+            rec["tflops"] = round(flops / us / 1e6, 1)
+        if mode == "decode" and nbytes:
+            rec["frac"] = round(nbytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 3)
+        elif mode == "prefill" and flops:
+            rec["frac"] = round(flops / (us * 1e-6) / 1e12 / pk["bf16_tflops"], 3)
+        out[kind] = rec
+    return out
+
+
+def decode_kernels(engine, batch, mean_ctx, cfg, pk):
+    """The kernel table of the decode step at `batch` (the graph of that bucket must have run)."""
+    import torch
+
+    from mlx_lm_b200 import ops
+    graph = engine._graphs[batch]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        ops.start_recording()
+        try:
+            graph._launch()
+        finally:
+            calls = ops.stop_recording()
+    side.synchronize()
+    kv_bytes = batch * mean_ctx * 2 * cfg["n_embd"] * 2
+    return kernel_table(calls, pk, "decode", attention_bytes=kv_bytes, attention_flops=2 * kv_bytes)
 
 
 def run_ours(args):
@@ -308,11 +431,110 @@ def run_ours(args):
                           "hbm_frac": round(step_bytes / (ms / 1e3) / 1e9 / pk["hbm_gbs"], 4),
                           "launches_per_step": launches}))
         return
+    if args.only == "kernels":
+        plen = args.prompt_len or PROMPT_LEN
+        ms, launches, mean_ctx = decode_loop(engine, DeviceSampler, model, B, plen, 8, 3, vocab)
+        table = decode_kernels(engine, B, mean_ctx, cfg, pk)
+        print(f"decode step, batch {B}, context {mean_ctx:.0f}: {ms * 1e3:.1f} us, {launches:.0f} launches; "
+              f"each kind alone:")
+        for kind, r in table.items():
+            print(f"  {kind:28s} x{r['n']:3d}  {r['us']:8.2f} us  {r.get('gbs', 0):8.1f} GB/s  "
+                  f"{r.get('tflops', 0):7.1f} TFLOP/s  {r.get('frac', 0):6.3f} of the HBM peak")
+        pf_ms, pf_table = prefill_step(engine, cfg, pk, vocab, args.prefill_prompts or 2, lin_flops, table=True)[1:]
+        print(f"prefill step, {args.prefill_prompts or 2} x 1024 tokens: {pf_ms * 1e3:.1f} us; each kind alone:")
+        for kind, r in pf_table.items():
+            print(f"  {kind:28s} x{r['n']:3d}  {r['us']:8.2f} us  {r.get('gbs', 0):8.1f} GB/s  "
+                  f"{r.get('tflops', 0):7.1f} TFLOP/s  {r.get('frac', 0):6.3f} of the bf16 peak")
+        return
 
     # ---- prefill: 2 x 1024 tokens in one step (more prompts only with --only prefill --prefill-prompts N)
     n_pf = (args.prefill_prompts or 2) if args.only == "prefill" else 2
     if not 1 <= n_pf <= max_b:
         raise SystemExit(f"--prefill-prompts {n_pf}: 1 to {max_b}")
+    prefill, pf_ms, pf_table = prefill_step(engine, cfg, pk, vocab, n_pf, lin_flops, table=not args.only)
+    if args.only == "prefill":
+        print(json.dumps({"only": "prefill", **prefill}))
+        return
+
+    # ---- decode, device-timed: five trials of K steps, each on fresh requests; the median counts
+    trials = []
+    with ClockSampler() as clocks:
+        for t in range(5):
+            ms, launches, mean_ctx = decode_loop(engine, DeviceSampler, model, B, PROMPT_LEN, K, W, vocab, seed=t)
+            trials.append(ms)
+    ms = sorted(trials)[len(trials) // 2]
+    value = B / (ms / 1e3)
+    step_bytes = weight_bytes + B * mean_ctx * kv_per_token
+    achieved = step_bytes / (ms / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": round(achieved / pk["hbm_gbs"], 4)}
+    kernels = {"decode": decode_kernels(engine, B, mean_ctx, cfg, pk), "prefill": pf_table}
+
+    points = {}
+    k_pts, w_pts = min(K, 64), max(3, min(W, 8))
+    for b in (1, 64):
+        pms = sorted(decode_loop(engine, DeviceSampler, model, b, PROMPT_LEN, k_pts, w_pts, vocab, seed=10 * b + t)[0]
+                     for t in range(3))[1]
+        points[f"decode_b{b}"] = round(b / (pms / 1e3), 1)
+    for b in (1, 8, 64):       # the same from 1000-token prompts: the cache a step reads is twice as long
+        pms = sorted(decode_loop(engine, DeviceSampler, model, b, 1000, 12, 8, vocab, seed=100 * b + t)[0]
+                     for t in range(3))[1]
+        points[f"decode_b{b}_prompt1000"] = round(b / (pms / 1e3), 1)
+    mixed = mixed_workload(model, engine, vocab, args)
+    points["mixed_64_requests_tokens_per_s"] = mixed["tokens_per_s"]
+    points["mixed_generated_tokens_per_s"] = mixed["generated_tokens_per_s"]
+    points["mixed_steps"] = mixed["steps"]
+    points["mixed_replayed_steps"] = mixed["replayed_steps"]
+
+    # ---- end to end through the Python entry point: host tokens in, host tokens out
+    e2e_trials = []
+    for t in range(3):
+        g = torch.Generator().manual_seed(2 + t)
+        host_prompts = [torch.randint(0, vocab, (PROMPT_LEN,), generator=g).tolist() for _ in range(B)]
+        gen = BatchGenerator(model, max_tokens=W + K + 1, engine=engine, completion_batch_size=max(B, 8),
+                             prefill_batch_size=max(B, 8), prefill_step_size=2048, max_tokens_per_step=4096, seed=0)
+        gen.insert(host_prompts)
+        n_out = 0
+        while n_out < B * (1 + W):            # prompts and warm-up steps
+            n_out += len(gen.next_generated())
+        torch.cuda.synchronize()
+        h2d0, d2h0 = engine.h2d_bytes, engine.d2h_bytes
+        t0 = time.perf_counter()
+        n_timed = 0
+        for _ in range(K):
+            n_timed += len(gen.next_generated())
+        torch.cuda.synchronize()
+        e2e_trials.append((n_timed / (time.perf_counter() - t0), (engine.h2d_bytes - h2d0) // K,
+                           (engine.d2h_bytes - d2h0) // K))
+        gen.close()
+    e2e_trials.sort()
+    e2e = {"value": round(e2e_trials[1][0], 1), "unit": "tokens/s", "h2d_bytes_per_step": int(e2e_trials[1][1]),
+           "d2h_bytes_per_step": int(e2e_trials[1][2])}
+
+    out = {
+        "metric": f"decode tokens/s, GPT-2 {args.size}, batch {B}, 512-token prompts, context 1024",
+        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random prompt tokens",
+        "config": {"model": f"gpt2-{args.size}", "n_layer": cfg["n_layer"], "n_layer_of_configuration": n_layer_full,
+                   "n_embd": cfg["n_embd"], "n_head": cfg["n_head"], "n_inner": cfg["n_inner"],
+                   "vocab_size": vocab, "n_positions": cfg["n_positions"], "global_batch": B,
+                   "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": 16, "parallelism": "single_gpu",
+                   "l2": "inputs larger than L2 (weights %.0f MB)" % (weight_bytes / 1e6),
+                   "peaks": pk["source"], "prefill_peak": "bf16_tflops (burst)", "trials": len(trials)},
+        "trials_ms": [round(t, 4) for t in trials],
+        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(round(launches * K)),
+        "prefill": prefill, "roofline": roofline, "points": points, "kernels": kernels, "impl": "ours",
+    }
+    print(json.dumps(out))
+
+
+def prefill_step(engine, cfg, pk, vocab, n_pf, lin_flops, table=False):
+    """One step of `n_pf` whole prompts of 1024 tokens, timed four times (the best of the last three counts)."""
+    import torch
+
+    from mlx_lm_b200.engine import StepEntry
+
     g = torch.Generator().manual_seed(1)
     prompts = [torch.randint(0, vocab, (1024,), generator=g).tolist() for _ in range(n_pf)]
     times = []
@@ -330,66 +552,15 @@ def run_ours(args):
             engine.finish(("pf", i))
     pf_ms = min(times[1:])
     D, L = cfg["n_embd"], cfg["n_layer"]
-    attn_flops = n_pf * L * 4 * D * (1024 * 1025 // 2)       # QK^T and PV over the causal half of every prompt
-    pf_flops = n_pf * 1024 * lin_flops + attn_flops + n_pf * 2 * D * vocab
+    attn_layer = n_pf * 4 * D * (1024 * 1025 // 2)        # QK^T and PV over the causal half of every prompt
+    pf_flops = n_pf * 1024 * lin_flops + L * attn_layer + n_pf * 2 * D * vocab
     prefill = {"value": round(n_pf * 1024 / (pf_ms / 1e3), 1), "tokens": n_pf * 1024, "ms": round(pf_ms, 4),
                "frac": round(pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), 4)}
-    if args.only == "prefill":
-        print(json.dumps({"only": "prefill", **prefill}))
-        return
-
-    # ---- decode, device-timed
-    with ClockSampler() as clocks:
-        ms, launches, mean_ctx = decode_loop(engine, DeviceSampler, model, B, PROMPT_LEN, K, W, vocab)
-    value = B / (ms / 1e3)
-    step_bytes = weight_bytes + B * mean_ctx * kv_per_token
-    achieved = step_bytes / (ms / 1e3) / 1e9
-    roofline = {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": round(achieved / pk["hbm_gbs"], 4)}
-
-    points = {}
-    for b in (1, 64):
-        pms, _, _ = decode_loop(engine, DeviceSampler, model, b, PROMPT_LEN, min(K, 64), max(3, min(W, 8)), vocab,
-                                seed=b)
-        points[f"decode_b{b}"] = round(b / (pms / 1e3), 1)
-
-    # ---- end to end through the Python entry point: host tokens in, host tokens out
-    g = torch.Generator().manual_seed(2)
-    host_prompts = [torch.randint(0, vocab, (PROMPT_LEN,), generator=g).tolist() for _ in range(B)]
-    gen = BatchGenerator(model, max_tokens=W + K + 1, engine=engine, completion_batch_size=max(B, 8),
-                         prefill_batch_size=max(B, 8), prefill_step_size=2048, max_tokens_per_step=4096)
-    gen.insert(host_prompts)
-    n_out = 0
-    while n_out < B * (1 + W):            # prompts and warm-up steps
-        n_out += len(gen.next_generated())
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    n_timed = 0
-    for _ in range(K):
-        n_timed += len(gen.next_generated())
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    gen.close()
-    W_tab = engine.cache.table_width
-    h2d = 4 * (3 * B + B + B + (B + 1) + B + B * W_tab + 3 * 4) + 64 * B     # step integers + sampler records
-    e2e = {"value": round(n_timed / e2e_s, 1), "unit": "tokens/s", "h2d_bytes_per_step": int(h2d),
-           "d2h_bytes_per_step": int(4 * (64 + B))}
-
-    out = {
-        "metric": f"decode tokens/s, GPT-2 {args.size}, batch {B}, 512-token prompts, context 1024",
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
-        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random prompt tokens",
-        "config": {"model": f"gpt2-{args.size}", "n_layer": cfg["n_layer"], "n_layer_of_configuration": n_layer_full,
-                   "n_embd": cfg["n_embd"], "n_head": cfg["n_head"], "n_inner": cfg["n_inner"],
-                   "vocab_size": vocab, "n_positions": cfg["n_positions"], "global_batch": B,
-                   "seq_len": CONTEXT, "prompt_len": PROMPT_LEN, "page_size": 16, "parallelism": "single_gpu",
-                   "l2": "inputs larger than L2 (weights %.0f MB)" % (weight_bytes / 1e6),
-                   "peaks": pk["source"], "prefill_peak": "bf16_tflops (burst)"},
-        "clocks": clocks.summary(), "e2e": e2e, "gpu_launches": int(round(launches * K)),
-        "prefill": prefill, "roofline": roofline, "points": points, "impl": "ours",
-    }
-    print(json.dumps(out))
+    tab = None
+    if table and engine.last_calls:
+        tab = kernel_table(engine.last_calls, pk, "prefill", attention_flops=attn_layer,
+                           attention_bytes=n_pf * 1024 * 4 * D * 2)
+    return prefill, pf_ms, tab
 
 
 def main():
@@ -400,11 +571,12 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 24 (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "timeline"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "timeline", "kernels"],
                     help="run just this part and print its figures (decode / prefill: short runs for profiling; "
                          "mixed: 64 requests with prompts of 16..1024 tokens through the scheduler, 256-token portions "
                          "beside decoding requests; timeline: every kernel of one step with its start and end, "
-                         "from torch.profiler)")
+                         "from torch.profiler; kernels: each kind of kernel of a decode and a prefill step timed "
+                         "alone, with bytes, flops and the fraction of the measured peak)")
     ap.add_argument("--prefill-prompts", type=int, default=0,
                     help="with --only prefill: 1024-token prompts in the one step (default and the contract's figure: "
                          "2); with --only timeline: the timeline of such a step instead of a decode step")
@@ -413,9 +585,7 @@ def main():
     ap.add_argument("--size", default="medium", choices=sorted(SIZES), help="layer sizes: GPT-2 medium, large or XL")
     a = ap.parse_args()
     if a.impl == "reference":
-        print(json.dumps({"impl": "reference", "unavailable":
-                          "mlx-lm 0.32.0 installs offline only with --no-deps and fails at 'import mlx.core': "
-                          "no MLX wheel exists for this machine and there is no network"}))
+        print(json.dumps(reference_arm()))
         return 0
     if a.gpus != 1 or int(os.environ.get("WORLD_SIZE", "1")) != 1:
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not offered")

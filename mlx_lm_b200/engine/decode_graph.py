@@ -90,6 +90,7 @@ class DecodeGraph:
         ctx.stream = ops.current_stream()
         before = ops.launch_count
         self.logits = self.engine.model.run(ctx)
+        ops.label("sampler", 0.0, 4.0 * self.logits.numel())
         ops.sample(self.logits, self.params, self.tok, self.lp, ctx.stream, status=self.engine.status,
                    status_out=self.out[2 * self.B:])
         self._count = ops.launch_count - before
@@ -122,6 +123,8 @@ class DecodeGraph:
             self.graph.replay()
             ops.launch_count += self.n_kernels
             self.out_host.copy_(self.out, non_blocking=True)
+            eng.h2d_bytes += 4 * self.total
+            eng.d2h_bytes += 4 * self.out.numel()
             torch.cuda.current_stream().synchronize()
         except BaseException:
             for e in entries:          # the step did not run to its end: undo the reservations

@@ -164,6 +164,8 @@ class Engine:
                                   max_len=self.max_len, dtype=model.dtype, device=model.device)
         self.ws = Workspace(model.device)
         self.status = torch.zeros(1, dtype=torch.int32, device=model.device)
+        self.h2d_bytes = self.d2h_bytes = 0     # bytes the steps copied to and from the device (counted at the copies)
+        self.last_calls = None    # the recorded launches of the last step that went through a launch plan
         self.host_status = 0      # the status word as a sampler's copy of a step's tokens last brought it to the host
         self._namespaces = 0
         self._host = [None, None]
@@ -212,6 +214,7 @@ class Engine:
 
     def _upload(self, i: int, n: int) -> None:
         self._dev[:n].copy_(self._host[i][:n], non_blocking=True)
+        self.h2d_bytes += 4 * n
         ev = torch.cuda.Event()
         ev.record()
         self._host_events[i] = ev   # the pinned buffer may be rewritten once this has passed
@@ -381,6 +384,7 @@ class Engine:
         if plan is not None and plan[0] == self.ws.generation:
             ops.replay(plan[1])
             self.n_replayed += 1
+            self.last_calls = plan[1]
             return plan[2]
         ops.start_recording()
         try:
@@ -390,6 +394,7 @@ class Engine:
         if len(self._plans) >= 256:
             self._plans.clear()
         self._plans[shape] = (self.ws.generation, calls, logits)
+        self.last_calls = calls
         return logits
 
     # ------------------------------------------------------------------ decode steps as CUDA graphs

@@ -119,14 +119,25 @@ def _fn(libname: str, fname: str, argtypes):
 
 
 launch_count = 0   # kernel launches issued through this module (bench.py reads and resets it)
-_recording = None  # while a list: every launch is appended as (launcher, library, name, arguments)
+_recording = None  # while a list: every launch is appended as (launcher, library, name, arguments, label)
+_label = None      # what the launches that follow are part of: (name, flops, bytes), set by the parts
+
+
+def label(name: str, flops: float = 0.0, nbytes: float = 0.0) -> None:
+    """Name the work the following launches belong to (a part's tensor name, say) with the floating-point
+    operations and the bytes it has to move, where the caller knows them.  Recorded launches carry the label;
+    the measuring tools group and rate kernels by it.  Costs nothing when nothing is recorded."""
+    global _label
+    if _recording is not None:
+        _label = (name, float(flops), float(nbytes))
 
 
 def start_recording() -> None:
     """Begin to note every launch with its raw arguments, so that a step of the same shape can be
     re-issued later without going through the checks and the parts again (``replay``)."""
-    global _recording
+    global _recording, _label
     _recording = []
+    _label = None
 
 
 def stop_recording():
@@ -138,7 +149,7 @@ def stop_recording():
 def replay(calls) -> None:
     """Re-issue recorded launches.  The caller guarantees that every buffer they name is still where it was."""
     global launch_count
-    for f, lib, fname, args in calls:
+    for f, lib, fname, args, _ in calls:
         rc = f(*args)
         if rc != 0:
             msg = lib.mlxb_last_error()
@@ -155,7 +166,7 @@ def _call(libname: str, fname: str, argtypes, *args) -> None:
         msg = lib.mlxb_last_error()
         raise KernelError(f"{fname} failed ({rc}): {msg.decode() if msg else ''}")
     if _recording is not None:
-        _recording.append((f, lib, fname, args))
+        _recording.append((f, lib, fname, args, _label))
 
 
 # --------------------------------------------------------------------------

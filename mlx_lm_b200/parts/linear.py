@@ -101,6 +101,7 @@ class Linear(Part):
         if self.few_rows(x.shape[0]) if few is None else few:
             return (f.colsum, f.eps)
         stats = ctx.ws.get("row_stats", x.shape[0], 2, torch.float32)
+        ops.label(f.norm.name + ".statistics", 3.0 * src.shape[0] * src.shape[1], 2.0 * src.shape[0] * src.shape[1])
         ops.row_stats(src, stats, f.eps, ctx.stream)
         return (f.colsum, stats)
 
@@ -109,6 +110,7 @@ class Linear(Part):
         to 64 rows, the tcgen05 kernel for more; an inner size that is no multiple of 8 (no 16-byte rows)
         goes to the generic kernel."""
         epi = ACTIVATIONS[activation]
+        M = x.shape[0]
         few = self.few_rows(x.shape[0])      # decided once, before the fold's argument is made for that kernel
         fold = None
         if isinstance(x, Normed):
@@ -119,6 +121,8 @@ class Linear(Part):
                                   f"Normed, not a tensor")
         fast = (x.dtype == torch.bfloat16 and self.n_in % 8 == 0 and x.stride(0) % 8 == 0
                 and x.data_ptr() % 16 == 0)
+        ops.label(self.name, 2.0 * M * self.n_in * self.n_out,
+                  self.weight.element_size() * (self.n_in * self.n_out + M * self.n_in) + out.element_size() * M * self.n_out)
         if fast and few:
             ops.linear_few_rows(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual, fold=fold)
         elif fast:

@@ -62,6 +62,9 @@ class Attention(Mixer):
             # nothing to do to q and k before the cache: the projection's epilogue puts keys and values
             # into the pages itself
             fold = self.qkv.fold_of(ctx, x, few=T <= ops.SMALL_M) if isinstance(x, Normed) else None
+            n_qkv = self.q_width + 2 * self.kv_width
+            ops.label(self.qkv.name, 2.0 * T * self.width * n_qkv,
+                      x.dtype.itemsize * (self.width * n_qkv + T * self.width + T * n_qkv))
             ops.linear_qkv_to_cache(src, self.qkv.weight, self.qkv.bias, qkv, ctx.positions, ctx.token_req,
                                     cache.block_table, cache.k, cache.v, self.q_width, ctx.status, ctx.stream,
                                     fold=fold)
@@ -75,6 +78,7 @@ class Attention(Mixer):
                 ops.kv_write(k, v, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, ctx.status,
                              ctx.stream)
         o = ctx.ws.get("attn_out", T, self.q_width, x.dtype)
+        ops.label(self.name + ".attention")      # its cost depends on the requests' lengths: the caller knows them
         self.attend(ctx, q, cache, o)
         return self.out.forward(ctx, o, residual, residual=residual)
 

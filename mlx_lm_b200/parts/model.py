@@ -50,6 +50,7 @@ class TokenEmbedding(Part):
     def forward(self, ctx, position: Optional[PositionEncoding]):
         x = ctx.ws.get("residual", ctx.n_tokens, self.width, self.table.dtype)
         table = position.embedding_table() if position is not None else None
+        ops.label(self.name, ctx.n_tokens * self.width, (3 if table is not None else 2) * x.element_size() * ctx.n_tokens * self.width)
         ops.embed_pos(ctx.tokens, ctx.positions, self.table, table, x, ctx.status, ctx.stream, scale=self.scale)
         return x
 
@@ -76,7 +77,9 @@ class OutputHead(Part):
 
     def forward(self, ctx, x):
         out = ctx.ws.get("logits", x.shape[0], self.vocab_size, torch.float32)
-        return self.linear.forward(ctx, x, out)
+        out = self.linear.forward(ctx, x, out)
+        ops.label("after the output head")
+        return out
 
 
 @dataclass

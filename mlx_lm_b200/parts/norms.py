@@ -36,6 +36,7 @@ class LayerNorm(Norm):
     def forward(self, ctx, x, rows=None, tag: str = "normed"):
         n = x.shape[0] if rows is None else rows.numel()
         out = ctx.ws.get(tag, n, self.width, x.dtype)
+        ops.label(self.name, 8.0 * n * self.width, 2.0 * x.element_size() * n * self.width)
         ops.layernorm(x, self.gain, self.bias, out, self.eps, ctx.stream, rows=rows)
         return out
 

@@ -70,6 +70,8 @@ class DeviceSampler:
         h = self._out_host.numpy()
         if self.engine is not None:
             self.engine.host_status = int(h[2 * cap])
+            self.engine.h2d_bytes += 4 * (R * ops.SAMPLE_WORDS + len(special))
+            self.engine.d2h_bytes += 4 * self._out.numel()
         return h[:R].tolist(), h[cap:cap + R].view(np.float32).tolist()
 
     def _process(self, logits, requests, stream) -> None:

@@ -18,8 +18,15 @@ from typing import Iterable, List, Optional, Sequence, Set
 
 class StreamingDetokenizer:
     """Text grows as tokens are added; ``last_segment`` is what the last ``add_token`` or
-    ``finalize`` made ready.  A trailing replacement character is held back until later bytes
-    complete it (what mlx_lm/tokenizer_utils.py:61-106 does for its naive detokenizer)."""
+    ``finalize`` made ready.
+
+    Incremental: a token costs one decode of the few tokens that are not flushed yet, not of the whole
+    sequence (mlx-lm streams byte-level BPE the same way, by hand over the vocabulary's byte table:
+    mlx_lm/tokenizer_utils.py:157-250).  The tokens since the last flush are decoded together with the one
+    token before them, and the text of that one token alone is cut off the front: a tokenizer that treats the
+    start of a sequence specially (a dropped leading blank) then sees the same left context as in a decode of
+    the whole sequence.  A tail that ends in the replacement character is an unfinished multi-byte character:
+    it is held back until later tokens complete it (mlx_lm/tokenizer_utils.py:61-106 holds it back likewise)."""
 
     def __init__(self, decode):
         self._decode = decode
@@ -28,18 +35,32 @@ class StreamingDetokenizer:
     def reset(self) -> None:
         self.tokens: List[int] = []
         self.text = ""
-        self._emitted = 0
-        self._offset = 0
+        self._offset = 0          # characters of ``text`` handed out by last_segment
+        self._flushed = 0         # tokens whose text is in ``text``
+
+    def _pending_text(self) -> str:
+        left = self.tokens[self._flushed - 1:self._flushed] if self._flushed else []
+        text = self._decode(left + self.tokens[self._flushed:])
+        if not left:
+            return text
+        head = self._decode(left)
+        if text.startswith(head):
+            return text[len(head):]
+        # the left token's text changes with what follows it: fall back to the whole sequence
+        return self._decode(self.tokens)[len(self.text):]
 
     def add_token(self, token: int) -> None:
         self.tokens.append(int(token))
-        text = self._decode(self.tokens)
-        if text.endswith("�"):
+        new = self._pending_text()
+        if new.endswith("\ufffd"):
             return
-        self.text = text
+        self.text += new
+        self._flushed = len(self.tokens)
 
     def finalize(self) -> None:
-        self.text = self._decode(self.tokens)
+        if self._flushed < len(self.tokens):
+            self.text += self._pending_text()
+            self._flushed = len(self.tokens)
 
     @property
     def last_segment(self) -> str:

@@ -57,12 +57,25 @@ def build_trace(lengths, vocab, seed):
 @pytest.mark.parametrize("case", list(CASES))
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_matches_plain(case, dtype, tmp_path):
+    replay_and_compare(case, dtype, tmp_path, page_size=16)
+
+
+@pytest.mark.parametrize("case,page_size", [("C-sharp", 8), ("A-sharp", 32), ("C", 32), ("B", 64)])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_with_other_page_sizes(case, page_size, dtype, tmp_path):
+    """The same cuttings with pages of 8, 32 and 64 tokens: page edges fall elsewhere in every kernel that
+    walks a block table (the cache write in the projections' epilogues, the three attention kernels)."""
+    replay_and_compare(case, dtype, tmp_path, page_size=page_size)
+
+
+def replay_and_compare(case, dtype, tmp_path, page_size):
     config, seed, sharp, lengths, tol_bf16 = CASES[case]
     limit = TOL_F32 if dtype == "float32" else tol_bf16
     weights = make_model_dir(str(tmp_path / "model"), config, seed, peaky=sharp)
     reqs, tr = build_trace(lengths, config["vocab_size"], seed)
     # the pool holds exactly what the busiest moment needs, so freed pages are taken again
-    got = run_trace(str(tmp_path / "model"), tr, dtype, str(tmp_path / "out"), max_tokens=max_live_tokens(tr))
+    got = run_trace(str(tmp_path / "model"), tr, dtype, str(tmp_path / "out"), max_tokens=max_live_tokens(tr),
+                    extra=["--page-size", str(page_size)])
     ref = {name: plain.logits(toks, weights, config).numpy() for name, toks in reqs.items()}
     worst, worst_key = 0.0, None
     n_rows = 0
@@ -76,7 +89,7 @@ def test_replay_matches_plain(case, dtype, tmp_path):
     # every position of every request in every cutting was written
     assert n_rows == 5 * sum(lengths)  # whole, tail, portions, mixed, mixed2
     biggest = max(float(np.abs(r).max()) for r in ref.values())
-    print(f"{case} {dtype}: worst relative difference {worst:.3e} at {worst_key} over {n_rows} rows "
+    print(f"{case} {dtype} pages of {page_size}: worst relative difference {worst:.3e} at {worst_key} over {n_rows} rows "
           f"(largest |logit| {biggest:.2f})")
     assert worst <= limit, f"worst at {worst_key}: {worst}"
     # the same position gives the same logits however it was cut (tighter than against the reference)

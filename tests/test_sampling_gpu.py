@@ -160,7 +160,8 @@ def test_device_sampler_rows_keep_their_own_options():
     probs = np.array([0.4, 0.3, 0.15, 0.15])
     plain_xtc = make_sampler(1.0, xtc_probability=1.0, xtc_threshold=0.2)
     keeps_0 = make_sampler(1.0, xtc_probability=1.0, xtc_threshold=0.2, xtc_special_tokens=(0,))
-    engine = SimpleNamespace(status=torch.zeros(1, dtype=torch.int32, device="cuda"), host_status=-1)
+    engine = SimpleNamespace(status=torch.zeros(1, dtype=torch.int32, device="cuda"), host_status=-1, h2d_bytes=0,
+                             d2h_bytes=0)
     ds = DeviceSampler("cuda", seed=4, engine=engine)
     seen = [set(), set(), set()]
     for p in range(60):

@@ -90,3 +90,41 @@ def test_streaming_detokenizer_holds_back_half_a_character(tmp_path):
     assert d.text == "" and d.tokens == [] and d.last_segment == ""
     # a detokenizer is a fresh object per request
     assert t.detokenizer is not t.detokenizer and isinstance(t.detokenizer, StreamingDetokenizer)
+
+
+def test_streaming_detokenizer_decodes_only_what_is_new(tmp_path):
+    """A token costs a decode of the few tokens not flushed yet (and one before them), not of the whole sequence
+    (mlx-lm streams byte-level BPE token by token as well, mlx_lm/tokenizer_utils.py:157-250)."""
+    byte_level_folder(str(tmp_path), eos_in_tokenizer_config=False)
+    t = load_tokenizer(str(tmp_path), {"vocab_size": 300})
+    text = "streaming ✓ text, a few hundred bytes of it: " * 8
+    ids = t.encode(text, add_special_tokens=False)
+    seen = []
+
+    def counting(tokens):
+        seen.append(len(tokens))
+        return t.decode(tokens)
+
+    d = StreamingDetokenizer(counting)
+    out = ""
+    for tok in ids:
+        d.add_token(tok)
+        out += d.last_segment
+    d.finalize()
+    out += d.last_segment
+    assert out == text and len(ids) > 300
+    assert max(seen) <= 4 and sum(seen) <= 4 * len(ids)      # "✓" is three tokens: at most they and one before
+
+
+def test_streaming_detokenizer_keeps_a_blank_that_a_sequence_start_would_drop():
+    """A decoder that drops a blank at the start of a sequence (as sentence-piece style decoders do): the pieces
+    still add up to the decode of the whole."""
+    words = {0: " a", 1: " b", 2: "c", 3: " d"}
+    decode = lambda toks: "".join(words[t] for t in toks).lstrip(" ")
+    d = StreamingDetokenizer(decode)
+    pieces = []
+    for tok in (0, 1, 2, 3, 1):
+        d.add_token(tok)
+        pieces.append(d.last_segment)
+    d.finalize()
+    assert "".join(pieces) + d.last_segment == decode([0, 1, 2, 3, 1]) == "a bc d b"
