@@ -3,14 +3,18 @@
 #include "gemm_smallm.cuh"
 #include "gemm_stream.cuh"
 
-// MLXB_SMALLM=registers selects the older kernel that stages weights in registers (gemm_smallm.cuh), for comparison.
-static bool use_stream() {
-  static int on = -1;
-  if (on < 0) {
+// Which of the two few-rows kernels runs: the one that streams weights through shared memory (gemm_stream.cuh)
+// where it is the faster one, else the one that stages them in registers (gemm_smallm.cuh).
+// MLXB_SMALLM=registers / =stream forces one of them wherever it can run, for comparison.
+static bool use_stream(int M, int N) {
+  static int forced = -1;
+  if (forced < 0) {
     const char* e = getenv("MLXB_SMALLM");
-    on = (e && e[0] == 'r') ? 0 : 1;
+    forced = !e ? 0 : (e[0] == 'r' ? 1 : (e[0] == 's' ? 2 : 0));
   }
-  return on == 1;
+  if (forced == 1) return false;
+  if (forced == 2) return M <= 16;
+  return gs::preferred(M, N);
 }
 
 MLXB_DEFINE_LAST_ERROR()
@@ -24,7 +28,7 @@ MLXB_EXPORT int mlxb_linear_smallm(int out_f32, const void* A, const void* W, co
   if (M <= 0 || N <= 0) return 0;
   if (int e = check_args(M, N, K, lda, ldc, epi, A, W)) return e;
   const KvScatter none = {};
-  if (use_stream()) {
+  if (use_stream(M, N)) {
     if (out_f32) return gs::launch<float, false, false>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, gs::NormFold{}, status, stream);
     return gs::launch<__nv_bfloat16, false, false>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, gs::NormFold{}, status, stream);
   }
@@ -46,7 +50,7 @@ MLXB_EXPORT int mlxb_linear_smallm_qkv(const void* A, const void* W, const float
     return mlxb_fail(MLXB_BAD_ARG, "linear (q|k|v): %d outputs for %d query columns and 2 x %d x %d", N, q_width, Hkv, Dh);
   KvScatter kv = {positions, token_req, block_table, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, status,
                   max_pages, n_pages, page, Hkv, Dh, q_width};
-  if (use_stream())
+  if (use_stream(M, N))
     return gs::launch<__nv_bfloat16, true, false>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, kv, gs::NormFold{}, status, stream);
   return launch<__nv_bfloat16, true, false>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, kv, NormFold{}, stream);
 }

@@ -1,10 +1,11 @@
-// Linear layer for few rows (decode steps): M <= 64 tokens against a weight that has to be streamed from HBM once.
+// Linear layer for up to 16 rows (decode steps) against a WIDE weight that has to be streamed from HBM once, such
+// as an output head over a vocabulary:
 //   C[M,N] = epilogue(A[M,K] . W[N,K]^T + bias[N]) (+ residual[M,N])
-// A, W, residual bfloat16; float32 accumulation; C bfloat16 or float32.
+// A, W, residual bfloat16; float32 accumulation; C bfloat16 or float32.  (The second of two few-rows kernels:
+// gemm_smallm.cuh stages weights in registers and is the faster one for the narrower layers inside a block;
+// `preferred()` below says which runs.)
 //
-// The kernel is bound by reading W, and a decode step is a chain of such kernels, each a few microseconds long,
-// so it is organised around two things: the weight stream must never stop, and as little as possible may be left
-// to do once the kernel before has finished.
+// The kernel is bound by reading W, so it is organised around the weight stream, which must never stop:
 //
 //   * One CTA per SM (at most) owns a contiguous range of 8*NW-row tiles of W.  A producer warp copies the CTA's
 //     slab into a ring of shared-memory stages with bulk asynchronous copies (cp.async.bulk, completion counted
@@ -21,8 +22,8 @@
 //     shared memory (rows padded by 64 bytes: the eight lanes of a quarter warp hit distinct banks), A fragments
 //     from global memory (L2); with one token tile and K <= 1024 a warp meets the same K blocks in every tile of
 //     the CTA and keeps its A fragments in registers for all of them.
-//   * The partial sums of the warps are added in warp order through shared memory (double-buffered, one named
-//     barrier per tile): the order of additions depends on K and on the size class of M (up to 16, 32, 64 rows),
+//   * The partial sums of the warps are added in warp order through shared memory (one named barrier for the
+//     tiles of a CTA, up to four at a time): the order of additions depends on K and on the size class of M (up to 16, 32, 64 rows),
 //     never on which rows share the call.  Bias, the activation, the residual add and, for the fused
 //     [q | k | v] projection, the write of keys and values into the pages (kv_scatter.cuh) follow.
 //
@@ -36,7 +37,7 @@
 // |mean|/std; both stay below bfloat16 resolution while |mean| is not more than a hundred times the row's spread.
 //
 // Every wait on a barrier is bounded.  A wait that gives up sets a flag all roles see: the compute warps skip
-// the rest of their work but still meet at every tile's barrier, the producer waits (bounded) for the copies it
+// the rest of their work but still meet at every barrier, the producer waits (bounded) for the copies it
 // has in flight, nothing more is stored, and the kernel reports MLXB_ST_WAIT_TIMEOUT in the status word.
 // K must be a multiple of 8 (16-byte rows); other K go to the generic kernel.
 #pragma once
@@ -119,24 +120,23 @@ struct Geo {
   static constexpr int KB = KS / 32;                     // 32-wide K blocks of a stage
 };
 
-// MT: 16-row token tiles (M <= 16*MT); NW: 8-row weight tiles per stage; STAGES: depth of the ring.
+// MT: 16-row token tiles (M <= 16*MT); NW: 8-row weight tiles per stage; STAGES: depth of the ring; TG: tiles
+// whose epilogues run together.
 // RESIDENT: one token tile and K <= 1024: a warp's A fragments stay in registers for all the CTA's tiles.
-template <int MT, int NW, int STAGES, bool RESIDENT, typename TO, int EPI, bool SCATTER, bool FOLD>
+template <int MT, int NW, int STAGES, int TG, bool RESIDENT, typename TO, int EPI, bool SCATTER, bool FOLD>
 __global__ void __launch_bounds__(THREADS, MT <= 2 ? 2 : 1)
 gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                    const float* __restrict__ bias, const __nv_bfloat16* residual, TO* C, int M, int N, int K, int lda,
                    int ldc, KvScatter kv, NormFold fold, int* __restrict__ status) {
   using G = Geo<NW>;
   constexpr int PER = MT * NW * 4;                 // accumulators of a thread
-  constexpr int PART = CW * PER * 32;              // floats of one buffer of partial sums
-  constexpr int NBUF = (MT * NW <= 2) ? 2 : 1;     // double-buffered where that is cheap
+  constexpr int PART = CW * PER * 32;              // floats of a tile's partial sums
   extern __shared__ __align__(128) uint8_t smem[];
   uint8_t* stages = smem;                                                  // [STAGES][STAGE_BYTES]
-  float* part = reinterpret_cast<float*>(smem + STAGES * G::STAGE_BYTES);  // [NBUF][CW][PER][32]
-  float* stat = part + NBUF * PART;                                        // [CW][16 * MT][2] sums of x, x^2
+  float* part = reinterpret_cast<float*>(smem + STAGES * G::STAGE_BYTES);  // [TG][CW][PER][32]
+  float* stat = part + TG * PART;                                          // [CW][16 * MT][2] sums of x, x^2
   __shared__ uint64_t full[STAGES], empty[STAGES];
   __shared__ long long s_row_base[SCATTER ? 16 * MT : 1];
-  __shared__ float s_mean[FOLD ? 16 * MT : 1], s_rstd[FOLD ? 16 * MT : 1];
   __shared__ int s_abort;
   volatile int* abort_flag = &s_abort;
 
@@ -240,82 +240,159 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         }
       }
     };
-    uint4 a_now[RESIDENT ? 1 : KBW][MT][2], a_next[AHEAD ? KBW : 1][MT][2];
-    if constexpr (AHEAD) load_stage_a(0, a_now);
+    // two sets of fragments used in turns (no copies between them: a copy would wait for the loads it copies)
+    uint4 a_ping[RESIDENT ? 1 : KBW][MT][2], a_pong[AHEAD ? KBW : 1][MT][2];
+    bool flip = false;     // AHEAD: the current stage's fragments are in a_pong
+    if constexpr (AHEAD) load_stage_a(0, a_ping);
 
-    int it = 0;
-    bool ok = true;
-    for (int tile = t_begin; tile < t_end; ++tile) {
-      const int n0 = tile * G::ROWS;
-      const bool first = tile == t_begin;
-      float acc[MT][NW][4];
+    // The products of one block of a stage: the thread's W fragments of the tile's NW row groups from shared memory
+    // against its A fragments, added to acc; with `stats` the sums of x and x^2 on the way.
+    auto block_products = [&](const uint8_t* st, int kb, int k, int n0, const uint4 (&af)[MT][2], float (&acc)[MT][NW][4],
+                              bool stats) {
+      const bool kin = k + 8 * q < K;
+      uint4 wv[NW];
 #pragma unroll
-      for (int i = 0; i < MT; ++i)
+      for (int j = 0; j < NW; ++j)
+        wv[j] = (kin && n0 + j * 8 + g < N) ? gs::lds128(st + (size_t)(j * 8 + g) * G::ROW_BYTES + (kb * 32 + 8 * q) * 2)
+                                            : zero;
 #pragma unroll
-        for (int j = 0; j < NW; ++j)
+      for (int i = 0; i < MT; ++i) {
+        const uint4 a0 = af[i][0], a1 = af[i][1];
 #pragma unroll
-          for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
-
-      for (int ks = 0; ks < n_ks && ok; ++ks, ++it) {
-        const int s = it % STAGES;
-        if constexpr (!RESIDENT && !AHEAD) load_stage_a(ks, a_now);
-        if constexpr (AHEAD) load_stage_a(ks + 1 < n_ks ? ks + 1 : 0, a_next);   // the next stage's, or the next tile's first
-        if (!(ok = mbar_wait_warp(&full[s], (uint32_t)((it / STAGES) & 1), abort_flag))) break;
-        const uint8_t* st = stages + (size_t)s * G::STAGE_BYTES;
-        const int k0 = ks * G::KS;
+        for (int j = 0; j < NW; ++j) {
+          gs::mma_bf16(acc[i][j], a0.x, a1.x, a0.y, a1.y, wv[j].x, wv[j].y);
+          gs::mma_bf16(acc[i][j], a0.z, a1.z, a0.w, a1.w, wv[j].z, wv[j].w);
+        }
+        if (stats) {
 #pragma unroll
-        for (int b = 0; b < KBW; ++b) {
-          const int kb = warp + b * CW;               // block of the stage
-          const int k = k0 + kb * 32;
-          if (kb < G::KB && k < K) {
-            const bool kin = k + 8 * q < K;
-            uint4 wv[NW];
+          for (int h = 0; h < 2; ++h) {
+            float v[8];
+            unpack8(h == 0 ? a0 : a1, v);
 #pragma unroll
-            for (int j = 0; j < NW; ++j)
-              wv[j] = (kin && n0 + j * 8 + g < N) ? gs::lds128(st + (size_t)(j * 8 + g) * G::ROW_BYTES + (kb * 32 + 8 * q) * 2)
-                                                  : zero;
-#pragma unroll
-            for (int i = 0; i < MT; ++i) {
-              uint4 a0, a1;
-              if constexpr (RESIDENT) { a0 = a_res[b][i][0]; a1 = a_res[b][i][1]; }
-              else { a0 = a_now[b][i][0]; a1 = a_now[b][i][1]; }
-#pragma unroll
-              for (int j = 0; j < NW; ++j) {
-                gs::mma_bf16(acc[i][j], a0.x, a1.x, a0.y, a1.y, wv[j].x, wv[j].y);
-                gs::mma_bf16(acc[i][j], a0.z, a1.z, a0.w, a1.w, wv[j].z, wv[j].w);
-              }
-              if (FOLD && first) {
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                  float v[8];
-                  unpack8(h == 0 ? a0 : a1, v);
-#pragma unroll
-                  for (int e = 0; e < 8; ++e) {
-                    sx[i][h] += v[e];
-                    sq[i][h] = fmaf(v[e], v[e], sq[i][h]);
-                  }
-                }
-              }
+            for (int e = 0; e < 8; ++e) {
+              sx[i][h] += v[e];
+              sq[i][h] = fmaf(v[e], v[e], sq[i][h]);
             }
           }
         }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(&empty[s]);
-        if constexpr (AHEAD) {
-#pragma unroll
-          for (int b = 0; b < KBW; ++b)
-#pragma unroll
-            for (int i = 0; i < MT; ++i) { a_now[b][i][0] = a_next[b][i][0]; a_now[b][i][1] = a_next[b][i][1]; }
-        }
       }
-
-      float* buf = part + (NBUF == 2 ? (tile & 1) * PART : 0);
+    };
+    auto store_partials = [&](int tg, const float (&acc)[MT][NW][4]) {
+      float* buf = part + tg * PART;
 #pragma unroll
       for (int i = 0; i < MT; ++i)
 #pragma unroll
         for (int j = 0; j < NW; ++j)
 #pragma unroll
           for (int c = 0; c < 4; ++c) buf[(warp * PER + (i * NW + j) * 4 + c) * 32 + lane] = acc[i][j][c];
+    };
+
+    // The CTA's tiles are worked off in groups of TG: the products of all tiles of a group first (their partial
+    // sums go to shared memory, a buffer per tile), then ONE barrier and one epilogue for the whole group, whose
+    // operands (bias, column sums: weights; residual: asked for right behind the wait for the kernel before) are in
+    // registers by then.  A CTA of a layer of GPT-2 medium has one group, so the work after the wait is: A
+    // fragments, products from shared memory, one barrier, sums, store.
+    constexpr int TILE_E = PER * 32;                                // elements (row, column) of a tile
+    constexpr int EPT = (TG * TILE_E + CW * 32 - 1) / (CW * 32);    // elements of a group a thread finishes
+    auto elem = [&](int e, int tile0, int& tg, int& m, int& n) {
+      tg = e / TILE_E;
+      const int r = e - tg * TILE_E, idx = r >> 5, ln = r & 31;
+      const int c = idx & 3, j = (idx >> 2) % NW, i = (idx >> 2) / NW;
+      m = i * 16 + (ln >> 2) + ((c & 2) ? 8 : 0);
+      n = (tile0 + tg) * G::ROWS + j * 8 + 2 * (ln & 3) + (c & 1);
+    };
+
+    int it = 0;
+    bool ok = true;
+    for (int tile0 = t_begin; tile0 < t_end; tile0 += TG) {
+      float e_bias[EPT], e_colsum[EPT], e_res[EPT];
+#pragma unroll
+      for (int x = 0; x < EPT; ++x) {
+        int tg, m, n;
+        elem(threadIdx.x + x * CW * 32, tile0, tg, m, n);
+        const bool in = threadIdx.x + x * CW * 32 < TG * TILE_E && tile0 + tg < t_end && m < M && n < N;
+        e_bias[x] = (in && bias) ? bias[n] : 0.f;
+        e_colsum[x] = (FOLD && in) ? fold.colsum[n] : 0.f;
+        e_res[x] = (in && residual) ? __bfloat162float(residual[(size_t)m * ldc + n]) : 0.f;
+      }
+      const bool first = tile0 == t_begin;
+      if constexpr (RESIDENT) {
+        // One stage per tile: the tiles of the group are worked on side by side, a block of all of them at a
+        // time, so that their chains of dependent products overlap.
+        const int n_group = min(TG, t_end - tile0);
+        float acc[TG][MT][NW][4];
+#pragma unroll
+        for (int tg = 0; tg < TG; ++tg)
+#pragma unroll
+          for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int j = 0; j < NW; ++j)
+#pragma unroll
+              for (int c = 0; c < 4; ++c) acc[tg][i][j][c] = 0.f;
+        for (int tg = 0; tg < n_group && ok; ++tg)
+          ok = mbar_wait_warp(&full[(it + tg) % STAGES], (uint32_t)(((it + tg) / STAGES) & 1), abort_flag);
+        if (ok) {
+#pragma unroll
+          for (int b = 0; b < KBW; ++b) {
+            const int kb = warp + b * CW, k = kb * 32;
+            if (kb < G::KB && k < K) {
+#pragma unroll
+              for (int tg = 0; tg < TG; ++tg)
+                if (tg < n_group)
+                  block_products(stages + (size_t)((it + tg) % STAGES) * G::STAGE_BYTES, kb, k, (tile0 + tg) * G::ROWS,
+                                 a_res[b], acc[tg], FOLD && first && tg == 0);
+            }
+          }
+          __syncwarp();
+          if (lane == 0)
+            for (int tg = 0; tg < n_group; ++tg) mbar_arrive(&empty[(it + tg) % STAGES]);
+        }
+        it += n_group;
+#pragma unroll
+        for (int tg = 0; tg < TG; ++tg)
+          if (tg < n_group) store_partials(tg, acc[tg]);
+      } else {
+#pragma unroll 1
+        for (int tg = 0; tg < TG; ++tg) {
+          const int tile = tile0 + tg;
+          if (tile >= t_end) break;
+          const int n0 = tile * G::ROWS;
+          const bool stats = FOLD && first && tg == 0;
+          float acc[MT][NW][4];
+#pragma unroll
+          for (int i = 0; i < MT; ++i)
+#pragma unroll
+            for (int j = 0; j < NW; ++j)
+#pragma unroll
+              for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
+          // one stage: its A fragments are in `use`; with AHEAD the next stage's (or the next tile's first) go to `fill`
+          auto stage = [&](int ks, uint4 (&use)[KBW][MT][2], uint4 (&fill)[AHEAD ? KBW : 1][MT][2]) {
+            const int s = it % STAGES;
+            if constexpr (!AHEAD) load_stage_a(ks, use);
+            if constexpr (AHEAD) load_stage_a(ks + 1 < n_ks ? ks + 1 : 0, fill);
+            if (!(ok = mbar_wait_warp(&full[s], (uint32_t)((it / STAGES) & 1), abort_flag))) return;
+            const uint8_t* st = stages + (size_t)s * G::STAGE_BYTES;
+#pragma unroll
+            for (int b = 0; b < KBW; ++b) {
+              const int kb = warp + b * CW, k = ks * G::KS + kb * 32;
+              if (kb < G::KB && k < K) block_products(st, kb, k, n0, use[b], acc, stats);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+            ++it;
+          };
+          for (int ks = 0; ks < n_ks && ok; ++ks) {
+            if constexpr (AHEAD) {
+              if (!flip) stage(ks, a_ping, a_pong);
+              else stage(ks, a_pong, a_ping);
+              flip = !flip;
+            } else {
+              stage(ks, a_ping, a_pong);
+            }
+          }
+          store_partials(tg, acc);
+        }
+      }
       if (FOLD && first) {
 #pragma unroll
         for (int i = 0; i < MT; ++i)
@@ -332,40 +409,31 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
           }
       }
       compute_barrier();
-      if (FOLD && first) {
-        if (threadIdx.x < 16 * MT) {
-          float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-          for (int w = 0; w < CW; ++w) {
-            s1 += stat[(w * 16 * MT + threadIdx.x) * 2];
-            s2 += stat[(w * 16 * MT + threadIdx.x) * 2 + 1];
-          }
-          const float mean = s1 / (float)K;
-          const float var = fmaxf(s2 / (float)K - mean * mean, 0.f);
-          s_mean[threadIdx.x] = mean;
-          s_rstd[threadIdx.x] = rsqrtf(var + fold.eps);
-        }
-        compute_barrier();
-      }
       if (!*abort_flag) {
-        // element e of the tile: accumulator (i, j, c) of lane ln, i.e. row m and column n
-        constexpr int EPT = (PER * 32 + CW * 32 - 1) / (CW * 32);
 #pragma unroll
         for (int x = 0; x < EPT; ++x) {
           const int e = threadIdx.x + x * CW * 32;
-          if (e >= PER * 32) break;
-          const int idx = e >> 5, ln = e & 31;
-          const int c = idx & 3, j = (idx >> 2) % NW, i = (idx >> 2) / NW;
-          const int m = i * 16 + (ln >> 2) + ((c & 2) ? 8 : 0);
-          const int n = n0 + j * 8 + 2 * (ln & 3) + (c & 1);
-          if (m < M && n < N) {
+          int tg, m, n;
+          elem(e, tile0, tg, m, n);
+          if (e < TG * TILE_E && tile0 + tg < t_end && m < M && n < N) {
+            const float* buf = part + tg * PART + (e - tg * TILE_E);
             float v = 0.f;
 #pragma unroll
-            for (int w = 0; w < CW; ++w) v += buf[w * PER * 32 + e];
-            if (FOLD) v = s_rstd[m] * (v - s_mean[m] * fold.colsum[n]);
-            if (bias) v += bias[n];
+            for (int w = 0; w < CW; ++w) v += buf[w * TILE_E];
+            if (FOLD) {   // the row's statistics: the warps' shares, added in warp order
+              float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+              for (int w = 0; w < CW; ++w) {
+                s1 += stat[(w * 16 * MT + m) * 2];
+                s2 += stat[(w * 16 * MT + m) * 2 + 1];
+              }
+              const float mean = s1 / (float)K;
+              const float var = fmaxf(s2 / (float)K - mean * mean, 0.f);
+              v = rsqrtf(var + fold.eps) * (v - mean * e_colsum[x]);
+            }
+            v += e_bias[x];
             v = activate<EPI, true>(v);
-            if (residual) v += __bfloat162float(residual[(size_t)m * ldc + n]);
+            v += e_res[x];
             if (SCATTER && n >= kv.q_width) {
               __nv_bfloat16* dst = kv_slot_at(kv, s_row_base[m], n);
               if (dst) *dst = __float2bfloat16_rn(v);
@@ -375,7 +443,7 @@ gemm_stream_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
           }
         }
       }
-      if (NBUF == 1) compute_barrier();   // the one buffer is written again by the next tile
+      if (tile0 + TG < t_end) compute_barrier();   // the buffers are written again by the next group
     }
   }
   __syncthreads();
@@ -392,7 +460,7 @@ static inline int sm_count() {
   return n;
 }
 
-template <int MT, int NW, int STAGES, bool RESIDENT, typename TO, bool SCATTER, bool FOLD>
+template <int MT, int NW, int STAGES, int TG, bool RESIDENT, typename TO, bool SCATTER, bool FOLD>
 static int launch_cfg(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N,
                       int K, int lda, int ldc, int epi, const KvScatter& kv, const NormFold& fold, int* status,
                       cudaStream_t stream) {
@@ -400,13 +468,12 @@ static int launch_cfg(const void* A, const void* W, const float* bias, const voi
   const int n_tiles = (N + G::ROWS - 1) / G::ROWS;
   const dim3 grid(n_tiles < sm_count() ? n_tiles : sm_count());
   constexpr int PER = MT * NW * 4;
-  constexpr int NBUF = (MT * NW <= 2) ? 2 : 1;
-  const size_t smem = (size_t)STAGES * G::STAGE_BYTES + (size_t)NBUF * CW * PER * 32 * sizeof(float) +
+  const size_t smem = (size_t)STAGES * G::STAGE_BYTES + (size_t)TG * CW * PER * 32 * sizeof(float) +
                       (size_t)CW * 16 * MT * 2 * sizeof(float);
   // The fused cache write has no activation: only the plain epilogue is built for it.
   return dispatch_activation(SCATTER ? (int)EPI_NONE : epi, [&](auto e) {
     constexpr int EPI = SCATTER ? (int)EPI_NONE : (int)decltype(e)::value;
-    auto kern = gemm_stream_kernel<MT, NW, STAGES, RESIDENT, TO, EPI, SCATTER, FOLD>;
+    auto kern = gemm_stream_kernel<MT, NW, STAGES, TG, RESIDENT, TO, EPI, SCATTER, FOLD>;
     static bool raised = false;   // once per instantiation, and never for the first time inside a stream capture
     if (!raised) {
       cudaError_t err = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -424,19 +491,22 @@ template <typename TO, bool SCATTER, bool FOLD>
 static int launch(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N, int K,
                   int lda, int ldc, int epi, const KvScatter& kv, const NormFold& fold, int* status,
                   cudaStream_t stream) {
-#define GS_GO(MT_, NW_, ST_, RES_) \
-  return launch_cfg<MT_, NW_, ST_, RES_, TO, SCATTER, FOLD>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, kv, fold, status, stream)
-  if (M <= 16) {
-    if (K <= 1024) GS_GO(1, 1, 5, true);
-    GS_GO(1, 1, 5, false);
-  }
-  if (M <= 32) GS_GO(2, 1, 5, false);
-  GS_GO(4, 2, 4, false);
+#define GS_GO(MT_, NW_, ST_, TG_, RES_) \
+  return launch_cfg<MT_, NW_, ST_, TG_, RES_, TO, SCATTER, FOLD>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, kv, fold, status, stream)
+  if (K <= 1024) GS_GO(1, 1, 5, 4, true);
+  GS_GO(1, 1, 5, 4, false);
 #undef GS_GO
 }
 
+// Where this kernel is the faster one of the two few-rows kernels (measured on a B200 with the widths of GPT-2
+// medium, large and XL): up to 16 rows against an output as wide as a vocabulary.  Each CTA then streams dozens
+// of tiles and the ring never runs dry.  For the layers inside a block (a few tiles per CTA) the kernel that
+// stages weights in registers (gemm_smallm.cuh) is as fast or faster: there a launch is bounded by what follows
+// the wait for the kernel before (A fragments, a chain of products, a barrier, the epilogue), not by the stream.
+static inline bool preferred(int M, int N) { return M <= 16 && N >= 8192; }
+
 static int check_args(int M, int N, int K, int lda, int ldc, int epi, const void* A, const void* W) {
-  if (M > 64) return mlxb_fail(MLXB_BAD_ARG, "linear (few rows): %d rows, at most 64", M);
+  if (M > 16) return mlxb_fail(MLXB_BAD_ARG, "linear (few rows, streamed): %d rows, at most 16", M);
   if (K <= 0 || (K & 7) || (lda & 7) || lda < K || ldc < N)
     return mlxb_fail(MLXB_BAD_ARG, "linear (few rows): K %d and row stride %d must be multiples of 8 (ldc %d, N %d)",
                      K, lda, ldc, N);
