@@ -1,21 +1,6 @@
 // The few-rows linear layer (gemm_smallm.cuh) as it is: plain, and with the cache write of a fused
 // [q | k | v] projection in its epilogue.
 #include "gemm_smallm.cuh"
-#include "gemm_stream.cuh"
-
-// Which of the two few-rows kernels runs: the one that streams weights through shared memory (gemm_stream.cuh)
-// where it is the faster one, else the one that stages them in registers (gemm_smallm.cuh).
-// MLXB_SMALLM=registers / =stream forces one of them wherever it can run, for comparison.
-static bool use_stream(int M, int N) {
-  static int forced = -1;
-  if (forced < 0) {
-    const char* e = getenv("MLXB_SMALLM");
-    forced = !e ? 0 : (e[0] == 'r' ? 1 : (e[0] == 's' ? 2 : 0));
-  }
-  if (forced == 1) return false;
-  if (forced == 2) return M <= 16;
-  return gs::preferred(M, N);
-}
 
 MLXB_DEFINE_LAST_ERROR()
 
@@ -23,15 +8,10 @@ MLXB_DEFINE_LAST_ERROR()
 // W: bfloat16 [N, K] contiguous; bias float32[N] or null; residual bfloat16 [M, N] at row stride ldc or null;
 // C: bfloat16 or float32 (out_f32) [M, N] at row stride ldc.  1 <= M <= 64, K % 8 == 0.
 MLXB_EXPORT int mlxb_linear_smallm(int out_f32, const void* A, const void* W, const float* bias, const void* residual,
-                                   void* C, int M, int N, int K, int lda, int ldc, int epi, int* status,
-                                   cudaStream_t stream) {
+                                   void* C, int M, int N, int K, int lda, int ldc, int epi, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (int e = check_args(M, N, K, lda, ldc, epi, A, W)) return e;
   const KvScatter none = {};
-  if (use_stream(M, N)) {
-    if (out_f32) return gs::launch<float, false, false>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, gs::NormFold{}, status, stream);
-    return gs::launch<__nv_bfloat16, false, false>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, gs::NormFold{}, status, stream);
-  }
   if (out_f32) return launch<float, false, false>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, NormFold{}, stream);
   return launch<__nv_bfloat16, false, false>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, NormFold{}, stream);
 }
@@ -50,7 +30,5 @@ MLXB_EXPORT int mlxb_linear_smallm_qkv(const void* A, const void* W, const float
     return mlxb_fail(MLXB_BAD_ARG, "linear (q|k|v): %d outputs for %d query columns and 2 x %d x %d", N, q_width, Hkv, Dh);
   KvScatter kv = {positions, token_req, block_table, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, status,
                   max_pages, n_pages, page, Hkv, Dh, q_width};
-  if (use_stream(M, N))
-    return gs::launch<__nv_bfloat16, true, false>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, kv, gs::NormFold{}, status, stream);
   return launch<__nv_bfloat16, true, false>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, kv, NormFold{}, stream);
 }

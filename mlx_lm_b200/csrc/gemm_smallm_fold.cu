@@ -2,37 +2,17 @@
 // W . diag(gain), bias the folded bias, colsum[n] = sum_k W[n,k] (float32), eps the norm's; A holds the rows
 // before the norm.  See NormFold in gemm_smallm.cuh.  Otherwise as the entry points of gemm_smallm.cu.
 #include "gemm_smallm.cuh"
-#include "gemm_stream.cuh"
-
-// Which of the two few-rows kernels runs: the one that streams weights through shared memory (gemm_stream.cuh)
-// where it is the faster one, else the one that stages them in registers (gemm_smallm.cuh).
-// MLXB_SMALLM=registers / =stream forces one of them wherever it can run, for comparison.
-static bool use_stream(int M, int N) {
-  static int forced = -1;
-  if (forced < 0) {
-    const char* e = getenv("MLXB_SMALLM");
-    forced = !e ? 0 : (e[0] == 'r' ? 1 : (e[0] == 's' ? 2 : 0));
-  }
-  if (forced == 1) return false;
-  if (forced == 2) return M <= 16;
-  return gs::preferred(M, N);
-}
 
 MLXB_DEFINE_LAST_ERROR()
 
 MLXB_EXPORT int mlxb_linear_smallm_fold(int out_f32, const void* A, const void* W, const float* bias,
                                         const void* residual, void* C, int M, int N, int K, int lda, int ldc, int epi,
-                                        const float* colsum, float eps, int* status, cudaStream_t stream) {
+                                        const float* colsum, float eps, cudaStream_t stream) {
   if (M <= 0 || N <= 0) return 0;
   if (int e = check_args(M, N, K, lda, ldc, epi, A, W)) return e;
   if (colsum == nullptr) return mlxb_fail(MLXB_BAD_ARG, "linear (folded norm): column sums missing");
   const KvScatter none = {};
   const NormFold fold = {colsum, eps};
-  if (use_stream(M, N)) {
-    const gs::NormFold f = {colsum, eps};
-    if (out_f32) return gs::launch<float, false, true>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, f, status, stream);
-    return gs::launch<__nv_bfloat16, false, true>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, f, status, stream);
-  }
   if (out_f32) return launch<float, false, true>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, fold, stream);
   return launch<__nv_bfloat16, false, true>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, none, fold, stream);
 }
@@ -50,9 +30,5 @@ MLXB_EXPORT int mlxb_linear_smallm_qkv_fold(const void* A, const void* W, const 
   KvScatter kv = {positions, token_req, block_table, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, status,
                   max_pages, n_pages, page, Hkv, Dh, q_width};
   const NormFold fold = {colsum, eps};
-  if (use_stream(M, N)) {
-    const gs::NormFold f = {colsum, eps};
-    return gs::launch<__nv_bfloat16, true, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, kv, f, status, stream);
-  }
   return launch<__nv_bfloat16, true, true>(A, W, bias, nullptr, C, M, N, K, lda, ldc, EPI_NONE, kv, fold, stream);
 }

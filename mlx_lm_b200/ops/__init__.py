@@ -282,12 +282,12 @@ def linear_generic(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=N
 
 
 _SMALLM_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                c_void_p, c_void_p]
+                c_void_p]
 
 SMALL_M = 64
 
 _SMALLM_FOLD_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                     c_void_p, c_float, c_void_p, c_void_p]
+                     c_void_p, c_float, c_void_p]
 
 
 def _fold_args(fold, N: int, what: str):
@@ -298,15 +298,14 @@ def _fold_args(fold, N: int, what: str):
     return colsum, float(eps)
 
 
-def linear_few_rows(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=None, fold=None, status=None) -> None:
+def linear_few_rows(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=None, fold=None) -> None:
     """``linear_generic``'s contract for bfloat16 and at most 64 rows: the weight is streamed from HBM once
     with 16-byte loads and multiplied on the tensor cores (csrc/gemm_smallm.cuh).  ``K`` and the row stride of
     ``x`` must be multiples of 8.
 
     ``fold = (colsum, eps)``: ``x`` holds the rows before a LayerNorm that has been folded into ``w`` and ``bias``
     (``parts.linear.Linear.fold_norm``); the kernel computes ``rstd (x w^T - mean colsum) + bias`` with the
-    rows' mean and 1/std found on the way.  ``status`` (optional) receives ``ST_WAIT_TIMEOUT`` if a bounded wait
-    of the kernel gives up."""
+    rows' mean and 1/std found on the way."""
     _need(x, torch.bfloat16, "linear x")
     _need(w, torch.bfloat16, "linear w")
     M, K = x.shape
@@ -327,10 +326,10 @@ def linear_few_rows(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=
     if fold is not None:
         colsum, eps = _fold_args(fold, N, "linear")
         _call("gemm_smallm_fold", "mlxb_linear_smallm_fold", _SMALLM_FOLD_ARGS, int(out.dtype == torch.float32), _p(x),
-              _p(w), _p(bias), _p(residual), _p(out), M, N, K, lda, ldc, epilogue, _p(colsum), eps, _p(status), stream)
+              _p(w), _p(bias), _p(residual), _p(out), M, N, K, lda, ldc, epilogue, _p(colsum), eps, stream)
         return
     _call("gemm_smallm", "mlxb_linear_smallm", _SMALLM_ARGS, int(out.dtype == torch.float32), _p(x), _p(w), _p(bias),
-          _p(residual), _p(out), M, N, K, lda, ldc, epilogue, _p(status), stream)
+          _p(residual), _p(out), M, N, K, lda, ldc, epilogue, stream)
 
 
 _TC_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,

@@ -124,8 +124,7 @@ class Linear(Part):
         ops.label(self.name, 2.0 * M * self.n_in * self.n_out,
                   self.weight.element_size() * (self.n_in * self.n_out + M * self.n_in) + out.element_size() * M * self.n_out)
         if fast and few:
-            ops.linear_few_rows(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual, fold=fold,
-                                status=ctx.status)
+            ops.linear_few_rows(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual, fold=fold)
         elif fast:
             ops.linear_tensor_cores(x, self.weight, self.bias, out, ctx.status, ctx.stream, epilogue=epi,
                                     residual=residual, fold=fold)

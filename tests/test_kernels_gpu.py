@@ -90,7 +90,7 @@ def test_row_stats(ops, R_, D, shift):
 
 
 @pytest.mark.parametrize("M,N,K,shift", [(1, 200, 96, 0.0), (7, 1000, 320, 1.5), (16, 72, 1600, 40.0), (33, 200, 96, -2.0),
-                                         (8, 8400, 1024, 1.5), (13, 9000, 2056, -3.0),      # the streaming kernel
+                                         (8, 8400, 1024, 1.5), (13, 9000, 2056, -3.0),      # very wide outputs
                                          (64, 1000, 320, 0.5), (200, 264, 96, 1.5), (130, 1000, 1600, 40.0)])
 def test_linear_with_folded_norm(ops, M, N, K, shift):
     """LayerNorm folded into the weights (parts.linear.Linear.fold_norm): the few-rows kernel (statistics from its
@@ -172,8 +172,7 @@ def test_linear_generic(ops, dtype, M, N, K):
 
 @pytest.mark.parametrize("M,N,K", [(1, 192, 64), (1, 1000, 96), (8, 320, 96), (16, 96, 320), (17, 3072, 1024),
                                    (33, 50257, 64), (64, 1600, 6400), (64, 50257, 1024), (5, 7, 8), (40, 1000, 1608),
-                                   # up to 16 rows against a very wide output: the kernel that streams weights through
-                                   # shared memory (one stage a tile, several stages a tile with a ragged last one)
+                                   # up to 16 rows against a very wide output, inner sizes with a ragged last block
                                    (8, 50257, 1024), (1, 50257, 64), (16, 9000, 1608), (3, 8200, 4096)])
 def test_linear_few_rows(ops, M, N, K):
     g = torch.Generator().manual_seed(M * N + K)
@@ -304,7 +303,7 @@ def test_linear_tensor_cores_finds_one_hot_entries(ops):
 
 
 @pytest.mark.parametrize("Hq,Hkv,Dh,page,K", [(4, 4, 16, 16, 64), (3, 3, 32, 16, 96), (6, 2, 48, 32, 288), (16, 16, 64, 16, 1024),
-                                              (48, 48, 64, 16, 256)])      # 9216 outputs: the streaming kernel
+                                              (48, 48, 64, 16, 256)])      # 9216 outputs
 def test_linear_qkv_to_cache(ops, Hq, Hkv, Dh, page, K):
     """The fused projection writes queries to its output and keys/values into the right page rows, as the
     plain projection followed by kv_write does; padding rows (request -1) write nothing."""
