@@ -23,6 +23,17 @@
 //
 // (Heads of 64 in tiles of 128 queries run on the tcgen05 kernel of attention_prefill_tc.cu instead; this one
 // serves every other head size that is a multiple of 16, and tiles of 64.)
+//
+// Single-token rows (decode steps) are tiles of one query: QW = 1, so a "group" is one warp that gathers and
+// multiplies key blocks of its own, and KSPLIT warps share a row's keys (block index modulo KSPLIT) and merge at
+// the end.  Fifteen of the sixteen query rows of every product are zeros, which costs nothing that matters: the
+// kernel is bound by reading keys and values, and per key it issues a tenth of the instructions of a kernel that
+// multiplies on the CUDA cores (one 16-byte copy per 8 elements and a handful of tensor-core instructions per
+// 64 keys, no unpacking, no shuffles per key).
+//
+// A tile's keys before its first query are older than this step, so the first block of each group is asked for
+// before the wait for the previous kernel if it lies wholly before that query; queries, and the blocks that hold
+// this step's own keys, are fetched after it.
 #include "common.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
@@ -67,6 +78,7 @@ __device__ __forceinline__ unsigned pack_bf16(float lo, float hi) {
 // tiles: int32 [n_tiles][4] = (row of the tile's first token among the step's tokens, queries in the tile
 // (1..16*WARPS), block-table row of the request, position of the tile's first query).
 __device__ __forceinline__ void group_barrier(int id, int threads) {
+  if (threads == 32) { __syncwarp(); return; }      // a group of one warp
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
@@ -91,11 +103,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
   __nv_bfloat16* sv = sk + 2 * BKV * STRIDE;                                                     // [2][BKV][STRIDE]
 
   pdl_trigger();
-  pdl_wait();
-  q = after_wait(q);
-  k_pool = after_wait(k_pool);
-  v_pool = after_wait(v_pool);
-  const int4 tile = tiles[blockIdx.x];
+  const int4 tile = tiles[blockIdx.x];      // the step's inputs: no kernel writes them
   const int row0 = tile.x, n_rows = tile.y, req = tile.z, pos0 = tile.w;
   const int h = blockIdx.y, hk = h / (Hq / Hkv);
   const int warp = gtid >> 5, lane = threadIdx.x & 31, g = lane >> 2, qd = lane & 3;
@@ -146,7 +154,15 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
 
   // this group's blocks: kb_first, kb_first + KSPLIT, ... (block indices congruent to `group`)
   const int kb_first = kb_lo + ((group - kb_lo) % KSPLIT + KSPLIT) % KSPLIT;
-  if (kb_first <= kb_hi) load_block(kb_first, 0);
+  // keys before the tile's first query are older than this step: such a block can be on its way before the
+  // wait for the kernel that wrote this step's queries, keys and values
+  const bool early = kb_first <= kb_hi && (kb_first + 1) * BKV <= pos0;
+  if (early) load_block(kb_first, 0);
+  pdl_wait();
+  q = after_wait(q);
+  k_pool = after_wait(k_pool);
+  v_pool = after_wait(v_pool);
+  if (!early && kb_first <= kb_hi) load_block(kb_first, 0);
 
   // this warp's 16 queries: rows r_lo = 16*warp + g and r_hi = r_lo + 8 of the tile
   const int r_lo = warp * 16 + g, r_hi = r_lo + 8;
@@ -375,6 +391,39 @@ MLXB_EXPORT int mlxb_attention_prefill(const void* q, int ldq, const int* tiles,
     GO(16); GO(32); GO(48); GO(64); GO(80); GO(96); GO(112); GO(128);
     default:
       return mlxb_fail(MLXB_BAD_ARG, "attention (portions): head size %d is not a multiple of 16 up to 128", Dh);
+  }
+#undef GO
+}
+
+// Rows with one query each (decode steps) as tiles of one query: tiles as above with 1 (or, for a padding row, 0)
+// queries.  ksplit: warps that share a row's key blocks, 2, 4 or 8; more warps shorten the chain of blocks a warp
+// walks, fewer leave room for several CTAs per SM.  A row's result depends on ksplit by rounding only.
+MLXB_EXPORT int mlxb_attention_rows(const void* q, int ldq, const int* tiles, int n_tiles, int ksplit,
+                                    const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
+                                    int Dh, int window, float scale, const void* k_pool, const void* v_pool, void* out,
+                                    int ldo, int* status, cudaStream_t stream) {
+  if (n_tiles <= 0) return 0;
+  if (page <= 0 || (page & (page - 1))) return mlxb_fail(MLXB_BAD_ARG, "attention (single rows): page size %d", page);
+  if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || Hq > 65535)
+    return mlxb_fail(MLXB_BAD_ARG, "attention (single rows): %d query heads over %d key/value heads", Hq, Hkv);
+  if ((ldq & 1) || (ldo & 1) || ((uintptr_t)q & 3) || ((uintptr_t)out & 3) || ((uintptr_t)tiles & 15))
+    return mlxb_fail(MLXB_BAD_ARG, "attention (single rows): rows must be 4-byte aligned, the tile list 16-byte aligned");
+  if (ksplit != 2 && ksplit != 4 && ksplit != 8)
+    return mlxb_fail(MLXB_BAD_ARG, "attention (single rows): %d warps per row (2, 4 or 8)", ksplit);
+#define GO(D)                                                                                                         \
+  case D:                                                                                                             \
+    if (ksplit == 2)                                                                                                  \
+      return launch<D, 1, 2>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,   \
+                             k_pool, v_pool, out, ldo, status, stream);                                               \
+    if (ksplit == 4 || (size_t)8 * 4 * BKV * (D + 8) * 2 > 200 * 1024)                                                \
+      return launch<D, 1, 4>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,   \
+                             k_pool, v_pool, out, ldo, status, stream);                                               \
+    return launch<D, 1, 8>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,     \
+                           k_pool, v_pool, out, ldo, status, stream)
+  switch (Dh) {
+    GO(16); GO(32); GO(48); GO(64); GO(80); GO(96); GO(112); GO(128);
+    default:
+      return mlxb_fail(MLXB_BAD_ARG, "attention (single rows): head size %d is not a multiple of 16 up to 128", Dh);
   }
 #undef GO
 }

@@ -39,7 +39,8 @@ class DecodeGraph:
         B, W = bucket, mgr.table_width
         pad = lambda n: (n + 3) & ~3
         sizes = [("tokens", B), ("positions", B), ("token_req", B), ("logit_rows", B), ("slots", B),
-                 ("req_first_token", B + 1), ("req_first_position", B), ("sample", B * ops.SAMPLE_WORDS)]
+                 ("req_first_token", B + 1), ("req_first_position", B), ("sample", B * ops.SAMPLE_WORDS),
+                 ("single_tiles", 4 * B)]
         sizes += [(f"table{g}", B * W) for g in range(len(mgr.kv_groups))]
         self.off, total = {}, 0
         for name, n in sizes:
@@ -54,6 +55,9 @@ class DecodeGraph:
         h[self.off["logit_rows"]: self.off["logit_rows"] + B] = np.arange(B)
         h[self.off["req_first_token"]: self.off["req_first_token"] + B + 1] = np.arange(B + 1)
         h[self.off["token_req"]: self.off["token_req"] + B] = -1
+        tiles = h[self.off["single_tiles"]: self.off["single_tiles"] + 4 * B].reshape(B, 4)
+        tiles[:] = 0
+        tiles[:, 0] = np.arange(B)          # (token row, 0 queries, ...): a padding row until a request takes it
         for g in range(len(mgr.kv_groups)):
             h[self.off[f"table{g}"]: self.off[f"table{g}"] + B * W] = -1
 
@@ -67,6 +71,7 @@ class DecodeGraph:
         ctx._slots = view("slots", B)
         ctx._tables = [view(f"table{g}", B * W).view(B, W) for g in range(len(mgr.kv_groups))]
         ctx.n_single, ctx.n_portion, ctx.max_q_len = B, 0, 1
+        ctx.single_tiles = view("single_tiles", 4 * B)
         self.ctx = ctx
         self.params = view("sample", B * ops.SAMPLE_WORDS)
         self.tok = self.out[:B]
@@ -101,6 +106,8 @@ class DecodeGraph:
         n = len(entries)
         h, off, W = self.host.numpy(), self.off, mgr.table_width
         h[off["token_req"] + n: off["token_req"] + B] = -1
+        tiles = h[off["single_tiles"]: off["single_tiles"] + 4 * B].reshape(B, 4)
+        tiles[n:, 1:] = 0
         words = []
         try:
             for i, e in enumerate(entries):
@@ -110,6 +117,7 @@ class DecodeGraph:
                 h[off["token_req"] + i] = i
                 h[off["slots"] + i] = mgr.requests[e.rid].slot
                 h[off["req_first_position"] + i] = start
+                tiles[i, 1], tiles[i, 2], tiles[i, 3] = 1, i, start
                 r = requests[i]
                 words.append(r.sampler.words(seed, r.uid, len(r.tokens)))
             h[off["sample"]: off["sample"] + n * ops.SAMPLE_WORDS] = np.frombuffer(b"".join(words), dtype=np.int32)

@@ -120,6 +120,9 @@ class StepContext:
         # block-table row, first position), longest context first
         self.portion_tiles = None
         self.n_portion_tiles = 0
+        # the single-token rows as tiles of one query: int32 [n_single, 4] = (token row, 1, block-table row,
+        # position), or (token row, 0, 0, 0) for a row that pads the step
+        self.single_tiles = None
         self._tables: List[torch.Tensor] = []
         self._slots: Optional[torch.Tensor] = None
 
@@ -291,7 +294,8 @@ class Engine:
         off, sizes = {}, [("tokens", T), ("positions", T), ("token_req", T), ("logit_rows", L_rows), ("slots", R),
                           ("req_first_token", R + 1), ("req_first_position", R),
                           ("single_rows", n_single_rows if mixed else 0),
-                          ("portion_rows", T - n_single_rows if mixed else 0), ("tiles", 4 * n_tiles)]
+                          ("portion_rows", T - n_single_rows if mixed else 0), ("tiles", 4 * n_tiles),
+                          ("single_tiles", 4 * n_single_rows)]
         sizes += [(f"table{g}", R * W) for g in range(len(mgr.kv_groups))]
         total = 0
         for name, n in sizes:
@@ -308,6 +312,7 @@ class Engine:
             single_rows: List[int] = []
             portion_rows: List[int] = []
             tiles: List[tuple] = []
+            single_tiles: List[tuple] = []
             for r, e in enumerate(entries):
                 n = len(e.tokens)
                 start = mgr.reserve(e.rid, n)
@@ -323,6 +328,8 @@ class Engine:
                     (single_rows if n == 1 else portion_rows).extend(range(t0, t0 + span[r]))
                 if n > 1:
                     tiles.extend((t0 + a, min(TQ, n - a), r, start + a) for a in range(0, n, TQ))
+                else:
+                    single_tiles.append((t0, 1, r, start))
                 ctx.spans.append(RequestSpan(e.rid, slot, t0, n, start))
                 ctx.max_q_len = max(ctx.max_q_len, n)
                 t0 += span[r]
@@ -333,6 +340,7 @@ class Engine:
                 h[off["req_first_position"] + r] = 0
                 if mixed:
                     single_rows.append(t0)
+                single_tiles.append((t0, 0, 0, 0))
                 t0 += 1
             h[off["req_first_token"] + R] = T
             if L_rows:
@@ -344,6 +352,9 @@ class Engine:
             if n_tiles:
                 tiles.sort(key=lambda t: -(t[3] + t[1]))     # tiles with the most keys start first
                 h[off["tiles"]: off["tiles"] + 4 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
+            if n_single_rows:
+                h[off["single_tiles"]: off["single_tiles"] + 4 * n_single_rows] = \
+                    np.asarray(single_tiles, dtype=np.int32).reshape(-1)
             rids = [e.rid for e in entries]
             for g in range(len(mgr.kv_groups)):
                 o = off[f"table{g}"]
@@ -364,6 +375,8 @@ class Engine:
                 ctx.portion_rows = view("portion_rows", T - n_single_rows)
             if n_tiles:
                 ctx.portion_tiles, ctx.n_portion_tiles = view("tiles", 4 * n_tiles), n_tiles
+            if n_single_rows:
+                ctx.single_tiles = view("single_tiles", 4 * n_single_rows)
             ctx._tables = [view(f"table{g}", R * W).view(R, W) for g in range(len(mgr.kv_groups))]
             logits = self._run(ctx, (T, R, L_rows, n_single_rows, n_tiles, ctx.stream, dev.data_ptr()))
         except BaseException:

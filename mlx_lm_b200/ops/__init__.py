@@ -517,6 +517,42 @@ def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out,
           _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream)
 
 
+_ROWS_ARGS = [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+
+
+def attention_rows_supported(dtype, head_dim: int) -> bool:
+    """Whether single-token rows can run on the tensor-core kernel (else: ``attention_decode``)."""
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+
+
+_sm_count = None
+
+
+def sm_count() -> int:
+    global _sm_count
+    if _sm_count is None:
+        _sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+    return _sm_count
+
+
+def attention_rows(q, tiles, n_rows: int, block_table, k_pool, v_pool, out, n_heads: int, scale: float, window: int,
+                   status, stream, ksplit: int = 0) -> None:
+    """Attention of rows with a single query each (decode steps) on tensor cores (bfloat16,
+    csrc/attention_prefill.cu): ``tiles`` is an int32 device tensor ``[n_rows, 4]`` = (token row, 1, block-table
+    row, position), or (token row, 0, 0, 0) for a padding row.  ``ksplit``: warps that share a row's keys
+    (default: 4 while there are no more (row, head) pairs than SMs, else 2, so that several CTAs fit an SM)."""
+    n_pages, Hkv, page, Dh = _attn_shapes(q, out, k_pool, n_heads, "attention_rows")
+    _need(tiles, torch.int32, "attention_rows tiles")
+    if tiles.numel() < 4 * n_rows:
+        raise KernelError(f"attention_rows: {tiles.numel()} integers for {n_rows} rows")
+    if not ksplit:
+        ksplit = 4 if n_rows * n_heads <= sm_count() else 2
+    _call("attention_prefill", "mlxb_attention_rows", _ROWS_ARGS, _p(q), _rows(q, "attention q"), _p(tiles), n_rows,
+          ksplit, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
+          _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream)
+
+
 _DEC_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
              c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
              c_void_p]

@@ -83,10 +83,15 @@ class Attention(Mixer):
         return self.out.forward(ctx, o, residual, residual=residual)
 
     def attend(self, ctx, q, cache, o) -> None:
-        """Rows of requests that bring one token go to the split-key kernel, the rest to the kernel for
-        portions; both write their rows of ``o``."""
+        """Rows of requests that bring one token go to a kernel for single queries (on tensor cores in bfloat16
+        for head sizes that are multiples of 16 up to 128, else the split-key kernel on the CUDA cores), the
+        rest to the kernel for portions; all write their rows of ``o``."""
         window = self.window or 0
-        if ctx.n_single:
+        single_tiles = getattr(ctx, "single_tiles", None)
+        if ctx.n_single and single_tiles is not None and ops.attention_rows_supported(q.dtype, self.head_dim):
+            ops.attention_rows(q, single_tiles, ctx.n_single, cache.block_table, cache.k, cache.v, o, self.n_heads,
+                               self.scale, window, ctx.status, ctx.stream)
+        elif ctx.n_single:
             scratch = ctx.ws.flat("attn_partial", ops.attention_decode_scratch(
                 ctx.n_single, self.n_heads, self.head_dim, ctx.max_len), torch.float32)
             counters = ctx.ws.flat("attn_tickets", ctx.n_single * self.n_heads, torch.int32)
