@@ -24,12 +24,8 @@
 // (Heads of 64 in tiles of 128 queries run on the tcgen05 kernel of attention_prefill_tc.cu instead; this one
 // serves every other head size that is a multiple of 16, and tiles of 64.)
 //
-// Single-token rows (decode steps) are tiles of one query: QW = 1, so a "group" is one warp that gathers and
-// multiplies key blocks of its own, and KSPLIT warps share a row's keys (block index modulo KSPLIT) and merge at
-// the end.  Fifteen of the sixteen query rows of every product are zeros, which costs nothing that matters: the
-// kernel is bound by reading keys and values, and per key it issues a tenth of the instructions of a kernel that
-// multiplies on the CUDA cores (one 16-byte copy per 8 elements and a handful of tensor-core instructions per
-// 64 keys, no unpacking, no shuffles per key).
+// Single-token rows (decode steps) have a kernel of their own below (attention_rows_kernel): one query per
+// (row, head), the CTA's warps share each key block by keys instead of by queries.
 //
 // A tile's keys before its first query are older than this step, so the first block of each group is asked for
 // before the wait for the previous kernel if it lies wholly before that query; queries, and the blocks that hold
@@ -395,31 +391,247 @@ MLXB_EXPORT int mlxb_attention_prefill(const void* q, int ldq, const int* tiles,
 #undef GO
 }
 
-// Rows with one query each (decode steps) as tiles of one query: tiles as above with 1 (or, for a padding row, 0)
-// queries.  ksplit: warps that share a row's key blocks, 2, 4 or 8; more warps shorten the chain of blocks a warp
-// walks, fewer leave room for several CTAs per SM.  A row's result depends on ksplit by rounding only.
-MLXB_EXPORT int mlxb_attention_rows(const void* q, int ldq, const int* tiles, int n_tiles, int ksplit,
-                                    const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
-                                    int Dh, int window, float scale, const void* k_pool, const void* v_pool, void* out,
-                                    int ldo, int* status, cudaStream_t stream) {
+
+// ---------------------------------------------------------------------------------------------------------------
+// Single-token rows (decode steps): one query per (row, head).
+//
+// One CTA of RW warps handles (row, query head) and walks the row's keys in blocks of 64 positions, gathered
+// through the block table with 16-byte cp.async into a ring of RS shared-memory stages by all its threads (so the
+// page lookups are shared, and RS - 1 blocks are in flight while one is multiplied).  Inside a block the warps
+// split the KEYS: warp w takes keys 64/RW * w .. of every block, multiplies them with the query on the tensor cores
+// (mma.sync m16n8k16 with the query in row 0 of the 16-row operand; the other rows are zeros and cost nothing that
+// matters, the kernel is bound by reading keys and values), keeps a running maximum, sum and output of its own,
+// and the warps' results are merged in warp order at the end.  Per key this issues a tenth of the instructions
+// of a kernel that multiplies on the CUDA cores: no unpacking of bfloat16, no shuffles and no exponential per
+// thread and key.  The order in which a row's keys are added depends only on its position.
+// Blocks that lie wholly before the row's position hold keys older than this step and are asked for before the
+// wait for the kernel that wrote this step's query, key and value.
+// The launcher sends only steps of many rows here ((row, head) pairs several times the number of SMs): with few
+// pairs a row's keys would have to be shared among CTAs, and the split-key kernel of attention.cu, which does
+// that, is the faster one there (measured; so is a variant of this kernel that shares a row among a thread-block
+// cluster and merges through distributed shared memory).
+template <int DH, int RW, int RS>
+__global__ void __launch_bounds__(RW * 32)
+attention_rows_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int4* __restrict__ tiles,
+                      const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
+                      int window, float scale_log2e, const __nv_bfloat16* __restrict__ k_pool,
+                      const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, int ldo,
+                      int* __restrict__ status) {
+  constexpr int THREADS = RW * 32;
+  constexpr int STRIDE = DH + 8;              // elements per shared-memory row (16 bytes of padding)
+  constexpr int KS = DH / 16;                 // k steps of q K^T
+  constexpr int NT = DH / 8;                  // n tiles of the output
+  constexpr int CHUNKS = DH / 8;              // 16-byte chunks per key row
+  constexpr int WK = BKV / RW;                // keys of a block a warp takes: 16 (4 warps) or 32 (2 warps)
+  constexpr int NIT = (BKV * CHUNKS + THREADS - 1) / THREADS;   // chunks of K (and of V) a thread copies per block
+  static_assert(WK % 16 == 0, "a warp takes whole 16-key steps");
+  extern __shared__ __align__(16) uint8_t smem_raw[];
+  __nv_bfloat16* sk = reinterpret_cast<__nv_bfloat16*>(smem_raw);    // [RS][BKV][STRIDE]
+  __nv_bfloat16* sv = sk + RS * BKV * STRIDE;                        // [RS][BKV][STRIDE]
+
+  pdl_trigger();
+  const int4 tile = tiles[blockIdx.x];        // the step's inputs: no kernel writes them
+  const int row = tile.x, req = tile.z, pos = tile.w;
+  if (tile.y <= 0) return;                    // a row that pads the step
+  const int h = blockIdx.y, hk = h / (Hq / Hkv);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, qd = lane & 3;
+  const int* bt = block_table + (size_t)req * max_pages;
+  const int shift = __ffs(page) - 1;
+  const int first_key = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  const int kb_lo = first_key / BKV, kb_hi = pos / BKV;
+  const int n_blocks = kb_hi - kb_lo + 1;
+  const size_t page_elems = (size_t)Hkv * page * DH;
+
+  auto load_block = [&](int kb, int st) {     // gather block kb into stage st; always one commit group
+    if (kb <= kb_hi) {
+      __nv_bfloat16* dk = sk + st * BKV * STRIDE;
+      __nv_bfloat16* dv = sv + st * BKV * STRIDE;
+#pragma unroll
+      for (int j = 0; j < NIT; ++j) {
+        const int i = threadIdx.x + j * THREADS;
+        if (i >= BKV * CHUNKS) break;
+        const int kr = i / CHUNKS, ch = i - kr * CHUNKS;
+        const int key = kb * BKV + kr;
+        bool ok = key <= pos && key >= first_key;
+        size_t off = 0;
+        if (ok) {
+          const int lp = key >> shift;
+          const int pg = lp < max_pages ? bt[lp] : -1;
+          if (pg < 0 || pg >= n_pages) {
+            atomicOr(status, pg < 0 ? MLXB_ST_POSITION_RANGE : MLXB_ST_PAGE_RANGE);
+            ok = false;
+          } else {
+            off = (size_t)pg * page_elems + (size_t)((hk * page + (key & (page - 1))) * DH + ch * 8);
+          }
+        }
+        cp_async16(dk + kr * STRIDE + ch * 8, k_pool + off, ok);
+        cp_async16(dv + kr * STRIDE + ch * 8, v_pool + off, ok);
+      }
+    }
+    cp_async_commit();
+  };
+
+  // the first RS - 1 blocks: those that are older than this step before the wait, the others after it
+  int issued = 0;
+  while (issued < RS - 1 && issued < n_blocks && (kb_lo + issued + 1) * BKV <= pos) {
+    load_block(kb_lo + issued, issued);
+    ++issued;
+  }
+  pdl_wait();
+  q = after_wait(q);
+  k_pool = after_wait(k_pool);
+  v_pool = after_wait(v_pool);
+  for (; issued < RS - 1; ++issued) load_block(kb_lo + issued, issued);
+
+  // the query in row 0 of the A operand (lanes g == 0), zeros in the other rows
+  unsigned qa[KS][4];
+  {
+    const __nv_bfloat16* qr = q + (size_t)row * ldq + h * DH;
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks) {
+      const int d = ks * 16 + 2 * qd;
+      qa[ks][0] = g == 0 ? *reinterpret_cast<const unsigned*>(qr + d) : 0u;
+      qa[ks][2] = g == 0 ? *reinterpret_cast<const unsigned*>(qr + d + 8) : 0u;
+      qa[ks][1] = qa[ks][3] = 0u;
+    }
+  }
+  float o[NT][2];      // row g of the product: only g == 0 is the query's
+#pragma unroll
+  for (int i = 0; i < NT; ++i) o[i][0] = o[i][1] = 0.f;
+  float m = -INFINITY, l = 0.f;   // running maximum in units of the exponent, this lane's share of the running sum
+  const int mi = lane >> 3, mr = lane & 7;   // ldmatrix: which 8x8 matrix this lane addresses, and its row
+
+  for (int i = 0; i < n_blocks; ++i) {
+    const int kb = kb_lo + i, st = i % RS;
+    cp_async_wait<RS - 2>();      // block i has landed (a group per block, RS - 1 of them issued ahead)
+    __syncthreads();              // ... for every thread's copies; and everyone is done with block i - 1
+    load_block(kb + RS - 1, (i + RS - 1) % RS);     // into the stage block i - 1 used
+    const int key_w = kb * BKV + warp * WK;         // this warp's first key of the block
+    if (key_w <= pos && key_w + WK > first_key) {
+      const __nv_bfloat16* bk = sk + (st * BKV + warp * WK) * STRIDE;
+      const __nv_bfloat16* bv = sv + (st * BKV + warp * WK) * STRIDE;
+      float s[WK / 8][4];
+#pragma unroll
+      for (int t = 0; t < WK / 8; ++t)
+#pragma unroll
+        for (int c = 0; c < 4; ++c) s[t][c] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KS; ++ks) {
+#pragma unroll
+        for (int np = 0; np < WK / 16; ++np) {   // pairs of 8-key tiles
+          unsigned b[4];
+          ldmatrix_x4(b, bk + (np * 16 + (mi >> 1) * 8 + mr) * STRIDE + ks * 16 + (mi & 1) * 8);
+          mma_bf16(s[2 * np], qa[ks], b[0], b[1]);
+          mma_bf16(s[2 * np + 1], qa[ks], b[2], b[3]);
+        }
+      }
+      // mask and maximum of row g (the query's row where g == 0; the other rows are rows of zeros)
+      const bool open = key_w + WK - 1 <= pos && key_w >= first_key;
+      float mx = -INFINITY;
+#pragma unroll
+      for (int t = 0; t < WK / 8; ++t)
+#pragma unroll
+        for (int c = 0; c < 2; ++c) {
+          const int key = key_w + t * 8 + 2 * qd + c;
+          if (!open && !(key <= pos && key >= first_key)) s[t][c] = -INFINITY;
+          mx = fmaxf(mx, s[t][c]);
+        }
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+      const float mn = fmaxf(m, mx * scale_log2e);      // scale > 0
+      const float base = mn == -INFINITY ? 0.f : mn;
+      const float corr = fast_exp2(m - base);           // 2^-inf = 0
+      m = mn;
+      float sum = 0.f;
+      unsigned pa[WK / 16][4];
+#pragma unroll
+      for (int t = 0; t < WK / 8; ++t) {
+        const float e0 = fast_exp2(fmaf(s[t][0], scale_log2e, -base)), e1 = fast_exp2(fmaf(s[t][1], scale_log2e, -base));
+        sum += e0 + e1;
+        pa[t >> 1][(t & 1) * 2] = pack_bf16(e0, e1);
+        pa[t >> 1][(t & 1) * 2 + 1] = 0u;
+      }
+      l = l * corr + sum;
+#pragma unroll
+      for (int t = 0; t < NT; ++t) { o[t][0] *= corr; o[t][1] *= corr; }
+#pragma unroll
+      for (int kk = 0; kk < WK / 16; ++kk) {
+#pragma unroll
+        for (int dp = 0; dp < NT / 2; ++dp) {   // pairs of output-dim tiles
+          unsigned b[4];
+          ldmatrix_x4_trans(b, bv + (kk * 16 + (mi & 1) * 8 + mr) * STRIDE + dp * 16 + (mi >> 1) * 8);
+          float acc0[4] = {o[2 * dp][0], o[2 * dp][1], 0.f, 0.f}, acc1[4] = {o[2 * dp + 1][0], o[2 * dp + 1][1], 0.f, 0.f};
+          mma_bf16(acc0, pa[kk], b[0], b[1]);
+          mma_bf16(acc1, pa[kk], b[2], b[3]);
+          o[2 * dp][0] = acc0[0]; o[2 * dp][1] = acc0[1];
+          o[2 * dp + 1][0] = acc1[0]; o[2 * dp + 1][1] = acc1[1];
+        }
+      }
+    }
+  }
+  cp_async_wait<0>();
+  __syncthreads();      // the stages are free: they carry the warps' results now
+
+  // merge the warps in warp order: lanes g == 0 of warp w hold (m, l share, o) of the query for their dims
+  l += __shfl_xor_sync(0xffffffffu, l, 1);
+  l += __shfl_xor_sync(0xffffffffu, l, 2);
+  float* xch = reinterpret_cast<float*>(smem_raw);     // [RW][2 + DH]
+  if (g == 0) {
+    float* dst = xch + warp * (2 + DH);
+    if (qd == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+    for (int t = 0; t < NT; ++t) { dst[2 + t * 8 + 2 * qd] = o[t][0]; dst[2 + t * 8 + 2 * qd + 1] = o[t][1]; }
+  }
+  __syncthreads();
+  float M = -INFINITY;
+#pragma unroll
+  for (int w = 0; w < RW; ++w) M = fmaxf(M, xch[w * (2 + DH)]);
+  const float base = M == -INFINITY ? 0.f : M;
+  float L = 0.f;
+#pragma unroll
+  for (int w = 0; w < RW; ++w) L = fmaf(xch[w * (2 + DH) + 1], fast_exp2(xch[w * (2 + DH)] - base), L);
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  for (int d = threadIdx.x; d < DH; d += THREADS) {
+    float acc = 0.f;
+#pragma unroll
+    for (int w = 0; w < RW; ++w) acc = fmaf(xch[w * (2 + DH) + 2 + d], fast_exp2(xch[w * (2 + DH)] - base), acc);
+    out[(size_t)row * ldo + h * DH + d] = __float2bfloat16_rn(acc * inv);
+  }
+}
+
+template <int DH, int RW, int RS>
+static int launch_rows(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table, int max_pages,
+                       int n_pages, int page, int Hq, int Hkv, int window, float scale, const void* k_pool,
+                       const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream) {
+  const size_t smem = (size_t)RS * 2 * BKV * (DH + 8) * sizeof(__nv_bfloat16);    // (the merge needs far less)
+  auto kern = attention_rows_kernel<DH, RW, RS>;
+  static bool raised = false;
+  if (smem > 48 * 1024 && !raised) {
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    raised = true;
+  }
+  launch_pdl(kern, dim3(n_tiles, Hq), dim3(RW * 32), smem, stream, (const __nv_bfloat16*)q, ldq, (const int4*)tiles,
+             block_table, max_pages, n_pages, page, Hq, Hkv, window, scale * 1.4426950408889634f,
+             (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, ldo, status);
+  return mlxb_check_launch("attention (single rows)");
+}
+
+// Rows with one query each (decode steps): tiles int32 [n_tiles][4] = (token row, 1, block-table row, position),
+// or (token row, 0, 0, 0) for a row that pads the step and is left alone.  bfloat16; Dh a multiple of 16 up to 128.
+MLXB_EXPORT int mlxb_attention_rows(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table,
+                                    int max_pages, int n_pages, int page, int Hq, int Hkv, int Dh, int window,
+                                    float scale, const void* k_pool, const void* v_pool, void* out, int ldo,
+                                    int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (page <= 0 || (page & (page - 1))) return mlxb_fail(MLXB_BAD_ARG, "attention (single rows): page size %d", page);
   if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || Hq > 65535)
     return mlxb_fail(MLXB_BAD_ARG, "attention (single rows): %d query heads over %d key/value heads", Hq, Hkv);
   if ((ldq & 1) || (ldo & 1) || ((uintptr_t)q & 3) || ((uintptr_t)out & 3) || ((uintptr_t)tiles & 15))
     return mlxb_fail(MLXB_BAD_ARG, "attention (single rows): rows must be 4-byte aligned, the tile list 16-byte aligned");
-  if (ksplit != 2 && ksplit != 4 && ksplit != 8)
-    return mlxb_fail(MLXB_BAD_ARG, "attention (single rows): %d warps per row (2, 4 or 8)", ksplit);
 #define GO(D)                                                                                                         \
   case D:                                                                                                             \
-    if (ksplit == 2)                                                                                                  \
-      return launch<D, 1, 2>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,   \
-                             k_pool, v_pool, out, ldo, status, stream);                                               \
-    if (ksplit == 4 || (size_t)8 * 4 * BKV * (D + 8) * 2 > 200 * 1024)                                                \
-      return launch<D, 1, 4>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,   \
-                             k_pool, v_pool, out, ldo, status, stream);                                               \
-    return launch<D, 1, 8>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,     \
-                           k_pool, v_pool, out, ldo, status, stream)
+    return launch_rows<D, 4, (D <= 64 ? 3 : 2)>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq,    \
+                                                Hkv, window, scale, k_pool, v_pool, out, ldo, status, stream)
   switch (Dh) {
     GO(16); GO(32); GO(48); GO(64); GO(80); GO(96); GO(112); GO(128);
     default:

@@ -20,6 +20,8 @@ import torch
 
 from . import build
 
+import os as _os
+
 F32, BF16 = 0, 1
 
 
@@ -481,8 +483,6 @@ def attention_generic(q, positions, token_req, block_table, k_pool, v_pool, out,
 _PRE_ARGS = [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
 
-import os as _os
-
 PREFILL_TILE = int(_os.environ.get("MLXB_PREFILL_TILE", "128"))   # queries per CTA of the attention kernels for portions
 PREFILL_TC = _os.environ.get("MLXB_PREFILL_TC", "1") != "0"         # heads of 64 in tiles of 128 on the tcgen05 kernel
 
@@ -517,13 +517,20 @@ def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out,
           _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream)
 
 
-_ROWS_ARGS = [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
+_ROWS_ARGS = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
               c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
 
 
-def attention_rows_supported(dtype, head_dim: int) -> bool:
-    """Whether single-token rows can run on the tensor-core kernel (else: ``attention_decode``)."""
-    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+# (row, head) pairs from which single-token rows run on the tensor-core kernel: about seven times the number
+# of SMs.  Below that the split-key kernel on the CUDA cores is as fast or faster inside a step (GPT-2 medium
+# on a B200, 512-token contexts: 16 rows 0.88 against 0.96 ms a step, 32 rows 1.37 both, 64 rows 2.24 against 2.07).
+ROWS_MIN_PAIRS = int(_os.environ.get("MLXB_ROWS_MIN_PAIRS", "1024"))
+
+
+def attention_rows_supported(dtype, head_dim: int, n_rows: int = 1 << 30, n_heads: int = 1) -> bool:
+    """Whether these single-token rows run on the tensor-core kernel (else: ``attention_decode``)."""
+    return (dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+            and n_rows * n_heads >= ROWS_MIN_PAIRS)
 
 
 _sm_count = None
@@ -537,19 +544,16 @@ def sm_count() -> int:
 
 
 def attention_rows(q, tiles, n_rows: int, block_table, k_pool, v_pool, out, n_heads: int, scale: float, window: int,
-                   status, stream, ksplit: int = 0) -> None:
+                   status, stream) -> None:
     """Attention of rows with a single query each (decode steps) on tensor cores (bfloat16,
     csrc/attention_prefill.cu): ``tiles`` is an int32 device tensor ``[n_rows, 4]`` = (token row, 1, block-table
-    row, position), or (token row, 0, 0, 0) for a padding row.  ``ksplit``: warps that share a row's keys
-    (default: 4 while there are no more (row, head) pairs than SMs, else 2, so that several CTAs fit an SM)."""
+    row, position), or (token row, 0, 0, 0) for a padding row."""
     n_pages, Hkv, page, Dh = _attn_shapes(q, out, k_pool, n_heads, "attention_rows")
     _need(tiles, torch.int32, "attention_rows tiles")
     if tiles.numel() < 4 * n_rows:
         raise KernelError(f"attention_rows: {tiles.numel()} integers for {n_rows} rows")
-    if not ksplit:
-        ksplit = 4 if n_rows * n_heads <= sm_count() else 2
     _call("attention_prefill", "mlxb_attention_rows", _ROWS_ARGS, _p(q), _rows(q, "attention q"), _p(tiles), n_rows,
-          ksplit, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
+          _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
           _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream)
 
 

@@ -88,7 +88,8 @@ class Attention(Mixer):
         rest to the kernel for portions; all write their rows of ``o``."""
         window = self.window or 0
         single_tiles = getattr(ctx, "single_tiles", None)
-        if ctx.n_single and single_tiles is not None and ops.attention_rows_supported(q.dtype, self.head_dim):
+        if (ctx.n_single and single_tiles is not None
+                and ops.attention_rows_supported(q.dtype, self.head_dim, ctx.n_single, self.n_heads)):
             ops.attention_rows(q, single_tiles, ctx.n_single, cache.block_table, cache.k, cache.v, o, self.n_heads,
                                self.scale, window, ctx.status, ctx.stream)
         elif ctx.n_single:

@@ -144,14 +144,15 @@ def max_live_tokens(trace, round_to=64):
     return worst
 
 
-def run_trace(model_dir, trace, dtype, out_dir, max_tokens=None, extra=(), timeout=600):
+def run_trace(model_dir, trace, dtype, out_dir, max_tokens=None, extra=(), timeout=600, env=None):
     """Run bin/trace_run over the trace; returns {(rid, position): float32 row}."""
     os.makedirs(out_dir, exist_ok=True)
     if max_tokens is None:
         max_tokens = max_live_tokens(trace)
     cmd = [sys.executable, TRACE_RUN, "--model", model_dir, "--dtype", dtype, "--out", out_dir, "--max-tokens",
            str(max_tokens), *extra]
-    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True)
+    proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True,
+                            env=dict(os.environ, **env) if env else None)
     try:
         for s in trace.steps:
             proc.stdin.write(json.dumps(s) + "\n")

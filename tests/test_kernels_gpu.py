@@ -470,14 +470,13 @@ def test_attention_single_token_rows(ops, dtype, Hq, Hkv, Dh, page, window, chun
     assert int(counters.abs().max().item()) == 0        # the ticket counters are left at zero
 
 
-@pytest.mark.parametrize("ksplit", [2, 4, 8])
 @pytest.mark.parametrize("Hq,Hkv,Dh,page,window", [(4, 4, 16, 16, 0), (3, 3, 32, 16, 0), (6, 2, 48, 32, 0),
                                                     (5, 1, 80, 64, 0), (2, 2, 128, 16, 40), (8, 4, 64, 16, 17),
                                                     (16, 16, 64, 16, 0), (25, 25, 64, 8, 0)])
-def test_attention_single_token_rows_on_tensor_cores(ops, Hq, Hkv, Dh, page, window, ksplit):
+def test_attention_single_token_rows_on_tensor_cores(ops, Hq, Hkv, Dh, page, window):
     """Single-token rows as tiles of one query on the tensor-core kernel: the single-token requests of a mixed
     step (contexts that end inside a block, on a block's edge and in its first key), padding rows that must
-    write nothing, every number of warps per row, against the plain statement."""
+    write nothing, against the plain statement."""
     lens, new = [0, 37, 130, 64, 511, 255, 63, 127, 128], [1, 1, 35, 1, 1, 1, 1, 1, 1]
     c = paged_case(torch.bfloat16, lens=lens, new=new, Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=Dh + page + 2)
     dev = {k: (v.cuda() if torch.is_tensor(v) else v) for k, v in c.items()}
@@ -493,7 +492,7 @@ def test_attention_single_token_rows_on_tensor_cores(ops, Hq, Hkv, Dh, page, win
     tiles = torch.tensor(single[:3] + padding[:1] + single[3:] + padding[1:], dtype=torch.int32).cuda()
     out = torch.zeros(c["T"], qw, dtype=torch.bfloat16, device="cuda")
     ops.attention_rows(q, tiles, tiles.shape[0], dev["bt"], dev["k_pool"], dev["v_pool"], out, Hq, scale, window,
-                       status, stream(), ksplit=ksplit)
+                       status, stream())
     assert int(status.item()) == 0
     rows = [t[0] for t in single]
     assert rel_err(out[rows], ref[rows]) <= 8e-3

@@ -68,14 +68,22 @@ def test_replay_with_other_page_sizes(case, page_size, dtype, tmp_path):
     replay_and_compare(case, dtype, tmp_path, page_size=page_size)
 
 
-def replay_and_compare(case, dtype, tmp_path, page_size):
+@pytest.mark.parametrize("case", ["C-sharp", "A", "B-sharp"])
+def test_replay_with_single_token_rows_on_tensor_cores(case, tmp_path):
+    """Steps of few rows send their single-token rows to the split-key kernel on the CUDA cores; only steps of
+    very many rows use the tensor-core kernel for them.  Here it is made to take every single-token row
+    (MLXB_ROWS_MIN_PAIRS=0), so that the cuttings, page reuse included, run through it too."""
+    replay_and_compare(case, "bfloat16", tmp_path, page_size=16, env={"MLXB_ROWS_MIN_PAIRS": "0"})
+
+
+def replay_and_compare(case, dtype, tmp_path, page_size, env=None):
     config, seed, sharp, lengths, tol_bf16 = CASES[case]
     limit = TOL_F32 if dtype == "float32" else tol_bf16
     weights = make_model_dir(str(tmp_path / "model"), config, seed, peaky=sharp)
     reqs, tr = build_trace(lengths, config["vocab_size"], seed)
     # the pool holds exactly what the busiest moment needs, so freed pages are taken again
     got = run_trace(str(tmp_path / "model"), tr, dtype, str(tmp_path / "out"), max_tokens=max_live_tokens(tr),
-                    extra=["--page-size", str(page_size)])
+                    extra=["--page-size", str(page_size)], env=env)
     ref = {name: plain.logits(toks, weights, config).numpy() for name, toks in reqs.items()}
     worst, worst_key = 0.0, None
     n_rows = 0
