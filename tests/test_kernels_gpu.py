@@ -91,7 +91,8 @@ def test_row_stats(ops, R_, D, shift):
 
 @pytest.mark.parametrize("M,N,K,shift", [(1, 200, 96, 0.0), (7, 1000, 320, 1.5), (16, 72, 1600, 40.0), (33, 200, 96, -2.0),
                                          (8, 8400, 1024, 1.5), (13, 9000, 2056, -3.0),      # very wide outputs
-                                         (64, 1000, 320, 0.5), (200, 264, 96, 1.5), (130, 1000, 1600, 40.0)])
+                                         (64, 1000, 320, 0.5), (200, 264, 96, 1.5), (130, 1000, 1600, 40.0), (2048, 3072, 1024, 2.0),
+                                         (300, 520, 1608, -1.0)])
 def test_linear_with_folded_norm(ops, M, N, K, shift):
     """LayerNorm folded into the weights (parts.linear.Linear.fold_norm): the few-rows kernel (statistics from its
     own fragments) and the tcgen05 kernel (statistics from row_stats) against LayerNorm followed by the linear
