@@ -48,24 +48,8 @@ EPI_GELU_NEW = ACTIVATION_CODES["gelu_new"]
 _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 # kernel sources that only a bfloat16 run launches from: a float32 run neither compiles nor loads them
-BF16_ONLY_LIBS = frozenset({"gemm_smallm", "gemm_smallm_fold", "gemm_tcgen05", "gemm_tcgen05_cluster",
-                            "attention_prefill", "attention_prefill_tc"})
-
-
-def tc_linear_libs():
-    """The libraries of the tcgen05 linear kernel: the plain one and, where its source is present, the one that
-    runs thread-block clusters with multicast copies (csrc/gemm_tcgen05_cluster.cu, a file that is left out
-    of runs on more than one GPU; ``MLXB_TC_CLUSTER=0`` leaves it out too)."""
-    libs = ["gemm_tcgen05"]
-    if _os.environ.get("MLXB_TC_CLUSTER", "1") != "0" and _os.path.exists(_os.path.join(build.CSRC, "gemm_tcgen05_cluster.cu")):
-        libs.append("gemm_tcgen05_cluster")
-    return libs
-
-
-def _tc_lib(n_rows: int) -> str:
-    """Which of them takes a product of ``n_rows`` rows: clusters pair two row tiles of 128."""
-    libs = tc_linear_libs()
-    return libs[-1] if n_rows > 128 else libs[0]
+BF16_ONLY_LIBS = frozenset({"gemm_smallm", "gemm_smallm_fold", "gemm_tcgen05", "attention_prefill",
+                            "attention_prefill_tc"})
 
 # status word bits set by kernels (csrc/common.cuh)
 ST_TOKEN_RANGE, ST_POSITION_RANGE, ST_PAGE_RANGE, ST_WAIT_TIMEOUT = 1, 2, 4, 8
@@ -387,10 +371,10 @@ def linear_tensor_cores(x, w, bias, out, status, stream, epilogue: int = EPI_NON
         _need(stats, torch.float32, "linear row statistics")
         if colsum.numel() != N or stats.shape != (M, 2) or not stats.is_contiguous():
             raise KernelError(f"linear: {colsum.numel()} column sums, statistics {tuple(stats.shape)} for {M} x {N}")
-        _call(_tc_lib(M), "mlxb_linear_tcgen05_fold", _TC_FOLD_ARGS, int(out.dtype == torch.float32), _p(x), _p(w),
+        _call("gemm_tcgen05", "mlxb_linear_tcgen05_fold", _TC_FOLD_ARGS, int(out.dtype == torch.float32), _p(x), _p(w),
               _p(bias), _p(residual), _p(out), M, N, K, lda, ldc, epilogue, _p(status), _p(colsum), _p(stats), stream)
         return
-    _call(_tc_lib(M), "mlxb_linear_tcgen05", _TC_ARGS, int(out.dtype == torch.float32), _p(x), _p(w), _p(bias),
+    _call("gemm_tcgen05", "mlxb_linear_tcgen05", _TC_ARGS, int(out.dtype == torch.float32), _p(x), _p(w), _p(bias),
           _p(residual), _p(out), M, N, K, lda, ldc, epilogue, _p(status), stream)
 
 
@@ -427,7 +411,7 @@ def linear_qkv_to_cache(x, w, bias, out, positions, token_req, block_table, k_po
         _need(colsum, torch.float32, "linear column sums")
         if not torch.is_tensor(stats) or stats.dtype != torch.float32 or stats.shape != (M, 2) or not stats.is_contiguous():
             raise KernelError(f"linear (q|k|v): more than {SMALL_M} rows need float32 row statistics [{M}, 2]")
-        _call(_tc_lib(M), "mlxb_linear_tcgen05_qkv_fold", _QKV_TC_FOLD_ARGS, _p(x), _p(w), _p(bias), _p(out), M, N, K,
+        _call("gemm_tcgen05", "mlxb_linear_tcgen05_qkv_fold", _QKV_TC_FOLD_ARGS, _p(x), _p(w), _p(bias), _p(out), M, N, K,
               _rows(x, "linear x"), _rows(out, "linear out"), _p(positions), _p(token_req), _p(block_table),
               block_table.shape[1], n_pages, page, Hkv, Dh, q_width, _p(k_pool), _p(v_pool), _p(status), _p(colsum),
               _p(stats), stream)
@@ -439,7 +423,7 @@ def linear_qkv_to_cache(x, w, bias, out, positions, token_req, block_table, k_po
               block_table.shape[1], n_pages, page, Hkv, Dh, q_width, _p(k_pool), _p(v_pool), _p(status), _p(colsum), eps,
               stream)
         return
-    lib, fn = ("gemm_smallm", "mlxb_linear_smallm_qkv") if M <= SMALL_M else (_tc_lib(M), "mlxb_linear_tcgen05_qkv")
+    lib, fn = ("gemm_smallm", "mlxb_linear_smallm_qkv") if M <= SMALL_M else ("gemm_tcgen05", "mlxb_linear_tcgen05_qkv")
     _call(lib, fn, _QKV_ARGS, _p(x), _p(w), _p(bias), _p(out), M, N, K,
           _rows(x, "linear x"), _rows(out, "linear out"), _p(positions), _p(token_req), _p(block_table),
           block_table.shape[1], n_pages, page, Hkv, Dh, q_width, _p(k_pool), _p(v_pool), _p(status), stream)

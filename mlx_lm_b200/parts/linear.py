@@ -23,7 +23,7 @@ ACTIVATIONS = {None: ops.EPI_NONE, **ops.ACTIVATION_CODES}
 
 class Linear(Part):
     replayable = True
-    kernel_libs = ("gemm_simt", "gemm_smallm", "gemm_smallm_fold", *ops.tc_linear_libs())
+    kernel_libs = ("gemm_simt", "gemm_smallm", "gemm_smallm_fold", "gemm_tcgen05")
 
     def __init__(self, name: str, n_in: int, n_out: int, bias: bool = True, stored: str = "out_in",
                  weight_suffix: str = ".weight", init: Init = Init(), bias_init: Init = Init(),
