@@ -101,6 +101,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
   pdl_trigger();
   const int4 tile = tiles[blockIdx.x];      // the step's inputs: no kernel writes them
   const int row0 = tile.x, n_rows = tile.y, req = tile.z, pos0 = tile.w;
+  if (n_rows <= 0) return;                  // a tile without queries pads the list to a size seen before
   const int h = blockIdx.y, hk = h / (Hq / Hkv);
   const int warp = gtid >> 5, lane = threadIdx.x & 31, g = lane >> 2, qd = lane & 3;
   const int* bt = block_table + (size_t)req * max_pages;

@@ -144,6 +144,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   extern __shared__ uint8_t smem_raw[];
   AtSmem& sm = *reinterpret_cast<AtSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (tiles[blockIdx.x].y <= 0) return;   // a tile without queries pads the list to a size seen before: nothing to do
 
   if (threadIdx.x == 0) {
     mbar_init(&sm.q_full, 1);
@@ -401,7 +402,7 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, int cols
 
 // bfloat16, heads of 64.  q: [n_tokens, >= Hq*64] at row stride ldq (a multiple of 8, base 16-byte aligned);
 // out: [*, Hq*64] at row stride ldo (a multiple of 8, 16-byte aligned); tiles: int32 [n_tiles][4], see the kernel
-// (tiles of at most 128 queries); pools [n_pages, Hkv, page, 64], page a power of two from 8 to 128.
+// (tiles of at most 128 queries; a tile of 0 queries is skipped); pools [n_pages, Hkv, page, 64], page a power of two from 8 to 128.
 MLXB_EXPORT int mlxb_attention_prefill_tc(const void* q, int ldq, int n_tokens, const int* tiles, int n_tiles,
                                           const int* block_table, int max_pages, int n_pages, int page, int Hq,
                                           int Hkv, int Dh, int window, float scale, const void* k_pool,

@@ -285,12 +285,26 @@ class Engine:
             if n_single > 64:
                 bucket = (n_single + 63) // 64 * 64
             n_fake = bucket - n_single
-        R = n_real + n_fake
-        T = sum(span) + n_fake
         n_single_rows = n_single + n_fake
-        mixed = 0 < n_single_rows < R
         n_tiles = sum((len(e.tokens) + TQ - 1) // TQ for e in entries if len(e.tokens) > 1)
+        T_portions = sum(sp for sp, e in zip(span, entries) if len(e.tokens) > 1)
         L_rows = max(L, n_single_rows + n_portions) if rounding and L else L   # wanted rows first, then filler
+        R = n_real + n_fake
+        n_pad_rows = 0              # rows without a request behind the last portion
+        if rounding and n_portions:
+            # The same for the step as a whole, so that steps of a scheduler that cuts prompts under a budget
+            # repeat their shapes: the portions' rows together go up to a multiple of 256 (of 64 below that), the
+            # list of tiles to an even length (a multiple of 4 above 8; tiles of 0 queries are skipped by the
+            # kernels), the requests to a multiple of 4 and the wanted rows to a multiple of 8.
+            grid = 256 if T_portions > 256 else 64
+            n_pad_rows = (T_portions + grid - 1) // grid * grid - T_portions
+            step_t = 2 if n_tiles <= 8 else 4
+            n_tiles = (n_tiles + step_t - 1) // step_t * step_t
+            R = (R + 3) // 4 * 4
+            if L_rows:
+                L_rows = (L_rows + 7) // 8 * 8
+        T = sum(span) + n_fake + n_pad_rows
+        mixed = 0 < n_single_rows < n_real + n_fake
         off, sizes = {}, [("tokens", T), ("positions", T), ("token_req", T), ("logit_rows", L_rows), ("slots", R),
                           ("req_first_token", R + 1), ("req_first_position", R),
                           ("single_rows", n_single_rows if mixed else 0),
@@ -342,6 +356,12 @@ class Engine:
                     single_rows.append(t0)
                 single_tiles.append((t0, 0, 0, 0))
                 t0 += 1
+            if mixed and n_pad_rows:
+                portion_rows.extend(range(t0, t0 + n_pad_rows))        # rows without a request: every kernel skips them
+            for r in range(n_real + n_fake, R):                        # requests that only fill the tables up
+                h[off["slots"] + r] = 0
+                h[off["req_first_token"] + r] = T
+                h[off["req_first_position"] + r] = 0
             h[off["req_first_token"] + R] = T
             if L_rows:
                 rows.extend([rows[0]] * (L_rows - L))
@@ -351,6 +371,7 @@ class Engine:
                 h[off["portion_rows"]: off["portion_rows"] + T - n_single_rows] = portion_rows
             if n_tiles:
                 tiles.sort(key=lambda t: -(t[3] + t[1]))     # tiles with the most keys start first
+                tiles.extend([(0, 0, 0, 0)] * (n_tiles - len(tiles)))      # tiles of 0 queries: skipped
                 h[off["tiles"]: off["tiles"] + 4 * n_tiles] = np.asarray(tiles, dtype=np.int32).reshape(-1)
             if n_single_rows:
                 h[off["single_tiles"]: off["single_tiles"] + 4 * n_single_rows] = \
