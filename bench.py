@@ -386,6 +386,42 @@ def decode_kernels(engine, batch, mean_ctx, cfg, pk):
     return kernel_table(calls, pk, "decode", attention_bytes=kv_bytes, attention_flops=2 * kv_bytes)
 
 
+def matmul_yardstick(cfg):
+    """torch.matmul (cuBLAS) on the model's four linear shapes at 2048 and 16384 rows, timed like the kinds of
+    `kernel_table`: eight weight matrices a shape in one CUDA graph, L2 flushed before every replay, CUDA events.
+    A yardstick for the hand-written linear kernels only: the library is nowhere on the engine's path."""
+    import torch
+
+    D, I = cfg["n_embd"], cfg["n_inner"] or 4 * cfg["n_embd"]
+    shapes = {"c_attn": (3 * D, D), "attn.c_proj": (D, D), "mlp.c_fc": (I, D), "mlp.c_proj": (D, I)}
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
+    for M in (2048, 16384):
+        for name, (N, K) in shapes.items():
+            x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+            ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) for _ in range(8)]
+            out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
+            side = torch.cuda.Stream()
+            with torch.cuda.stream(side):
+                for w in ws:
+                    torch.matmul(x, w.t(), out=out)
+            side.synchronize()
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=side):
+                for w in ws:
+                    torch.matmul(x, w.t(), out=out)
+            times = []
+            for _ in range(6):
+                flush_l2(flush)
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                graph.replay()
+                e.record()
+                torch.cuda.synchronize()
+                times.append(s.elapsed_time(e) * 1e3 / len(ws))
+            us = sorted(times[1:])[2]
+            print(f"torch.matmul  {M:5d} rows  {name:12s} {N} x {K}: {us:7.2f} us  {2.0 * M * N * K / us / 1e6:7.1f} TFLOP/s")
+
+
 def run_ours(args):
     import torch
 
@@ -413,6 +449,9 @@ def run_ours(args):
 
     if args.only == "mixed":
         print(json.dumps(mixed_workload(model, engine, vocab, args)))
+        return
+    if args.only == "yardstick":
+        matmul_yardstick(cfg)
         return
     if args.only == "timeline":
         if args.prefill_prompts:
@@ -571,12 +610,13 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 24 (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "timeline", "kernels"],
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "timeline", "kernels", "yardstick"],
                     help="run just this part and print its figures (decode / prefill: short runs for profiling; "
                          "mixed: 64 requests with prompts of 16..1024 tokens through the scheduler, 256-token portions "
                          "beside decoding requests; timeline: every kernel of one step with its start and end, "
                          "from torch.profiler; kernels: each kind of kernel of a decode and a prefill step timed "
-                         "alone, with bytes, flops and the fraction of the measured peak)")
+                         "alone, with bytes, flops and the fraction of the measured peak; yardstick: torch.matmul on the "
+                         "model's linear shapes, to hold the hand-written kernels against)")
     ap.add_argument("--prefill-prompts", type=int, default=0,
                     help="with --only prefill: 1024-token prompts in the one step (default and the contract's figure: "
                          "2); with --only timeline: the timeline of such a step instead of a decode step")
