@@ -213,9 +213,12 @@ def test_linear_few_rows(ops, M, N, K):
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (65, 192, 64), (200, 320, 96), (130, 1000, 96), (257, 96, 320),
                                    (2048, 3072, 1024), (300, 1600, 6400), (1000, 50257, 64), (129, 7, 8),
                                    (512, 1024, 4096)])
-def test_linear_tensor_cores(ops, M, N, K):
+@pytest.mark.parametrize("pairs", ["single CTAs", "pairs of CTAs"])
+def test_linear_tensor_cores(ops, M, N, K, pairs, monkeypatch):
     """The tcgen05 kernel against the plain statement: tiles with ragged edges in M, N and K, many K stages,
-    both output dtypes, every epilogue, in place on the residual."""
+    both output dtypes, every epilogue, in place on the residual; once with every tile on one CTA and once with
+    every bfloat16 product of more than 128 rows on pairs of CTAs (the launcher otherwise picks by cost)."""
+    monkeypatch.setenv("MLXB_TC_PAIR", "1" if pairs == "pairs of CTAs" else "0")
     g = torch.Generator().manual_seed(M + N + K)
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).cuda()
     w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).cuda()
@@ -240,6 +243,19 @@ def test_linear_tensor_cores(ops, M, N, K):
     sub = torch.empty(n_sub, N, dtype=torch.float32, device="cuda")
     ops.linear_tensor_cores(x[M - n_sub:], w, b, sub, status, stream())
     assert torch.equal(sub, out32[M - n_sub:])
+    assert int(status.item()) == 0
+    # pairs and single CTAs add the same products in the same order
+    ops.linear_tensor_cores(x, w, b, out, status, stream())
+    monkeypatch.setenv("MLXB_TC_PAIR", "0")
+    single = torch.empty_like(out)
+    ops.linear_tensor_cores(x, w, b, single, status, stream())
+    assert torch.equal(out, single)
+    for width in ("128", "192", "256"):          # every tile width, whatever the launcher would pick
+        monkeypatch.setenv("MLXB_TC_BN", width)
+        monkeypatch.setenv("MLXB_TC_PAIR", "1" if pairs == "pairs of CTAs" else "0")
+        forced = torch.empty_like(out)
+        ops.linear_tensor_cores(x, w, b, forced, status, stream())
+        assert torch.equal(forced, single), width
     assert int(status.item()) == 0
 
 
@@ -334,9 +350,11 @@ def test_linear_qkv_to_cache(ops, Hq, Hkv, Dh, page, K):
 
 @pytest.mark.parametrize("Hq,Hkv,Dh,page,K", [(3, 3, 32, 16, 96), (6, 2, 48, 32, 288), (16, 16, 64, 16, 1024),
                                               (5, 1, 80, 16, 200)])
-def test_linear_qkv_to_cache_many_rows(ops, Hq, Hkv, Dh, page, K):
+@pytest.mark.parametrize("pairs", ["single CTAs", "pairs of CTAs"])
+def test_linear_qkv_to_cache_many_rows(ops, Hq, Hkv, Dh, page, K, pairs, monkeypatch):
     """More than 64 rows (portions of prompts): the tcgen05 kernel's epilogue does the same cache write.  Rows of
     several requests, starting in the middle of a page, with padding rows between them."""
+    monkeypatch.setenv("MLXB_TC_PAIR", "1" if pairs == "pairs of CTAs" else "0")
     lens, new = [0, 37, 130, 5], [150, 75, 1, 91]
     c = paged_case(torch.bfloat16, lens=lens, new=new, Hq=Hq, Hkv=Hkv, Dh=Dh, page=page, seed=K + 1)
     g = torch.Generator().manual_seed(K)
