@@ -386,40 +386,61 @@ def decode_kernels(engine, batch, mean_ctx, cfg, pk):
     return kernel_table(calls, pk, "decode", attention_bytes=kv_bytes, attention_flops=2 * kv_bytes)
 
 
-def matmul_yardstick(cfg):
-    """torch.matmul (cuBLAS) on the model's four linear shapes at 2048 and 16384 rows, timed like the kinds of
-    `kernel_table`: eight weight matrices a shape in one CUDA graph, L2 flushed before every replay, CUDA events.
-    A yardstick for the hand-written linear kernels only: the library is nowhere on the engine's path."""
+def matmul_yardstick(cfg, rows=(2048, 16384), variants=("library", "ours", "ours, single CTAs", "ours, pairs of CTAs"),
+                     n_weights=8, reps=6):
+    """torch.matmul (cuBLAS) and the engine's own tcgen05 linear kernel (as its launcher picks tiles, then forced to
+    single CTAs and to pairs) on the model's four linear shapes, timed like the kinds of `kernel_table`: eight weight
+    matrices a shape in one CUDA graph, L2 flushed before every replay, CUDA events; no bias, no epilogue.  The
+    library is a yardstick only: it is nowhere on the engine's path."""
     import torch
+    from mlx_lm_b200 import ops
 
     D, I = cfg["n_embd"], cfg["n_inner"] or 4 * cfg["n_embd"]
     shapes = {"c_attn": (3 * D, D), "attn.c_proj": (D, D), "mlp.c_fc": (I, D), "mlp.c_proj": (D, I)}
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
-    for M in (2048, 16384):
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    side = torch.cuda.Stream()
+    for M in rows:
         for name, (N, K) in shapes.items():
             x = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
-            ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) for _ in range(8)]
+            ws = [torch.randn(N, K, device="cuda", dtype=torch.bfloat16) for _ in range(n_weights)]
             out = torch.empty(M, N, device="cuda", dtype=torch.bfloat16)
-            side = torch.cuda.Stream()
-            with torch.cuda.stream(side):
-                for w in ws:
-                    torch.matmul(x, w.t(), out=out)
-            side.synchronize()
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=side):
-                for w in ws:
-                    torch.matmul(x, w.t(), out=out)
-            times = []
-            for _ in range(6):
-                flush_l2(flush)
-                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                s.record()
-                graph.replay()
-                e.record()
-                torch.cuda.synchronize()
-                times.append(s.elapsed_time(e) * 1e3 / len(ws))
-            us = sorted(times[1:])[2]
-            print(f"torch.matmul  {M:5d} rows  {name:12s} {N} x {K}: {us:7.2f} us  {2.0 * M * N * K / us / 1e6:7.1f} TFLOP/s")
+            line = []
+            for variant in variants:
+                os.environ.pop("MLXB_TC_PAIR", None)
+                if variant.endswith("single CTAs"):
+                    os.environ["MLXB_TC_PAIR"] = "0"
+                elif variant.endswith("pairs of CTAs"):
+                    os.environ["MLXB_TC_PAIR"] = "1"
+
+                def product(w):
+                    if variant == "library":
+                        torch.matmul(x, w.t(), out=out)
+                    else:
+                        ops.linear_tensor_cores(x, w, None, out, status, side.cuda_stream)
+
+                with torch.cuda.stream(side):
+                    for w in ws:
+                        product(w)
+                side.synchronize()
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=side):
+                    for w in ws:
+                        product(w)
+                times = []
+                for _ in range(reps):
+                    flush_l2(flush)
+                    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s.record()
+                    graph.replay()
+                    e.record()
+                    torch.cuda.synchronize()
+                    times.append(s.elapsed_time(e) * 1e3 / len(ws))
+                us = sorted(times[1:])[(len(times) - 1) // 2]
+                line.append(f"{variant} {us:.2f} us, {2.0 * M * N * K / us / 1e6:.0f} TFLOP/s")
+            os.environ.pop("MLXB_TC_PAIR", None)
+            print(f"{M:5d} rows  {name:12s} {N} x {K}:  " + ";  ".join(line), flush=True)
+    assert int(status.item()) == 0
 
 
 def run_ours(args):
@@ -451,7 +472,11 @@ def run_ours(args):
         print(json.dumps(mixed_workload(model, engine, vocab, args)))
         return
     if args.only == "yardstick":
-        matmul_yardstick(cfg)
+        if args.prefill_prompts:     # a small case for a profiler: one row count, the engine's kernel only
+            matmul_yardstick(cfg, rows=(1024 * args.prefill_prompts,), variants=("ours, single CTAs", "ours, pairs of CTAs"),
+                             n_weights=1, reps=2)
+        else:
+            matmul_yardstick(cfg)
         return
     if args.only == "timeline":
         if args.prefill_prompts:
