@@ -372,7 +372,7 @@ def decode_kernels(engine, batch, mean_ctx, cfg, pk):
     import torch
 
     from mlx_lm_b200 import ops
-    graph = engine._graphs[batch]
+    graph = engine._graphs[(batch, False)]
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):

@@ -400,7 +400,12 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
     return launch_epi<MT_, NW_, 8, TO, SCATTER, FOLD>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, kv, fold,  \
                                                       stream);                                                  \
   }
-  if (mt == 1) GO(1, 1);
+  if (mt == 1) {
+    // a vocabulary-sized output: two weight tiles per CTA halve the number of short-lived CTAs (50 257 outputs of a
+    // 1024-wide model at 8 rows: 26.6 against 36.8 microseconds; four tiles: 30.8)
+    if (tiles >= 2048) GO(1, 2);
+    GO(1, 1);
+  }
   if (mt == 2) { if (nw == 2) GO(2, 2); GO(2, 1); }
   if (nw == 4) GO(4, 4);
   if (nw == 2) GO(4, 2);

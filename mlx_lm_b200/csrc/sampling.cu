@@ -103,6 +103,12 @@ __device__ __forceinline__ void block_argmax(float& v, int& idx, float* redv, in
   idx = redi[32];
 }
 
+// What the categorical draw maximises (Gumbel-max): logit / temperature + Gumbel noise from 32 random bits.  The
+// row's logsumexp is left out: it is the same for every candidate.
+__device__ __forceinline__ float draw_value(float logit, float inv_temp, unsigned bits) {
+  return fmaf(logit, inv_temp, -logf(-logf(uniform01(bits))));
+}
+
 struct Keep {          // which vocabulary entries are still candidates
   unsigned lo_key;     // keep fkey(logit) >= lo_key
   bool xtc;            // and, if set, drop q_i > xtc_cut unless special
@@ -123,21 +129,11 @@ struct Keep {          // which vocabulary entries are still candidates
   }
 };
 
-__global__ void __launch_bounds__(1024)
-sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleParams* __restrict__ params,
-              const int* __restrict__ xtc_special, int n_special, int* __restrict__ out_token,
-              float* __restrict__ out_logprob, float* __restrict__ out_logprobs, int ldo,
-              const int* status_in, int* __restrict__ status_out) {
-  __shared__ float redf[40];
-  __shared__ int redi[40];
-  pdl_trigger();
-  pdl_wait();
-  logits = after_wait(logits);
-  const int row = blockIdx.x;
-  // The step's status word rides along with the tokens: one copy to the host brings both.
-  if (status_out && row == 0 && threadIdx.x == 0) *status_out = __ldcg(after_wait(status_in));
-  const float* lg = logits + (size_t)row * ld;
-  const SampleParams P = params[row];
+// One row by one thread block: every pass walks the whole row.
+__device__ __forceinline__ void sample_row(const float* __restrict__ lg, int V, const SampleParams& P, int row,
+                                           const int* __restrict__ xtc_special, int n_special,
+                                           int* __restrict__ out_token, float* __restrict__ out_logprob,
+                                           float* __restrict__ out_logprobs, int ldo, float* redf, int* redi) {
   const int tid = threadIdx.x, nt = blockDim.x;
 
   float bv = -INFINITY;
@@ -244,8 +240,7 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleParam
     if (!keep(i, l, lse)) continue;
     unsigned r[4];
     philox4x32_10((unsigned)i, P.position, P.request, 0u, P.seed_lo, P.seed_hi, r);
-    const float g = -logf(-logf(uniform01(r[0])));
-    const float v = (l - lse) * inv_t + g;
+    const float v = draw_value(l, inv_t, r[0]);
     if (v > bv) { bv = v; bi = i; }
   }
   block_argmax(bv, bi, redf, redi);
@@ -256,13 +251,180 @@ sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleParam
   }
 }
 
+__global__ void __launch_bounds__(1024)
+sample_kernel(const float* __restrict__ logits, int ld, int V, const SampleParams* __restrict__ params,
+              const int* __restrict__ xtc_special, int n_special, int* __restrict__ out_token,
+              float* __restrict__ out_logprob, float* __restrict__ out_logprobs, int ldo,
+              const int* status_in, int* __restrict__ status_out) {
+  __shared__ float redf[40];
+  __shared__ int redi[40];
+  pdl_trigger();
+  pdl_wait();
+  logits = after_wait(logits);
+  const int row = blockIdx.x;
+  // The step's status word rides along with the tokens: one copy to the host brings both.
+  if (status_out && row == 0 && threadIdx.x == 0) *status_out = __ldcg(after_wait(status_in));
+  sample_row(logits + (size_t)row * ld, V, params[row], row, xtc_special, n_special, out_token, out_logprob,
+             out_logprobs, ldo, redf, redi);
+}
+
+// Wide vocabularies: a row is cut into SAMPLE_SLICES slices, one thread block each.  A block finds its slice's
+// maximum (first index among equals), the sum of exponentials relative to it and, for a row that is drawn from
+// without filters, the slice's best draw value; it leaves these in scratch memory and takes a ticket.  The block
+// that takes a row's last ticket merges the slices in slice order (so the result does not depend on which block
+// that is, nor on how many rows the launch has) and writes the token.  Nobody waits for anybody.  A row with
+// filters (top-p, min-p, XTC, top-k) is done whole by that last block, as in sample_kernel.
+constexpr int SAMPLE_SLICES = 8;
+constexpr int SAMPLE_SLICE_WORDS = 8;    // maximum, its index, sum, best draw value, its index, 3 unused
+constexpr int SAMPLE_SPLIT_FROM = 8192;  // vocabulary sizes from which rows are cut
+constexpr int SAMPLE_SPLIT_THREADS = 256;
+constexpr int SAMPLE_KEEP = 8;           // logits a thread keeps in registers between its passes
+
+// (maximum with the first index among equals, sum of exponentials relative to that maximum) of two parts
+struct SoftmaxPart { float m; int idx; float s; };
+__device__ __forceinline__ SoftmaxPart merge(const SoftmaxPart& a, const SoftmaxPart& b) {   // a: lower indices on ties
+  SoftmaxPart o;
+  const bool take_b = b.m > a.m || (b.m == a.m && b.idx < a.idx);
+  o.m = take_b ? b.m : a.m;
+  o.idx = take_b ? b.idx : a.idx;
+  const float sa = a.m == -INFINITY ? 0.f : a.s * expf(a.m - o.m), sb = b.m == -INFINITY ? 0.f : b.s * expf(b.m - o.m);
+  o.s = sa + sb;
+  return o;
+}
+
+__global__ void __launch_bounds__(SAMPLE_SPLIT_THREADS)
+sample_split_kernel(const float* __restrict__ logits, int ld, int V, const SampleParams* __restrict__ params,
+                    const int* __restrict__ xtc_special, int n_special, int* __restrict__ out_token,
+                    float* __restrict__ out_logprob, const int* status_in, int* __restrict__ status_out,
+                    int* __restrict__ tickets, float* __restrict__ partials) {
+  __shared__ float redf[40];
+  __shared__ int redi[40];
+  __shared__ float w_m[8], w_s[8], w_g[8];
+  __shared__ int w_i[8], w_gi[8];
+  __shared__ int s_last;
+  const int row = blockIdx.y, slice = blockIdx.x;
+  const SampleParams P = params[row];      // written by the host before the step, not by the kernel before
+  const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+  constexpr int nt = SAMPLE_SPLIT_THREADS;
+  const bool filters = P.temp != 0.f && ((P.top_p > 0.f && P.top_p < 1.f) || P.min_p > 0.f ||
+                                         P.xtc_probability > 0.f || (P.top_k > 0 && P.top_k < V));
+  const bool draws = P.temp != 0.f && !filters;
+  const int per = (((V + SAMPLE_SLICES - 1) / SAMPLE_SLICES) + 3) & ~3;
+  const int i0 = slice * per, i1 = min(V, i0 + per);
+  pdl_trigger();
+  pdl_wait();
+  logits = after_wait(logits);
+  if (status_out && row == 0 && slice == 0 && tid == 0) *status_out = __ldcg(after_wait(status_in));
+  const float* lg = logits + (size_t)row * ld;
+
+  // one pass over global memory: the first SAMPLE_KEEP logits of a thread stay in registers
+  float keep[SAMPLE_KEEP];
+  SoftmaxPart mine = {-INFINITY, 0x7fffffff, 0.f};
+#pragma unroll
+  for (int k = 0; k < SAMPLE_KEEP; ++k) {
+    const int i = i0 + tid + k * nt;
+    keep[k] = i < i1 ? lg[i] : -INFINITY;
+    if (keep[k] > mine.m) { mine.m = keep[k]; mine.idx = i; }
+  }
+  for (int i = i0 + tid + SAMPLE_KEEP * nt; i < i1; i += nt) {
+    const float l = lg[i];
+    if (l > mine.m) { mine.m = l; mine.idx = i; }
+  }
+  if (mine.m != -INFINITY) {
+#pragma unroll
+    for (int k = 0; k < SAMPLE_KEEP; ++k) mine.s += expf(keep[k] - mine.m);   // exp(-inf) = 0 for what lies outside
+    for (int i = i0 + tid + SAMPLE_KEEP * nt; i < i1; i += nt) mine.s += expf(lg[i] - mine.m);
+  }
+  float gv = -INFINITY;
+  int gi = 0x7fffffff;
+  if (draws) {
+    const float inv_t = 1.f / P.temp;
+#pragma unroll
+    for (int k = 0; k < SAMPLE_KEEP; ++k) {
+      const int i = i0 + tid + k * nt;
+      if (i < i1) {
+        unsigned r[4];
+        philox4x32_10((unsigned)i, P.position, P.request, 0u, P.seed_lo, P.seed_hi, r);
+        const float v = draw_value(keep[k], inv_t, r[0]);
+        if (v > gv) { gv = v; gi = i; }
+      }
+    }
+    for (int i = i0 + tid + SAMPLE_KEEP * nt; i < i1; i += nt) {
+      unsigned r[4];
+      philox4x32_10((unsigned)i, P.position, P.request, 0u, P.seed_lo, P.seed_hi, r);
+      const float v = draw_value(lg[i], inv_t, r[0]);
+      if (v > gv) { gv = v; gi = i; }
+    }
+  }
+  // one reduction for all of it, in a fixed tree: lanes, then warps
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    SoftmaxPart other;
+    other.m = __shfl_xor_sync(0xffffffffu, mine.m, o);
+    other.idx = __shfl_xor_sync(0xffffffffu, mine.idx, o);
+    other.s = __shfl_xor_sync(0xffffffffu, mine.s, o);
+    mine = merge(mine, other);
+    const float ov = __shfl_xor_sync(0xffffffffu, gv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, gi, o);
+    if (ov > gv || (ov == gv && oi < gi)) { gv = ov; gi = oi; }
+  }
+  if (lane == 0) { w_m[wid] = mine.m; w_i[wid] = mine.idx; w_s[wid] = mine.s; w_g[wid] = gv; w_gi[wid] = gi; }
+  __syncthreads();
+  if (tid == 0) {
+    SoftmaxPart all = {w_m[0], w_i[0], w_s[0]};
+    float bg = w_g[0];
+    int bgi = w_gi[0];
+    for (int w = 1; w < nt / 32; ++w) {
+      all = merge(all, SoftmaxPart{w_m[w], w_i[w], w_s[w]});
+      if (w_g[w] > bg || (w_g[w] == bg && w_gi[w] < bgi)) { bg = w_g[w]; bgi = w_gi[w]; }
+    }
+    float* rec = partials + ((size_t)row * SAMPLE_SLICES + slice) * SAMPLE_SLICE_WORDS;
+    rec[0] = all.m;
+    rec[1] = __int_as_float(all.idx);
+    rec[2] = all.s;
+    rec[3] = bg;
+    rec[4] = __int_as_float(bgi);
+    __threadfence();
+    s_last = atomicAdd(&tickets[row], 1) == SAMPLE_SLICES - 1;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (tid == 0) tickets[row] = 0;             // for the next launch
+  if (filters) {   // not what this kernel is launched for, but right: the whole row by this block
+    sample_row(lg, V, P, row, xtc_special, n_special, out_token, out_logprob, nullptr, 0, redf, redi);
+    return;
+  }
+  if (tid == 0) {
+    const float* recs = partials + (size_t)row * SAMPLE_SLICES * SAMPLE_SLICE_WORDS;
+    SoftmaxPart all = {-INFINITY, 0x7fffffff, 0.f};
+    float bg = -INFINITY;
+    int bgi = 0x7fffffff;
+    for (int k = 0; k < SAMPLE_SLICES; ++k) {      // slices in index order: the first of equals wins
+      const float* rk = recs + k * SAMPLE_SLICE_WORDS;
+      all = merge(all, SoftmaxPart{__ldcg(rk), __float_as_int(__ldcg(rk + 1)), __ldcg(rk + 2)});
+      const float gk = __ldcg(rk + 3);
+      if (gk > bg) { bg = gk; bgi = __float_as_int(__ldcg(rk + 4)); }
+    }
+    const float lse = all.m + logf(all.s);
+    const int tok = (draws && bgi != 0x7fffffff) ? bgi : all.idx;
+    out_token[row] = tok;
+    out_logprob[row] = lg[tok] - lse;
+  }
+}
+
 // logits: float32 [R, V] at row stride ld.  params: R records of 16 words (SampleParams).
 // xtc_special: int32 [n_special], the rows' XTC special tokens one list after the other; each record names its range.
 // out_logprobs (optional): float32 [R, V] at row stride ldo receives logits - logsumexp.
 // status_in / status_out (optional, both or neither): the word at status_in is copied to status_out.
+// scratch (optional): mlxb_sample_scratch_words(R) 32-bit words, zero when first given and left zero by every
+// launch; with it (and without out_logprobs) rows of wide vocabularies are cut into slices over several thread blocks.
+MLXB_EXPORT int mlxb_sample_scratch_words(int R) { return R * (SAMPLE_SLICES * SAMPLE_SLICE_WORDS + 1); }
+
 MLXB_EXPORT int mlxb_sample(const float* logits, int ld, int R, int V, const void* params, const int* xtc_special,
                             int n_special, int* out_token, float* out_logprob, float* out_logprobs, int ldo,
-                            const int* status_in, int* status_out, cudaStream_t stream) {
+                            const int* status_in, int* status_out, void* scratch, int scratch_words,
+                            cudaStream_t stream) {
   if (R <= 0) return 0;
   if (V <= 0 || ld < V) return mlxb_fail(MLXB_BAD_ARG, "sample: vocabulary %d, row stride %d", V, ld);
   if (n_special < 0 || (n_special > 0 && !xtc_special))
@@ -270,6 +432,20 @@ MLXB_EXPORT int mlxb_sample(const float* logits, int ld, int R, int V, const voi
   if ((status_in == nullptr) != (status_out == nullptr))
     return mlxb_fail(MLXB_BAD_ARG, "sample: the status word needs both a source and a destination");
   const int threads = V >= 16384 ? 1024 : (V >= 2048 ? 512 : 256);
+  if (scratch != nullptr && out_logprobs == nullptr && V >= SAMPLE_SPLIT_FROM && R <= 65535) {
+    if (scratch_words < mlxb_sample_scratch_words(R) || ((uintptr_t)scratch & 15))
+      return mlxb_fail(MLXB_BAD_ARG, "sample: %d words of scratch memory for %d rows, %d needed (16-byte aligned)",
+                       scratch_words, R, mlxb_sample_scratch_words(R));
+    // tickets first, one word per row the scratch memory has room for (the same words whatever R is, so that they
+    // are zero when a launch begins), the slices' records behind them
+    const int room = scratch_words / (SAMPLE_SLICES * SAMPLE_SLICE_WORDS + 1);
+    int* tickets = (int*)scratch;
+    float* partials = (float*)scratch + room;
+    launch_pdl(sample_split_kernel, dim3(SAMPLE_SLICES, R), dim3(SAMPLE_SPLIT_THREADS), 0, stream, logits, ld, V,
+               (const SampleParams*)params, xtc_special, n_special, out_token, out_logprob, status_in, status_out,
+               tickets, partials);
+    return mlxb_check_launch("sample");
+  }
   launch_pdl(sample_kernel, dim3(R), dim3(threads), 0, stream, logits, ld, V, (const SampleParams*)params,
              xtc_special, n_special, out_token, out_logprob, out_logprobs, ldo, status_in, status_out);
   return mlxb_check_launch("sample");

@@ -32,8 +32,10 @@ class DecodeGraph:
             return False
         return all(not r.processors and not r.sampler.xtc_special_tokens for r in requests)
 
-    def __init__(self, engine, bucket: int):
-        self.engine, self.B = engine, bucket
+    def __init__(self, engine, bucket: int, filters: bool = False):
+        # filters: whether rows with top-p, min-p, XTC or top-k may come.  Without them the sampling kernel is the
+        # one that cuts every row into slices over several thread blocks; a step is replayed on the graph of its kind.
+        self.engine, self.B, self.filters = engine, bucket, filters
         mgr = engine.cache
         dev = engine.model.device
         B, W = bucket, mgr.table_width
@@ -50,6 +52,7 @@ class DecodeGraph:
         self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
         self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
         self.out = torch.zeros(2 * B + 1, dtype=torch.int32, device=dev)  # tokens | log-probability bits | status word
+        self.sample_scratch = ops.sample_scratch(B, dev)
         self.out_host = torch.zeros(2 * B + 1, dtype=torch.int32).pin_memory()
         h = self.host.numpy()
         h[self.off["logit_rows"]: self.off["logit_rows"] + B] = np.arange(B)
@@ -97,7 +100,7 @@ class DecodeGraph:
         self.logits = self.engine.model.run(ctx)
         ops.label("sampler", 0.0, 4.0 * self.logits.numel())
         ops.sample(self.logits, self.params, self.tok, self.lp, ctx.stream, status=self.engine.status,
-                   status_out=self.out[2 * self.B:])
+                   status_out=self.out[2 * self.B:], scratch=None if self.filters else self.sample_scratch)
         self._count = ops.launch_count - before
 
     def run(self, entries: Sequence[StepEntry], requests: Sequence, seed: int) -> Tuple[List[int], List[float]]:

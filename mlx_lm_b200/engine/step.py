@@ -448,9 +448,10 @@ class Engine:
         if not ok:
             return sampler(self.step(entries), requests)
         bucket = next(b for b in self.GRAPH_BUCKETS if b >= n)
-        graph = self._graphs.get(bucket)
+        filters = any(r.sampler.filters for r in requests)
+        graph = self._graphs.get((bucket, filters))
         if graph is None:
-            graph = self._graphs[bucket] = DecodeGraph(self, bucket)
+            graph = self._graphs[(bucket, filters)] = DecodeGraph(self, bucket, filters)
         return graph.run(entries, requests, sampler.seed)
 
     def read_status(self) -> int:

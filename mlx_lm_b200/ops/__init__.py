@@ -596,11 +596,18 @@ def attention_decode(q, positions, token_req, block_table, k_pool, v_pool, out, 
 SAMPLE_WORDS, PROCESS_WORDS = 16, 8
 
 _SAMPLE_ARGS = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int,
-                c_void_p, c_void_p, c_void_p]
+                c_void_p, c_void_p, c_void_p, c_int, c_void_p]
+SAMPLE_SCRATCH_WORDS_PER_ROW = 65      # csrc/sampling.cu: mlxb_sample_scratch_words
+
+
+def sample_scratch(n_rows: int, device) -> torch.Tensor:
+    """Scratch memory for ``sample`` over up to ``n_rows`` rows: zero, and left zero by every launch.  One per
+    stream on which launches may overlap."""
+    return torch.zeros(max(1, n_rows) * SAMPLE_SCRATCH_WORDS_PER_ROW, dtype=torch.int32, device=device)
 
 
 def sample(logits, params, out_token, out_logprob, stream, xtc_special=None, out_logprobs=None, status=None,
-           status_out=None) -> None:
+           status_out=None, scratch=None) -> None:
     """One token per row of float32 ``logits [R, V]``.
 
     ``params``: int32 ``[R, 16]`` holding the bit patterns of csrc/sampling.cu's ``SampleParams``;
@@ -608,7 +615,9 @@ def sample(logits, params, out_token, out_logprob, stream, xtc_special=None, out
     under the unfiltered distribution); ``out_logprobs`` (optional) float32 ``[R, V]`` receives
     ``logits - logsumexp(logits)``.  ``xtc_special``: int32 list of the rows' XTC special tokens, each
     row's record naming its range.  ``status`` / ``status_out`` (int32, one word each): the kernel copies
-    the step's status word next to its results, so that the host reads both with one copy."""
+    the step's status word next to its results, so that the host reads both with one copy.  ``scratch``
+    (from ``sample_scratch``, for at least this many rows): with it the rows of a wide vocabulary are cut into
+    slices over several thread blocks; the tokens are the same with and without it."""
     _need(logits, torch.float32, "sample logits")
     _need(params, torch.int32, "sample params")
     _need(out_token, torch.int32, "sample out_token")
@@ -633,7 +642,7 @@ def sample(logits, params, out_token, out_logprob, stream, xtc_special=None, out
         _need(status_out, torch.int32, "sample status_out")
     _call("sampling", "mlxb_sample", _SAMPLE_ARGS, _p(logits), _rows(logits, "sample logits"), R, V, _p(params),
           _p(xtc_special), n_special, _p(out_token), _p(out_logprob), _p(out_logprobs), ldo, _p(status),
-          _p(status_out), stream)
+          _p(status_out), _p(scratch), 0 if scratch is None else scratch.numel(), stream)
 
 
 _PROCESS_ARGS = [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]

@@ -33,6 +33,12 @@ class Sampler:
     xtc_special_tokens: tuple = ()
     seed: Optional[int] = None     # None: the scheduler's seed
 
+    @property
+    def filters(self) -> bool:
+        """Whether the draw is restricted (top-p, min-p, XTC, top-k): such rows take many passes over the
+        vocabulary in the kernel, greedy and plain temperature rows one."""
+        return self.temp != 0 and (0 < self.top_p < 1 or self.min_p > 0 or self.xtc_probability > 0 or self.top_k > 0)
+
     def words(self, seed: int, request: int, position: int, special_offset: int = 0) -> bytes:
         """The 16 words of csrc/sampling.cu's SampleParams for one row.  ``special_offset``: where this
         row's XTC special tokens begin in the list the kernel is given."""

@@ -29,7 +29,7 @@ class DeviceSampler:
             seed = int.from_bytes(os.urandom(8), "little")
         self.device, self.seed, self.return_logprobs, self.engine = device, int(seed), return_logprobs, engine
         self._cap = 0
-        self._host = self._dev_params = self._out = self._out_host = None
+        self._host = self._dev_params = self._out = self._out_host = self._scratch = None
         self.last_logprobs = None
 
     def _ensure(self, R: int) -> None:
@@ -39,6 +39,7 @@ class DeviceSampler:
         self._host = torch.empty(cap * ops.SAMPLE_WORDS, dtype=torch.int32).pin_memory()
         self._dev_params = torch.empty(cap * ops.SAMPLE_WORDS, dtype=torch.int32, device=self.device)
         self._out = torch.zeros(2 * cap + 1, dtype=torch.int32, device=self.device)   # tokens | logprob bits | status
+        self._scratch = ops.sample_scratch(cap, self.device)
         self._out_host = torch.zeros(2 * cap + 1, dtype=torch.int32).pin_memory()
         self._cap = cap
 
@@ -63,7 +64,8 @@ class DeviceSampler:
             full = torch.empty_like(logits)
         status = self.engine.status if self.engine is not None else None
         ops.sample(logits, self._dev_params, tok, lp, stream, xtc_special=xs, out_logprobs=full, status=status,
-                   status_out=self._out[2 * cap:] if status is not None else None)
+                   status_out=self._out[2 * cap:] if status is not None else None,
+                   scratch=None if any(r.sampler.filters for r in requests) else self._scratch)
         self.last_logprobs = full
         self._out_host.copy_(self._out, non_blocking=True)
         torch.cuda.current_stream().synchronize()

@@ -115,7 +115,7 @@ def test_decoding_as_cuda_graphs_at_the_benchmarked_layer_sizes(dtype, batch, me
     got = [[] for _ in reqs]
     for s in range(n_steps):
         eng.decode_sampled([StepEntry(r.uid, [r.tokens[-1]], [0]) for r in reqs], reqs, sampler)
-        graph = eng._graphs[batch]
+        graph = eng._graphs[(batch, False)]
         lg = graph.logits[:batch].float().cpu()
         for i, r in enumerate(reqs):
             got[i].append(lg[i])
@@ -133,7 +133,7 @@ def test_decoding_as_cuda_graphs_at_the_benchmarked_layer_sizes(dtype, batch, me
         for i, r in enumerate(reqs):
             r.tokens.append(seqs[i][-1])
         eng.decode_sampled([StepEntry(r.uid, [r.tokens[-1]], [0]) for r in reqs], reqs, sampler)
-        off = eng._graphs[batch].logits[:batch].float().cpu()
+        off = eng._graphs[(batch, False)].logits[:batch].float().cpu()
         ref_last = torch.stack([plain.hidden_states(t, w32, CFG)[-1] for t in seqs]) @ w32["wte.weight"].T
         assert rel_rows(off[:1], ref_last[:1]) > 1.5 * TOL[dtype], "a wrong page is not seen"
         assert rel_rows(off[1:], ref_last[1:]) <= TOL[dtype]

@@ -16,7 +16,9 @@ def run_sampler(logits, sampler, seed=0, request=0, position=0, full=False):
     lp = torch.empty(1, dtype=torch.float32, device="cuda")
     out = torch.empty_like(x) if full else None
     sp = torch.tensor(list(sampler.xtc_special_tokens), dtype=torch.int32).cuda() if sampler.xtc_special_tokens else None
-    ops.sample(x, params, tok, lp, ops.current_stream(), xtc_special=sp, out_logprobs=out)
+    # without full log-probabilities the row of a wide vocabulary is cut into slices over several thread blocks
+    ops.sample(x, params, tok, lp, ops.current_stream(), xtc_special=sp, out_logprobs=out,
+               scratch=None if full else ops.sample_scratch(1, "cuda"))
     return int(tok.item()), float(lp.item()), (out[0].cpu().numpy() if full else None)
 
 
@@ -116,6 +118,44 @@ def test_rows_are_independent():
     ops.sample(x, params, tok, lp, ops.current_stream())
     alone = [run_sampler(x[r].cpu().numpy(), s, 9, r, 40 + r)[0] for r, s in enumerate(samplers)]
     assert tok.tolist() == alone
+
+
+def test_rows_cut_into_slices_give_the_same_tokens():
+    """Wide vocabularies: with scratch memory a row is cut into slices over several thread blocks and merged by
+    the block that finishes last.  Tokens are those of the one-block kernel, whatever the options, with ties
+    across slices, rows of -inf, and launches of changing numbers of rows on the same scratch memory."""
+    from mlx_lm_b200 import ops
+    from mlx_lm_b200.sampling import make_sampler
+    V = 50257
+    rng = np.random.RandomState(7)
+    samplers = [make_sampler(0.0), make_sampler(0.8), make_sampler(1.3, top_p=0.9), make_sampler(0.0),
+                make_sampler(1.0, top_k=7), make_sampler(0.6), make_sampler(0.9, min_p=0.02), make_sampler(0.0)]
+    x = rng.randn(len(samplers), V).astype(np.float32) * 3
+    x[0, 40000] = x[0, 123] = x[0].max() + 1.0        # equal maxima in different slices: the first wins
+    x[3, :] = -np.inf
+    x[3, 50000] = 0.5                                  # all but one entry masked out
+    x[5, 6283:2 * 6283] = -np.inf                      # a slice that is empty of candidates
+    scratch = ops.sample_scratch(len(samplers), "cuda")
+    for n in (8, 3, 5, 8, 1):
+        rows = list(range(n))
+        rec = b"".join(samplers[r].words(11, r, 70 + r) for r in rows)
+        params = torch.tensor(np.frombuffer(rec, dtype=np.int32).copy()).cuda()
+        xs = torch.tensor(x[:n]).cuda()
+        tok, lp = (torch.empty(n, dtype=t, device="cuda") for t in (torch.int32, torch.float32))
+        tok1, lp1 = (torch.empty(n, dtype=t, device="cuda") for t in (torch.int32, torch.float32))
+        ops.sample(xs, params, tok, lp, ops.current_stream(), scratch=scratch)
+        ops.sample(xs, params, tok1, lp1, ops.current_stream())
+        assert tok.tolist() == tok1.tolist(), n
+        assert torch.allclose(lp, lp1, atol=2e-5), n
+        assert int(scratch[:len(samplers)].abs().sum().item()) == 0   # tickets back at zero
+    first = torch.empty(1, dtype=torch.int32, device="cuda")
+    ops.sample(torch.tensor(x[:1]).cuda(), torch.tensor(np.frombuffer(samplers[0].words(11, 0, 70), dtype=np.int32).copy()).cuda(),
+               first, torch.empty(1, dtype=torch.float32, device="cuda"), ops.current_stream(), scratch=scratch)
+    assert first.item() == 123
+    with pytest.raises(ops.KernelError):
+        ops.sample(torch.tensor(x[:8]).cuda(), params.repeat(8), torch.empty(8, dtype=torch.int32, device="cuda"),
+                   torch.empty(8, dtype=torch.float32, device="cuda"), ops.current_stream(),
+                   scratch=ops.sample_scratch(2, "cuda"))
 
 
 def test_logits_processors():
