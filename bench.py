@@ -143,19 +143,27 @@ def decode_loop(engine, sampler_cls, model, batch, prompt_len, steps, warmup, vo
         for r, t in zip(chunk, toks):
             r.tokens.append(t)
 
-    def one_step():     # model and sampler as one call: a CUDA graph replay for these batch sizes
-        toks, _ = engine.decode_sampled([StepEntry(r.uid, r.tokens[-1:], [0]) for r in reqs], reqs, sample)
-        for r, t in zip(reqs, toks):
-            r.tokens.append(t)
+    def run_steps(k):
+        """k decode steps as the scheduler runs them: each is model and sampler in one CUDA graph; the step after
+        it is launched (its tokens handed over on the device) before the host waits for this one's tokens."""
+        rows = list(range(len(reqs)))
+        flying = engine.decode_launch([StepEntry(r.uid, r.tokens[-1:], [0]) for r in reqs], reqs, sample)
+        for i in range(k):
+            ahead = None
+            if i + 1 < k:
+                ahead = engine.decode_launch([StepEntry(r.uid, [0], [0]) for r in reqs], reqs, sample,
+                                             source=(flying, rows))
+            toks, _ = engine.decode_collect(flying)
+            for r, t in zip(reqs, toks):
+                r.tokens.append(t)
+            flying = ahead
 
-    for _ in range(warmup):
-        one_step()
+    run_steps(warmup)
     torch.cuda.synchronize()
     ops.launch_count = 0
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     start.record()
-    for _ in range(steps):
-        one_step()
+    run_steps(steps)
     end.record()
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / steps

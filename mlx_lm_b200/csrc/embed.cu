@@ -53,3 +53,24 @@ MLXB_EXPORT int mlxb_embed_pos(int dtype, const int* tok, const int* pos, const 
     return mlxb_fail(MLXB_BAD_DTYPE, "embed_pos: dtype code %d", dtype);
   return mlxb_check_launch("embed_pos");
 }
+
+// Tokens that are still on the device: dst[i] = src[index[i]] where index[i] >= 0 (dst[i] stays as it is where
+// index[i] < 0).  Used to feed the tokens a step has just sampled into the next step without a round trip
+// through the host; src has n_src words, an index outside it sets MLXB_ST_TOKEN_RANGE and leaves dst[i] alone.
+__global__ void gather_tokens_kernel(const int* __restrict__ src, int n_src, const int* __restrict__ index,
+                                     int* __restrict__ dst, int n, int* __restrict__ status) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int j = index[i];
+  if (j < 0) return;
+  if (j >= n_src) { atomicOr(status, MLXB_ST_TOKEN_RANGE); return; }
+  dst[i] = src[j];
+}
+
+MLXB_EXPORT int mlxb_gather_tokens(const int* src, int n_src, const int* index, int* dst, int n, int* status,
+                                   cudaStream_t stream) {
+  if (n <= 0) return 0;
+  if (n_src <= 0) return mlxb_fail(MLXB_BAD_ARG, "gather_tokens: %d source words", n_src);
+  gather_tokens_kernel<<<(n + 127) / 128, 128, 0, stream>>>(src, n_src, index, dst, n, status);
+  return mlxb_check_launch("gather_tokens");
+}

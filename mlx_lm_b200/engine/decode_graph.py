@@ -10,11 +10,19 @@ buffer, copies it, replays the graph and reads the chosen tokens back.
 A batch smaller than its bucket is padded with rows whose request index is -1: the cache write
 and the attention kernels skip them, the other kernels compute rows nobody reads.  The graph has
 a workspace of its own, so that a later, larger step cannot move the buffers it was captured on.
+
+A step is ``launch`` (everything enqueued, nothing waited for) and ``collect`` (wait, read the
+tokens).  Between the two the caller may launch the step after it: a request's token for that
+step is then taken on the device from the output of the step before (``source``), so the device
+runs step after step while the host reads the tokens one step behind (mlx-lm overlaps the same
+way with ``mx.async_eval``, mlx_lm/generate.py:434-451).  Two pinned staging buffers alternate,
+so that a launch never writes what an earlier copy may still read.
 """
 
 from __future__ import annotations
 
-from typing import List, Sequence, Tuple
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
 
 import numpy as np
 import torch
@@ -22,6 +30,16 @@ import torch
 from .. import ops
 from ..sampling import LogitsProcessors
 from .step import StepContext, StepEntry, Workspace
+
+
+@dataclass
+class PendingStep:
+    """A launched decode step whose tokens have not been read yet."""
+    graph: "DecodeGraph"
+    slot: int                  # which staging buffer its results arrive in
+    n: int                     # live rows
+    event: object
+    collected: bool = False
 
 
 class DecodeGraph:
@@ -42,27 +60,32 @@ class DecodeGraph:
         pad = lambda n: (n + 3) & ~3
         sizes = [("tokens", B), ("positions", B), ("token_req", B), ("logit_rows", B), ("slots", B),
                  ("req_first_token", B + 1), ("req_first_position", B), ("sample", B * ops.SAMPLE_WORDS),
-                 ("single_tiles", 4 * B)]
+                 ("single_tiles", 4 * B), ("source_rows", B)]
         sizes += [(f"table{g}", B * W) for g in range(len(mgr.kv_groups))]
         self.off, total = {}, 0
         for name, n in sizes:
             self.off[name] = total
             total += pad(n)
         self.total = total
-        self.host = torch.zeros(total, dtype=torch.int32).pin_memory()
+        self.hosts = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(2)]
         self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
         self.out = torch.zeros(2 * B + 1, dtype=torch.int32, device=dev)  # tokens | log-probability bits | status word
         self.sample_scratch = ops.sample_scratch(B, dev)
-        self.out_host = torch.zeros(2 * B + 1, dtype=torch.int32).pin_memory()
-        h = self.host.numpy()
-        h[self.off["logit_rows"]: self.off["logit_rows"] + B] = np.arange(B)
-        h[self.off["req_first_token"]: self.off["req_first_token"] + B + 1] = np.arange(B + 1)
-        h[self.off["token_req"]: self.off["token_req"] + B] = -1
-        tiles = h[self.off["single_tiles"]: self.off["single_tiles"] + 4 * B].reshape(B, 4)
-        tiles[:] = 0
-        tiles[:, 0] = np.arange(B)          # (token row, 0 queries, ...): a padding row until a request takes it
-        for g in range(len(mgr.kv_groups)):
-            h[self.off[f"table{g}"]: self.off[f"table{g}"] + B * W] = -1
+        self.out_hosts = [torch.zeros(2 * B + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.pending: List[Optional[PendingStep]] = [None, None]     # the last step launched from each staging buffer
+        self.n_launched = 0
+        self.events = [torch.cuda.Event(), torch.cuda.Event()]
+        for host in self.hosts:
+            h = host.numpy()
+            h[self.off["logit_rows"]: self.off["logit_rows"] + B] = np.arange(B)
+            h[self.off["req_first_token"]: self.off["req_first_token"] + B + 1] = np.arange(B + 1)
+            h[self.off["token_req"]: self.off["token_req"] + B] = -1
+            h[self.off["source_rows"]: self.off["source_rows"] + B] = -1
+            tiles = h[self.off["single_tiles"]: self.off["single_tiles"] + 4 * B].reshape(B, 4)
+            tiles[:] = 0
+            tiles[:, 0] = np.arange(B)          # (token row, 0 queries, ...): a padding row until a request takes it
+            for g in range(len(mgr.kv_groups)):
+                h[self.off[f"table{g}"]: self.off[f"table{g}"] + B * W] = -1
 
         view = lambda name, n: self.dev[self.off[name]: self.off[name] + n]
         ctx = StepContext(engine)
@@ -81,7 +104,7 @@ class DecodeGraph:
         self.lp = self.out[B:2 * B].view(torch.float32)
 
         # once eagerly on a side stream (loads libraries, sizes the workspace), then capture
-        self.dev.copy_(self.host)
+        self.dev.copy_(self.hosts[0])
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
@@ -103,26 +126,42 @@ class DecodeGraph:
                    status_out=self.out[2 * self.B:], scratch=None if self.filters else self.sample_scratch)
         self._count = ops.launch_count - before
 
-    def run(self, entries: Sequence[StepEntry], requests: Sequence, seed: int) -> Tuple[List[int], List[float]]:
+    def launch(self, entries: Sequence[StepEntry], requests: Sequence, seed: int,
+               source: Optional[Tuple[PendingStep, Sequence[int]]] = None) -> PendingStep:
+        """Enqueue the step and return without waiting.  ``source = (step, rows)``: entry i's token is not known to
+        the host yet; it is row ``rows[i]`` of what ``step`` (launched, not yet collected) samples (``rows[i] < 0``:
+        the token of the entry, as without a source), and the request's sampling position is one further than its
+        host-side token count says."""
         eng, mgr, B = self.engine, self.engine.cache, self.B
         eng._validate(entries)
         n = len(entries)
-        h, off, W = self.host.numpy(), self.off, mgr.table_width
+        slot = self.n_launched & 1
+        if self.pending[slot] is not None and not self.pending[slot].collected:
+            # its caller went away without reading it (a generator closed early): wait, so that the staging
+            # buffers are free, and forget it
+            self.pending[slot].event.synchronize()
+            self.pending[slot].collected = True
+        h, off, W = self.hosts[slot].numpy(), self.off, mgr.table_width
         h[off["token_req"] + n: off["token_req"] + B] = -1
+        h[off["source_rows"]: off["source_rows"] + B] = -1
         tiles = h[off["single_tiles"]: off["single_tiles"] + 4 * B].reshape(B, 4)
         tiles[n:, 1:] = 0
         words = []
+        rows = source[1] if source is not None else None
         try:
             for i, e in enumerate(entries):
                 start = mgr.reserve(e.rid, 1)
-                h[off["tokens"] + i] = e.tokens[0]
+                ahead = rows is not None and rows[i] >= 0
+                h[off["tokens"] + i] = 0 if ahead else e.tokens[0]
+                if ahead:
+                    h[off["source_rows"] + i] = rows[i]
                 h[off["positions"] + i] = start
                 h[off["token_req"] + i] = i
                 h[off["slots"] + i] = mgr.requests[e.rid].slot
                 h[off["req_first_position"] + i] = start
                 tiles[i, 1], tiles[i, 2], tiles[i, 3] = 1, i, start
                 r = requests[i]
-                words.append(r.sampler.words(seed, r.uid, len(r.tokens)))
+                words.append(r.sampler.words(seed, r.uid, len(r.tokens) + (1 if ahead else 0)))
             h[off["sample"]: off["sample"] + n * ops.SAMPLE_WORDS] = np.frombuffer(b"".join(words), dtype=np.int32)
             h[off["sample"] + n * ops.SAMPLE_WORDS: off["sample"] + B * ops.SAMPLE_WORDS] = 0
             rids = [e.rid for e in entries]
@@ -130,20 +169,39 @@ class DecodeGraph:
                 o = off[f"table{g}"]
                 mgr.block_table(g, rids, out=h[o: o + n * W].reshape(n, W))
                 h[o + n * W: o + B * W] = -1
-            self.dev.copy_(self.host, non_blocking=True)
+            self.dev.copy_(self.hosts[slot], non_blocking=True)
+            if source is not None:
+                src = source[0].graph.out[:source[0].graph.B]
+                ops.gather_tokens(src, self.dev[off["source_rows"]: off["source_rows"] + n],
+                                  self.dev[off["tokens"]: off["tokens"] + n], eng.status, ops.current_stream())
             self.graph.replay()
             ops.launch_count += self.n_kernels
-            self.out_host.copy_(self.out, non_blocking=True)
+            self.out_hosts[slot].copy_(self.out, non_blocking=True)
+            event = self.events[slot]
+            event.record()
             eng.h2d_bytes += 4 * self.total
             eng.d2h_bytes += 4 * self.out.numel()
-            torch.cuda.current_stream().synchronize()
         except BaseException:
-            for e in entries:          # the step did not run to its end: undo the reservations
+            for e in entries:          # the step was not enqueued whole: undo the reservations
                 mgr.rollback(e.rid)
             raise
+        # Enqueued: what later steps read of the cache comes after this step in stream order, so the lengths move
+        # on now and the next step can be laid out before this one has run.
         for e in entries:
             mgr.commit(e.rid)
         eng.n_steps += 1
-        o = self.out_host.numpy()
-        eng.host_status = int(o[2 * B])
+        self.n_launched += 1
+        step = self.pending[slot] = PendingStep(self, slot, n, event)
+        return step
+
+    def collect(self, step: PendingStep) -> Tuple[List[int], List[float]]:
+        """Wait for a launched step; its tokens and their log-probabilities."""
+        step.event.synchronize()
+        step.collected = True
+        o = self.out_hosts[step.slot].numpy()
+        self.engine.host_status = int(o[2 * self.B])
+        n, B = step.n, self.B
         return o[:n].tolist(), o[B:B + n].view(np.float32).tolist()
+
+    def run(self, entries: Sequence[StepEntry], requests: Sequence, seed: int) -> Tuple[List[int], List[float]]:
+        return self.collect(self.launch(entries, requests, seed))

@@ -24,6 +24,15 @@ Decisions, all made in ``plan`` (plain Python, no device):
             (mlx_lm/generate.py:1504-1514), ``"cancelled"`` for a request taken out with ``remove``
             (reported once, by the next ``next``); pages and slot are given back at once.
 
+One step ahead: while the device runs a pure decode step, the host cannot know its tokens, but it knows nearly
+everything else about the step after it (who goes on, positions, pages, sampling records), and the tokens can stay on
+the device.  So before ``next`` waits for a decode step it launches the following one (``lookahead``; the engine's
+``decode_launch`` with the step in flight as the source of the tokens) whenever nothing else is due: nobody waits to be
+admitted, nobody is in its prompt, pages are there.  Requests that reach ``max_tokens`` with the step in flight are
+left out; a request that turns out to have stopped (a stop sequence) or was cancelled has one row computed in vain,
+which is dropped when that step is read.  The tokens are the same with and without (mlx-lm overlaps the same way:
+``mx.async_eval`` of the next step before the current token is read, mlx_lm/generate.py:434-451).
+
 After every step that hands out tokens the scheduler looks at the status word the kernels set instead of
 faulting (a token, position or page id out of range, a bounded wait that gave up), which the sampler brought
 back with the tokens, and raises ``KernelError`` rather than hand out tokens of a step that went wrong.
@@ -141,6 +150,8 @@ class Scheduler:
         # never collide
         self._namespace = engine.new_namespace() if hasattr(engine, "new_namespace") else None
         self._cancelled: List[Response] = []
+        self._inflight = None          # (handle, planned entries) of a decode step launched but not read yet
+        self.lookahead = True
         self._admissions = 0
         self.stats = SchedulerStats()
         self.last_step_tokens = self.last_step_prompt_tokens = 0
@@ -181,10 +192,13 @@ class Scheduler:
         self.waiting = deque(r for r in self.waiting if r.uid not in uids)
         out = [Response(r.uid, -1, 0.0, "cancelled", all_tokens=list(r.tokens)) for r in gone]
         self._cancelled.extend(out)
+        if self._inflight is not None and not any(p.request in self.running for p in self._inflight[1]):
+            self.engine.decode_collect(self._inflight[0])      # nobody is left to read that step: wait and drop it
+            self._inflight = None
         return out
 
     def has_work(self) -> bool:
-        return bool(self.waiting or self.running or self._cancelled)
+        return bool(self.waiting or self.running or self._cancelled or self._inflight)
 
     # ------------------------------------------------------------------ decisions
     def _preempt(self, victim: Request) -> None:
@@ -282,6 +296,8 @@ class Scheduler:
     # ------------------------------------------------------------------ one iteration
     def next(self) -> Tuple[List[PromptProgress], List[Response]]:
         cancelled, self._cancelled = self._cancelled, []
+        if self._inflight is not None:
+            return [], cancelled + self._read_inflight()
         planned = self.plan()
         self.last_step_tokens = self.last_step_prompt_tokens = 0
         if not planned:
@@ -291,6 +307,11 @@ class Scheduler:
         sampled = [p.request for p in planned if p.wants_logits]
         fused = (len(sampled) == len(planned) and hasattr(self.engine, "decode_sampled")
                  and all(p.n_tokens == 1 for p in planned))
+        if fused and self.lookahead and hasattr(self.engine, "decode_launch"):
+            handle = self.engine.decode_launch(entries, sampled, self.sample)
+            if handle is not None:      # a CUDA graph took it: on its way; the step after it may follow before we wait
+                self._inflight = (handle, planned)
+                return [], cancelled + self._read_inflight()
         if fused:     # a pure decode step: model and sampler in one call (a CUDA graph where it fits)
             tokens, logprobs = self.engine.decode_sampled(entries, sampled, self.sample)
         else:
@@ -298,11 +319,63 @@ class Scheduler:
             tokens, logprobs = self.sample(logits, sampled) if sampled else ([], [])
         if sampled:
             self._check_status()
+        prompts, responses = self._account(planned, tokens, logprobs)
+        return prompts, cancelled + responses
+
+    def _read_inflight(self) -> List[Response]:
+        """The tokens of the decode step in flight; before waiting for them, the step after it is launched if it
+        can be laid out without them."""
+        handle, planned = self._inflight
+        self._inflight = None
+        ahead = self._launch_ahead(handle, planned)
+        tokens, logprobs = self.engine.decode_collect(handle)
+        self._check_status()
+        self.last_step_tokens = self.last_step_prompt_tokens = 0
+        _, responses = self._account(planned, tokens, logprobs)
+        self._inflight = ahead
+        return responses
+
+    def _launch_ahead(self, handle, planned: List[PlannedEntry]):
+        """Launch the decode step that follows the one in flight, or None if that step cannot be decided yet:
+        somebody waits for admission or was cancelled, somebody is still in its prompt, nobody goes on, or pages
+        are short (``plan`` then decides, with the tokens in hand)."""
+        if self.waiting or self._cancelled:
+            return None
+        live = {id(r) for r in self.running}
+        flying = {id(p.request) for p in planned}
+        if any(id(r) not in flying for r in self.running):
+            return None
+        rows, goes_on = [], []
+        for i, p in enumerate(planned):
+            r = p.request
+            if id(r) in live and r.n_generated + 1 < r.max_tokens:      # not cancelled, not at its last token
+                rows.append(i)
+                goes_on.append(r)
+        if not goes_on:
+            return None
+        taken = [0] * len(self.engine.cache.kv_groups)
+        for r in goes_on:
+            need = self._fits(taken, r, 1)
+            if need is None:
+                return None
+            taken = [t + c for t, c in zip(taken, need)]
+        entries = [StepEntry(r.rid, [0], [0]) for r in goes_on]     # the tokens are on the device
+        ahead = self.engine.decode_launch(entries, goes_on, self.sample, source=(handle, rows))
+        if ahead is None:
+            return None
+        return ahead, [PlannedEntry(r, 1, True) for r in goes_on]
+
+    def _account(self, planned: List[PlannedEntry], tokens, logprobs) -> Tuple[List[PromptProgress], List[Response]]:
+        """Book a finished step: progress of prompts, the new tokens, who is done.  Rows of requests that have left
+        meanwhile (stopped or cancelled while the step was in flight) are dropped."""
         self.stats.steps += 1
         self.stats.most_running = max(self.stats.most_running, len(self.running))
+        live = {id(r) for r in self.running}
         prompts: List[PromptProgress] = []
         for p in planned:
             r = p.request
+            if id(r) not in live:
+                continue
             if r.n_cached < r.n_prompt:
                 done = min(r.n_cached + p.n_tokens, r.n_prompt)
                 self.stats.prompt_tokens += done - r.n_cached
@@ -312,22 +385,24 @@ class Scheduler:
             self.stats.tokens += p.n_tokens
             self.last_step_tokens += p.n_tokens
         responses: List[Response] = []
-        if sampled:
-            for r, tok, lp in zip(sampled, tokens, logprobs):
-                r.tokens.append(int(tok))
-                r.n_generated += 1
-                self.stats.generation_tokens += 1
-                reason = None
-                if r.stop.matches(r.generated):
-                    reason = "stop"
-                elif r.n_generated >= r.max_tokens:
-                    reason = "length"
-                if reason is not None:
-                    self.engine.finish(r.rid)
-                    self.running.remove(r)
-                responses.append(Response(r.uid, int(tok), lp, reason,
-                                          all_tokens=list(r.tokens) if reason is not None else None))
-        return prompts, cancelled + responses
+        sampled = [p.request for p in planned if p.wants_logits]
+        for r, tok, lp in zip(sampled, tokens, logprobs):
+            if id(r) not in live:
+                continue
+            r.tokens.append(int(tok))
+            r.n_generated += 1
+            self.stats.generation_tokens += 1
+            reason = None
+            if r.stop.matches(r.generated):
+                reason = "stop"
+            elif r.n_generated >= r.max_tokens:
+                reason = "length"
+            if reason is not None:
+                self.engine.finish(r.rid)
+                self.running.remove(r)
+            responses.append(Response(r.uid, int(tok), lp, reason,
+                                      all_tokens=list(r.tokens) if reason is not None else None))
+        return prompts, responses
 
     def _check_status(self) -> None:
         """Raise if a kernel of the steps since the last look reported something (``Engine.host_status``: the

@@ -440,19 +440,34 @@ class Engine:
         When every entry brings a single token and the samplers need nothing beyond the sampling
         kernel, the whole step (model and sampler) is replayed as a CUDA graph captured for the next
         batch size in ``GRAPH_BUCKETS``; otherwise it is ``step`` followed by ``sampler``."""
+        step = self.decode_launch(entries, requests, sampler)
+        if step is None:
+            return sampler(self.step(entries), requests)
+        return self.decode_collect(step)
+
+    def decode_launch(self, entries: Sequence[StepEntry], requests: Sequence, sampler, source=None):
+        """Enqueue such a step as a CUDA graph and return at once with a handle for ``decode_collect``; None if the
+        step does not fit a graph (more rows than the largest bucket, an entry of several tokens, samplers that
+        need more than the sampling kernel).  ``source = (handle, rows)``: the entries' tokens are rows ``rows`` of
+        what the step behind ``handle`` samples (still on its way), see ``DecodeGraph.launch``.  At most two steps
+        are in flight; they are collected in the order they were launched."""
         from .decode_graph import DecodeGraph
 
         n = len(entries)
         ok = (self.use_graphs and n <= self.GRAPH_BUCKETS[-1] and all(len(e.tokens) == 1 for e in entries)
               and DecodeGraph.samplers_fit(requests, sampler))
         if not ok:
-            return sampler(self.step(entries), requests)
+            return None
         bucket = next(b for b in self.GRAPH_BUCKETS if b >= n)
         filters = any(r.sampler.filters for r in requests)
         graph = self._graphs.get((bucket, filters))
         if graph is None:
             graph = self._graphs[(bucket, filters)] = DecodeGraph(self, bucket, filters)
-        return graph.run(entries, requests, sampler.seed)
+        return graph.launch(entries, requests, sampler.seed, source)
+
+    def decode_collect(self, step):
+        """Wait for a step launched by ``decode_launch``: ``(tokens, logprobs)`` as lists."""
+        return step.graph.collect(step)
 
     def read_status(self) -> int:
         """Bits kernels set instead of faulting (token, position or page id out of range, a bounded wait that

@@ -194,6 +194,17 @@ def embed_pos(tokens, positions, wte, wpe, out, status, stream, scale: float = 1
           _p(wpe), _p(out), T, D, wte.shape[0], 0 if wpe is None else wpe.shape[0], scale, _p(status), stream)
 
 
+def gather_tokens(src, index, dst, status, stream) -> None:
+    """``dst[i] = src[index[i]]`` where ``index[i] >= 0`` (int32 all): tokens a step has just sampled, handed
+    to the next step on the device."""
+    for t, what in ((src, "src"), (index, "index"), (dst, "dst")):
+        _need(t, torch.int32, f"gather_tokens {what}")
+    if index.numel() < dst.numel():
+        raise KernelError(f"gather_tokens: {index.numel()} indices for {dst.numel()} tokens")
+    _call("embed", "mlxb_gather_tokens", [c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+          _p(src), src.numel(), _p(index), _p(dst), dst.numel(), _p(status), stream)
+
+
 # --------------------------------------------------------------------------
 # norms
 

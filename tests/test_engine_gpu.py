@@ -306,11 +306,12 @@ def test_decode_as_a_cuda_graph_equals_the_eager_step(dtype, tmp_path):
     prompts = [random_tokens(n, 1000, 50 + n) for n in (3, 17, 40, 33, 9)]       # 5 requests: bucket of 8
     max_tokens = [30, 12, 25, 5, 18]
 
-    def run(use_graphs):
+    def run(use_graphs, lookahead=True, sampler=make_sampler(0.7, top_k=20)):
         engine = get_engine(model, page_size=16, num_pages=64, max_requests=8)
         engine.use_graphs = use_graphs
-        gen = BatchGenerator(model, engine=engine, sampler=make_sampler(0.7, top_k=20), seed=3,
+        gen = BatchGenerator(model, engine=engine, sampler=sampler, seed=3,
                              completion_batch_size=8, prefill_batch_size=8)
+        gen.scheduler.lookahead = lookahead
         uids = gen.insert(prompts, max_tokens)
         out = {u: [] for u in uids}
         while gen.scheduler.has_work():
@@ -325,6 +326,10 @@ def test_decode_as_a_cuda_graph_equals_the_eager_step(dtype, tmp_path):
     assert [[t for t, _ in o] for o in eager] == [[t for t, _ in o] for o in graphed]
     assert eager == graphed
     engine.check_status()
+    # the step launched ahead of the tokens (the default above) changes nothing, with filters and without
+    assert run(True, lookahead=False)[0] == graphed
+    plain = make_sampler(0.9)
+    assert run(True, True, plain)[0] == run(True, False, plain)[0] == run(False, True, plain)[0]
 
 
 @pytest.mark.parametrize("dtype", DTYPES)

@@ -336,3 +336,125 @@ def test_two_schedulers_on_one_engine_do_not_collide():
 def fake_rid_sample(rows, requests):
     assert [r.rid for r in requests] == [rid for rid, _ in rows]
     return [token_fn(r.uid, pos + 1) for r, (_, pos) in zip(requests, rows)], [0.0] * len(rows)
+
+
+# ---------------------------------------------------------------------------------------------- one step ahead
+
+class Handle:
+    def __init__(self, rids, tokens):
+        self.rids, self.tokens, self.collected = rids, tokens, False
+
+
+class AheadEngine(FakeEngine):
+    """A fake of the engine's launch/collect pair: a launched step books its pages at once; its tokens (a function
+    of request and position, as in ``fake_sample``) become known to the caller only at ``decode_collect``."""
+
+    def __init__(self, *a, **k):
+        super().__init__(*a, **k)
+        self.launched, self.ahead_rows, self.in_flight = 0, 0, []
+
+    def decode_sampled(self, entries, requests, sample):
+        return self.decode_collect(self.decode_launch(entries, requests, sample))
+
+    def decode_launch(self, entries, requests, sample, source=None):
+        assert len(self.in_flight) < 2, "at most two steps in flight"
+        rec, toks = [], []
+        for i, e in enumerate(entries):
+            assert len(e.tokens) == 1
+            start = self.cache.reserve(e.rid, 1)
+            assert start == len(self.fed[e.rid])
+            if source is not None and source[1][i] >= 0:
+                assert not source[0].collected
+                tok = source[0].tokens[source[1][i]]          # handed over "on the device"
+                assert source[0].rids[source[1][i]] == e.rid
+                self.ahead_rows += 1
+            else:
+                tok = e.tokens[0]
+            self.fed[e.rid].append(tok)
+            rec.append((e.rid, start, 1, [0]))
+            uid = e.rid[1] if isinstance(e.rid, tuple) else e.rid
+            toks.append(token_fn(uid, start + 1))
+        for e in entries:
+            self.cache.commit(e.rid)
+        self.cache.check()
+        self.steps.append(rec)
+        self.launched += 1
+        h = Handle([e.rid for e in entries], toks)
+        self.in_flight.append(h)
+        return h
+
+    def decode_collect(self, h):
+        assert self.in_flight and self.in_flight[0] is h, "steps are collected in the order they were launched"
+        self.in_flight.pop(0)
+        h.collected = True
+        return list(h.tokens), [0.0] * len(h.tokens)
+
+
+def both_ways(n_pages, inserts, **kw):
+    """The same requests with and without the step ahead: (tokens, reasons, engine) of each."""
+    res = []
+    for ahead in (False, True):
+        eng = AheadEngine(n_pages=n_pages)
+        s = Scheduler(eng, fake_sample, **kw)
+        s.lookahead = ahead
+        for prompt, max_tokens, stop in inserts:
+            s.insert(prompt, max_tokens, stop=StopSequenceMatcher(stop) if stop else None)
+        out, reasons = run(s)
+        assert eng.cache.pages_in_use() == [0] and not eng.in_flight
+        eng.cache.check()
+        res.append((out, reasons, eng))
+    return res
+
+
+def test_a_step_ahead_gives_the_same_tokens():
+    inserts = [(list(range(20)), 9, None), (list(range(33)), 30, None), (list(range(5)), 1, None),
+               (list(range(47)), 17, None), (list(range(8)), 30, None)]
+    (out0, why0, e0), (out1, why1, e1) = both_ways(64, inserts, max_requests=3, prefill_step_size=16,
+                                                  max_tokens_per_step=32)
+    assert out0 == out1 and why0 == why1
+    for uid, (prompt, n, _) in enumerate(inserts):
+        assert out1[uid] == expected(uid, len(prompt), n)
+    assert e1.ahead_rows > 20 and e0.ahead_rows == 0
+    # a request at its last token is not in the step ahead: nobody computes a token past max_tokens
+    assert sum(len(st) for st in e1.steps) == sum(len(st) for st in e0.steps)
+
+
+def test_a_stop_found_one_step_late_drops_the_row_computed_in_vain():
+    # request 0 stops when its fourth token comes; the step ahead has computed its fifth by then
+    stop_tok = expected(0, 12, 4)[3]
+    inserts = [(list(range(12)), 20, [[stop_tok]]), (list(range(7)), 10, None)]
+    (out0, why0, e0), (out1, why1, e1) = both_ways(32, inserts, max_requests=4)
+    assert out0 == out1 and why0 == why1 == {0: "stop", 1: "length"}
+    assert len(out1[0]) == 4
+    assert sum(len(st) for st in e1.steps) == sum(len(st) for st in e0.steps) + 1     # the one row in vain
+
+
+def test_pages_that_run_out_end_the_run_ahead_and_preemption_still_works():
+    inserts = [(list(range(30)), 40, None), (list(range(30)), 40, None), (list(range(30)), 40, None)]
+    (out0, why0, e0), (out1, why1, e1) = both_ways(11, inserts, max_requests=3)      # 11 pages of 16: not enough for all
+    assert out0 == out1 and why0 == why1
+    for uid in range(3):
+        assert out1[uid] == expected(uid, 30, 40)
+
+
+def test_cancelling_while_a_step_is_in_flight():
+    eng = AheadEngine(n_pages=32)
+    s = Scheduler(eng, fake_sample, max_requests=4)
+    a = s.insert(list(range(10)), 50)
+    b = s.insert(list(range(6)), 50)
+    seen = {a: [], b: []}
+    for _ in range(6):
+        for r in s.next()[1]:
+            seen[r.uid].append(r.token)
+    assert s._inflight is not None
+    s.remove([a])                                   # its row of the step in flight is dropped when that step is read
+    for _ in range(5):
+        for r in s.next()[1]:
+            if r.finish_reason != "cancelled":
+                assert r.uid == b
+                seen[b].append(r.token)
+    assert seen[b] == expected(b, 6, len(seen[b])) and len(seen[a]) <= 6
+    s.remove([b])                                   # nobody left: the step in flight is waited for and dropped
+    assert s._inflight is None and not eng.in_flight
+    assert eng.cache.pages_in_use() == [0]
+    eng.cache.check()
