@@ -71,6 +71,16 @@ __device__ __forceinline__ T* after_wait(T* p) {
   return p;
 }
 
+static inline int mlxb_sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    cudaGetDevice(&dev);
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+  }
+  return n;
+}
+
 static inline bool mlxb_pdl_enabled() {
   static int on = -1;
   if (on < 0) {

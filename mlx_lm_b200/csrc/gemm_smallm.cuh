@@ -379,15 +379,21 @@ static int launch_epi(const void* A, const void* W, const float* bias, const voi
 template <typename TO, bool SCATTER, bool FOLD>
 static int launch(const void* A, const void* W, const float* bias, const void* residual, void* C, int M, int N, int K,
                   int lda, int ldc, int epi, const KvScatter& kv, const NormFold& fold, cudaStream_t stream) {
-  // Weight tiles per CTA.  Every CTA reads all M rows of the activations from L2, so with many rows and many
-  // CTAs that traffic (M x K x 2 bytes per CTA) exceeds the weight stream itself; wide outputs therefore get
-  // more tiles per CTA once M is large (measured at 1024-wide models: 3072 and 4096 outputs at 33-64 rows
-  // are a quarter faster with four tiles, 4096 outputs at 17-32 rows with two; narrow outputs need the CTAs).
+  // Weight tiles (of 8 outputs) per CTA.  Two things pull apart.  Every CTA reads all M rows of the activations from
+  // L2, so with many rows and many CTAs that traffic (M x K x 2 bytes per CTA) exceeds the weight stream itself; and
+  // a launch with more CTAs than the SMs hold at once runs in waves, of which only the first can fetch its weights
+  // while the kernel before still runs.  Measured on 1024-, 1280- and 1600-wide models: at up to 16 rows two tiles
+  // wherever one-tile CTAs would be more than one per SM (1024-wide, 8 rows: 3072 outputs 3.9 against 5.6
+  // microseconds, 4096 outputs 4.0 against 5.4, a decode step 0.59 against 0.65 ms; a vocabulary-sized output 26.6
+  // against 36.8; four tiles are slower everywhere, and so are two for outputs that fit one CTA per SM); four tiles
+  // for wide outputs at 17 to 32 rows (a step of 32 rows 1.14 against 1.20 ms) and at 33 to 64 rows (a quarter
+  // faster than one).
   const int tiles = (N + 7) / 8;
   const int mt = M <= 16 ? 1 : (M <= 32 ? 2 : 4);
   int nw = 1;
   if (mt == 4) nw = tiles >= 384 ? 4 : (tiles >= 2 * 148 ? 2 : 1);
-  else if (mt == 2) nw = tiles >= 512 ? 2 : 1;
+  else if (mt == 2) nw = tiles >= 2 * 148 ? 4 : 1;
+  else nw = tiles > mlxb_sm_count() ? 2 : 1;
 
   // K blocks are shared by 8 warps; a long K with few output tiles gets 16 so that a warp's chain of
   // dependent loads stays short, and so do more than 32 rows with one weight tile per CTA (a 1024-wide output at
@@ -400,13 +406,8 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
     return launch_epi<MT_, NW_, 8, TO, SCATTER, FOLD>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, kv, fold,  \
                                                       stream);                                                  \
   }
-  if (mt == 1) {
-    // a vocabulary-sized output: two weight tiles per CTA halve the number of short-lived CTAs (50 257 outputs of a
-    // 1024-wide model at 8 rows: 26.6 against 36.8 microseconds; four tiles: 30.8)
-    if (tiles >= 2048) GO(1, 2);
-    GO(1, 1);
-  }
-  if (mt == 2) { if (nw == 2) GO(2, 2); GO(2, 1); }
+  if (mt == 1) { if (nw == 2) GO(1, 2); GO(1, 1); }
+  if (mt == 2) { if (nw == 4) GO(2, 4); GO(2, 1); }
   if (nw == 4) GO(4, 4);
   if (nw == 2) GO(4, 2);
   GO(4, 1);
