@@ -40,6 +40,7 @@ MEDIUM = dict(model_type="gpt2", n_layer=24, n_embd=1024, n_head=16, n_inner=409
 SIZES = {"medium": MEDIUM,
          "large": dict(MEDIUM, n_layer=36, n_embd=1280, n_head=20, n_inner=5120),
          "xl": dict(MEDIUM, n_layer=48, n_embd=1600, n_head=25, n_inner=6400)}
+PAGE_SIZE = 16
 PROMPT_LEN = 512
 CONTEXT = 1024
 
@@ -473,7 +474,7 @@ def run_ours(args):
         model, _ = load_model(d, dtype="bfloat16", device="cuda:0")
     vocab = cfg["vocab_size"]
     max_b = max(B, 64)
-    engine = Engine(model, page_size=16, max_tokens=max_b * CONTEXT, max_requests=max_b)
+    engine = Engine(model, page_size=PAGE_SIZE, max_tokens=max_b * CONTEXT, max_requests=max_b)
     weight_bytes, kv_per_token, lin_flops = model_bytes_and_flops(cfg, cfg["n_layer"])
 
     if args.only == "mixed":
@@ -636,7 +637,9 @@ def prefill_step(engine, cfg, pk, vocab, n_pf, lin_flops, table=False):
 
 
 def main():
+    global PAGE_SIZE
     ap = argparse.ArgumentParser()
+    ap.add_argument("--page-size", type=int, default=16, help="positions per page of the key/value cache")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
@@ -657,6 +660,7 @@ def main():
                     help="with --only decode: prompt length before the timed steps (default 512, the contract's)")
     ap.add_argument("--size", default="medium", choices=sorted(SIZES), help="layer sizes: GPT-2 medium, large or XL")
     a = ap.parse_args()
+    PAGE_SIZE = a.page_size
     if a.impl == "reference":
         print(json.dumps(reference_arm()))
         return 0
