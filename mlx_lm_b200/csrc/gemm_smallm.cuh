@@ -385,7 +385,9 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
   // while the kernel before still runs.  Measured on 1024-, 1280- and 1600-wide models: at up to 16 rows two tiles
   // wherever one-tile CTAs would be more than one per SM (1024-wide, 8 rows: 3072 outputs 3.9 against 5.6
   // microseconds, 4096 outputs 4.0 against 5.4, a decode step 0.59 against 0.65 ms; a vocabulary-sized output 26.6
-  // against 36.8; four tiles are slower everywhere, and so are two for outputs that fit one CTA per SM); four tiles
+  // against 36.8; four tiles are slower everywhere, and so are two for outputs that fit one CTA per SM; three tiles
+  // where two would still be more CTAs than fit at once: 1280-wide, 5120 outputs, a step 1.18 against 1.28 ms; 1600-wide
+  // 2.05 against 2.12; three tiles where two fit are slower); four tiles
   // for wide outputs at 17 to 32 rows (a step of 32 rows 1.14 against 1.20 ms) and at 33 to 64 rows (a quarter
   // faster than one).
   const int tiles = (N + 7) / 8;
@@ -393,7 +395,11 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
   int nw = 1;
   if (mt == 4) nw = tiles >= 384 ? 4 : (tiles >= 2 * 148 ? 2 : 1);
   else if (mt == 2) nw = tiles >= 2 * 148 ? 4 : 1;
-  else nw = tiles > mlxb_sm_count() ? 2 : 1;
+  else {
+    const int sms = mlxb_sm_count();
+    nw = tiles > sms ? 2 : 1;
+    if (tiles < 2048 && (tiles + 1) / 2 > 2 * sms) nw = 3;   // two tiles would still leave more CTAs than fit at once
+  }
 
   // K blocks are shared by 8 warps; a long K with few output tiles gets 16 so that a warp's chain of
   // dependent loads stays short, and so do more than 32 rows with one weight tile per CTA (a 1024-wide output at
@@ -406,7 +412,7 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
     return launch_epi<MT_, NW_, 8, TO, SCATTER, FOLD>(A, W, bias, residual, C, M, N, K, lda, ldc, epi, kv, fold,  \
                                                       stream);                                                  \
   }
-  if (mt == 1) { if (nw == 2) GO(1, 2); GO(1, 1); }
+  if (mt == 1) { if (nw == 3) GO(1, 3); if (nw == 2) GO(1, 2); GO(1, 1); }
   if (mt == 2) { if (nw == 4) GO(2, 4); GO(2, 1); }
   if (nw == 4) GO(4, 4);
   if (nw == 2) GO(4, 2);
