@@ -32,6 +32,10 @@ from ..sampling import LogitsProcessors
 from .step import StepContext, StepEntry, Workspace
 
 
+class StaleSource(RuntimeError):
+    """The step named as the source of tokens is no longer what its graph's output buffer holds."""
+
+
 @dataclass
 class PendingStep:
     """A launched decode step whose tokens have not been read yet."""
@@ -67,25 +71,16 @@ class DecodeGraph:
             self.off[name] = total
             total += pad(n)
         self.total = total
-        self.hosts = [torch.zeros(total, dtype=torch.int32).pin_memory() for _ in range(2)]
+        self.hosts = []          # pinned staging buffers, one per step that may be in flight (see _staging)
         self.dev = torch.zeros(total, dtype=torch.int32, device=dev)
         self.out = torch.zeros(2 * B + 1, dtype=torch.int32, device=dev)  # tokens | log-probability bits | status word
         self.sample_scratch = ops.sample_scratch(B, dev)
-        self.out_hosts = [torch.zeros(2 * B + 1, dtype=torch.int32).pin_memory() for _ in range(2)]
-        self.pending: List[Optional[PendingStep]] = [None, None]     # the last step launched from each staging buffer
+        self.out_hosts, self.events = [], []
+        self.pending: List[Optional[PendingStep]] = []     # the last step launched from each staging buffer
+        self.last: Optional[PendingStep] = None            # the step launched last: what ``out`` holds (or will)
         self.n_launched = 0
-        self.events = [torch.cuda.Event(), torch.cuda.Event()]
-        for host in self.hosts:
-            h = host.numpy()
-            h[self.off["logit_rows"]: self.off["logit_rows"] + B] = np.arange(B)
-            h[self.off["req_first_token"]: self.off["req_first_token"] + B + 1] = np.arange(B + 1)
-            h[self.off["token_req"]: self.off["token_req"] + B] = -1
-            h[self.off["source_rows"]: self.off["source_rows"] + B] = -1
-            tiles = h[self.off["single_tiles"]: self.off["single_tiles"] + 4 * B].reshape(B, 4)
-            tiles[:] = 0
-            tiles[:, 0] = np.arange(B)          # (token row, 0 queries, ...): a padding row until a request takes it
-            for g in range(len(mgr.kv_groups)):
-                h[self.off[f"table{g}"]: self.off[f"table{g}"] + B * W] = -1
+        self._staging()
+        self._staging()
 
         view = lambda name, n: self.dev[self.off[name]: self.off[name] + n]
         ctx = StepContext(engine)
@@ -116,6 +111,26 @@ class DecodeGraph:
         torch.cuda.current_stream(dev).wait_stream(side)
         self.n_kernels = self._count
 
+    def _staging(self) -> int:
+        """One more pair of pinned staging buffers (integers in, tokens out) with its event; its index."""
+        B, W, mgr = self.B, self.engine.cache.table_width, self.engine.cache
+        host = torch.zeros(self.total, dtype=torch.int32).pin_memory()
+        h = host.numpy()
+        h[self.off["logit_rows"]: self.off["logit_rows"] + B] = np.arange(B)
+        h[self.off["req_first_token"]: self.off["req_first_token"] + B + 1] = np.arange(B + 1)
+        h[self.off["token_req"]: self.off["token_req"] + B] = -1
+        h[self.off["source_rows"]: self.off["source_rows"] + B] = -1
+        tiles = h[self.off["single_tiles"]: self.off["single_tiles"] + 4 * B].reshape(B, 4)
+        tiles[:] = 0
+        tiles[:, 0] = np.arange(B)          # (token row, 0 queries, ...): a padding row until a request takes it
+        for g in range(len(mgr.kv_groups)):
+            h[self.off[f"table{g}"]: self.off[f"table{g}"] + B * W] = -1
+        self.hosts.append(host)
+        self.out_hosts.append(torch.zeros(2 * B + 1, dtype=torch.int32).pin_memory())
+        self.events.append(torch.cuda.Event())
+        self.pending.append(None)
+        return len(self.hosts) - 1
+
     def _launch(self) -> None:
         ctx = self.ctx
         ctx.stream = ops.current_stream()
@@ -135,12 +150,17 @@ class DecodeGraph:
         eng, mgr, B = self.engine, self.engine.cache, self.B
         eng._validate(entries)
         n = len(entries)
-        slot = self.n_launched & 1
-        if self.pending[slot] is not None and not self.pending[slot].collected:
-            # its caller went away without reading it (a generator closed early): wait, so that the staging
-            # buffers are free, and forget it
-            self.pending[slot].event.synchronize()
-            self.pending[slot].collected = True
+        if source is not None and source[0].graph.last is not source[0]:
+            # another caller's step went through that graph since: its output is no longer the source's
+            raise StaleSource("the step to take the tokens from is not the last one launched on its graph")
+        # a staging buffer whose last step has been read (two alternate for one caller; a second caller with a
+        # step of its own in flight gets a third)
+        slot = next((i for i, p in enumerate(self.pending) if p is None or p.collected), -1)
+        if slot < 0:
+            slot = self._staging() if len(self.hosts) < 8 else 0
+            if self.pending[slot] is not None and not self.pending[slot].collected:
+                self.pending[slot].event.synchronize()      # eight steps nobody has read: their callers are gone
+                self.pending[slot].collected = True
         h, off, W = self.hosts[slot].numpy(), self.off, mgr.table_width
         h[off["token_req"] + n: off["token_req"] + B] = -1
         h[off["source_rows"]: off["source_rows"] + B] = -1
@@ -191,7 +211,7 @@ class DecodeGraph:
             mgr.commit(e.rid)
         eng.n_steps += 1
         self.n_launched += 1
-        step = self.pending[slot] = PendingStep(self, slot, n, event)
+        step = self.pending[slot] = self.last = PendingStep(self, slot, n, event)
         return step
 
     def collect(self, step: PendingStep) -> Tuple[List[int], List[float]]:

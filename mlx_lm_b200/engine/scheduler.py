@@ -360,7 +360,10 @@ class Scheduler:
                 return None
             taken = [t + c for t, c in zip(taken, need)]
         entries = [StepEntry(r.rid, [0], [0]) for r in goes_on]     # the tokens are on the device
-        ahead = self.engine.decode_launch(entries, goes_on, self.sample, source=(handle, rows))
+        try:
+            ahead = self.engine.decode_launch(entries, goes_on, self.sample, source=(handle, rows))
+        except OutOfPages:       # (the check above should have seen it) nothing was booked: decide with the tokens in hand
+            return None
         if ahead is None:
             return None
         return ahead, [PlannedEntry(r, 1, True) for r in goes_on]

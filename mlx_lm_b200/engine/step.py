@@ -451,7 +451,7 @@ class Engine:
         need more than the sampling kernel).  ``source = (handle, rows)``: the entries' tokens are rows ``rows`` of
         what the step behind ``handle`` samples (still on its way), see ``DecodeGraph.launch``.  At most two steps
         are in flight; they are collected in the order they were launched."""
-        from .decode_graph import DecodeGraph
+        from .decode_graph import DecodeGraph, StaleSource
 
         n = len(entries)
         ok = (self.use_graphs and n <= self.GRAPH_BUCKETS[-1] and all(len(e.tokens) == 1 for e in entries)
@@ -463,7 +463,10 @@ class Engine:
         graph = self._graphs.get((bucket, filters))
         if graph is None:
             graph = self._graphs[(bucket, filters)] = DecodeGraph(self, bucket, filters)
-        return graph.launch(entries, requests, sampler.seed, source)
+        try:
+            return graph.launch(entries, requests, sampler.seed, source)
+        except StaleSource:
+            return None      # somebody else's step went through that graph meanwhile: the caller reads its tokens first
 
     def decode_collect(self, step):
         """Wait for a step launched by ``decode_launch``: ``(tokens, logprobs)`` as lists."""

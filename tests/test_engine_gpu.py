@@ -538,6 +538,47 @@ def test_temperature_sampling_does_not_depend_on_batching(tmp_path):
     assert all(len(t) == 24 for t in together) and len({tuple(t) for t in together}) == 3
 
 
+def test_two_generators_taking_turns_on_one_engine(tmp_path):
+    """Two generators on the engine of one model, each with decode steps launched ahead of their tokens, called in
+    turns: the steps of one go through the same CUDA graph between a step of the other and the step after it, so the
+    tokens must come from the host then (the graph's output buffer holds the other's by that time).  Each gets the
+    tokens it gets alone."""
+    from mlx_lm_b200 import load
+    from mlx_lm_b200.generate import BatchGenerator, get_engine
+    from mlx_lm_b200.sampling import make_sampler
+    make_model_dir(str(tmp_path), dict(CONFIG_B, ln_gain_std=0.3), 5, peaky=6.0)
+    model, _ = load(str(tmp_path), dtype="bfloat16")
+    engine = get_engine(model, page_size=16, num_pages=96, max_requests=8)
+    jobs = [([random_tokens(n, 1000, 7 + n) for n in (9, 30)], 20, make_sampler(0.8)),
+            ([random_tokens(n, 1000, 90 + n) for n in (14, 5)], 26, make_sampler(0.0))]
+
+    def start(job):
+        prompts, max_tokens, sampler = job
+        gen = BatchGenerator(model, engine=engine, sampler=sampler, seed=11, max_tokens=max_tokens,
+                             completion_batch_size=4, prefill_batch_size=4)
+        return gen, gen.insert(prompts), {}
+
+    def drain(gen, out, steps):
+        for _ in range(steps):
+            if not gen.scheduler.has_work():
+                return
+            for r in gen.next_generated():
+                out.setdefault(r.uid, []).append(r.token)
+
+    alone = []
+    for job in jobs:
+        gen, uids, out = start(job)
+        drain(gen, out, 10 ** 6)
+        alone.append([out[u] for u in uids])
+    a, b = start(jobs[0]), start(jobs[1])
+    while a[0].scheduler.has_work() or b[0].scheduler.has_work():
+        drain(a[0], a[2], 1)
+        drain(b[0], b[2], 2)
+    assert [a[2][u] for u in a[1]] == alone[0] and [b[2][u] for u in b[1]] == alone[1]
+    assert engine.cache.pages_in_use() == [0]
+    engine.check_status()
+
+
 def test_scheduler_preempts_and_recomputes_on_the_gpu(tmp_path):
     """A pool too small for all requests at once: some are preempted and recomputed, and every
     request still gets the tokens it gets when it runs alone."""
