@@ -9,7 +9,9 @@ bfloat16 weights, a batch of 8 requests with 512-token prompts and a context of 
 prompts are in the cache, W untimed and K timed decode steps follow.  One JSON line is printed:
 
   value      decoded tokens per second, timed on the device (CUDA events around the K steps): the median of
-             five trials of K steps, each on fresh requests (`trials_ms` lists them)
+             five trials of K steps, each on fresh requests (`trials_ms` lists them).  The steps run as the
+             scheduler runs them: each is a CUDA graph (model and sampler), launched one ahead of the tokens (the
+             next step takes them on the device from the step in flight, the host reads them one step behind)
   e2e        the same through the Python entry point (BatchGenerator): host token ids in, host
              token ids out, every step's inputs copied from pinned host memory and its tokens read back
              (bytes counted at the copies); median of three trials
