@@ -38,8 +38,10 @@ class StaleSource(RuntimeError):
 
 @dataclass
 class PendingStep:
-    """A launched decode step whose tokens have not been read yet."""
-    graph: "DecodeGraph"
+    """A launched decode step whose tokens have not been read yet.  It names its graph by the engine's key, not by
+    reference: graph and step would keep one another alive until the cycle collector runs, and a CUDA graph must
+    not be destroyed at a moment of the collector's choosing (while another one is being captured, for one)."""
+    key: tuple                 # (bucket, filters) of its graph in Engine._graphs
     slot: int                  # which staging buffer its results arrive in
     n: int                     # live rows
     event: object
@@ -106,8 +108,18 @@ class DecodeGraph:
             self._launch()
         side.synchronize()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph, stream=side):
-            self._launch()
+        # Nothing may be destroyed by the cycle collector while the capture runs (a CUDA graph or a pinned buffer of
+        # an engine that is gone would invalidate it): torch collects before the capture begins, and the collector
+        # rests until it has ended.
+        import gc
+        was_enabled = gc.isenabled()
+        gc.disable()
+        try:
+            with torch.cuda.graph(self.graph, stream=side):
+                self._launch()
+        finally:
+            if was_enabled:
+                gc.enable()
         torch.cuda.current_stream(dev).wait_stream(side)
         self.n_kernels = self._count
 
@@ -150,7 +162,8 @@ class DecodeGraph:
         eng, mgr, B = self.engine, self.engine.cache, self.B
         eng._validate(entries)
         n = len(entries)
-        if source is not None and source[0].graph.last is not source[0]:
+        source_graph = eng._graphs.get(source[0].key) if source is not None else None
+        if source is not None and (source_graph is None or source_graph.last is not source[0]):
             # another caller's step went through that graph since: its output is no longer the source's
             raise StaleSource("the step to take the tokens from is not the last one launched on its graph")
         # a staging buffer whose last step has been read (two alternate for one caller; a second caller with a
@@ -191,7 +204,7 @@ class DecodeGraph:
                 h[o + n * W: o + B * W] = -1
             self.dev.copy_(self.hosts[slot], non_blocking=True)
             if source is not None:
-                src = source[0].graph.out[:source[0].graph.B]
+                src = source_graph.out[:source_graph.B]
                 ops.gather_tokens(src, self.dev[off["source_rows"]: off["source_rows"] + n],
                                   self.dev[off["tokens"]: off["tokens"] + n], eng.status, ops.current_stream())
             self.graph.replay()
@@ -211,7 +224,7 @@ class DecodeGraph:
             mgr.commit(e.rid)
         eng.n_steps += 1
         self.n_launched += 1
-        step = self.pending[slot] = self.last = PendingStep(self, slot, n, event)
+        step = self.pending[slot] = self.last = PendingStep((self.B, self.filters), slot, n, event)
         return step
 
     def collect(self, step: PendingStep) -> Tuple[List[int], List[float]]:

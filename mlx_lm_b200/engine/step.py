@@ -470,7 +470,7 @@ class Engine:
 
     def decode_collect(self, step):
         """Wait for a step launched by ``decode_launch``: ``(tokens, logprobs)`` as lists."""
-        return step.graph.collect(step)
+        return self._graphs[step.key].collect(step)
 
     def read_status(self) -> int:
         """Bits kernels set instead of faulting (token, position or page id out of range, a bounded wait that
