@@ -579,14 +579,17 @@ def test_two_generators_taking_turns_on_one_engine(tmp_path):
     engine.check_status()
 
 
-def test_scheduler_preempts_and_recomputes_on_the_gpu(tmp_path):
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_scheduler_preempts_and_recomputes_on_the_gpu(dtype, tmp_path):
     """A pool too small for all requests at once: some are preempted and recomputed, and every
-    request still gets the tokens it gets when it runs alone."""
+    request still gets the tokens it gets when it runs alone (in bfloat16: up to a choice between two logits
+    that the plain model has closer together than bfloat16 resolves).  The decode graphs are left and entered
+    again at other batch sizes on the way, with a step launched ahead whenever nobody waits."""
     from mlx_lm_b200 import load
     from mlx_lm_b200.generate import BatchGenerator, get_engine
     config = dict(CONFIG_A, ln_gain_std=0.3)
     weights = make_model_dir(str(tmp_path), config, 6, peaky=10.0)
-    model, _ = load(str(tmp_path), dtype="float32")
+    model, _ = load(str(tmp_path), dtype=dtype)
     prompts = [random_tokens(30, 512, 10 + i) for i in range(3)]
     want = [plain.greedy_generate(p, 20, weights, config) for p in prompts]
     engine = get_engine(model, page_size=16, num_pages=6, max_requests=4)
@@ -597,8 +600,17 @@ def test_scheduler_preempts_and_recomputes_on_the_gpu(tmp_path):
         for r in gen.next_generated():
             out[r.uid].append(r.token)
     assert gen.scheduler.stats.preemptions > 0
-    assert [out[u] for u in uids] == want
+    for u, w, p in zip(uids, want, prompts):
+        got = out[u]
+        assert len(got) == len(w)
+        for i, (a, b) in enumerate(zip(got, w)):
+            if a != b:
+                lg = plain.logits(p + w[:i], weights, config)[-1]
+                top = torch.topk(lg, 2).values
+                assert dtype == "bfloat16" and float(top[0] - top[1]) < 0.05 * float(lg.abs().max()), (got, w)
+                break
     assert engine.cache.pages_in_use() == [0]
+    engine.check_status()
 
 
 # ----------------------------------------------------------------------------------------------
