@@ -12,7 +12,7 @@ import torch
 
 import kernel_refs as R
 import plain_gpt2 as plain
-from helpers import CONFIG_A, CONFIG_B, make_model_dir, random_tokens
+from helpers import CONFIG_A, CONFIG_B, CONFIG_C, make_model_dir, random_tokens
 
 pytestmark = pytest.mark.gpu
 
@@ -214,6 +214,102 @@ def test_a_wrong_page_is_seen(dtype, tmp_path):
     assert worst > 1.5 * TOL[dtype], f"a wrong page moved the logits by only {worst}"     # measured: 2.5e-2
     eng.check_status()                                  # every id is a page of the pool: no kernel can tell
     pages[0] = first
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("config", [CONFIG_A, CONFIG_C], ids=["heads of 16", "heads of 64"])
+def test_pages_nobody_was_given_keep_their_canaries(dtype, config, tmp_path):
+    """Every page of the pools is filled with a canary (NaN) before the first step; pages that are handed out are
+    then cleared by the test, as the manager's zero-filled pool would have them.  Requests come and go through
+    portions, single tokens, mixed steps and decode graphs, with pages given back and used again.  At the end
+    the pages that were never handed out still hold the canary bit for bit (no kernel wrote outside its block
+    table), and every logit along the way is finite and right (no kernel read outside it: a NaN would have
+    spread, masked or not)."""
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.sampling import GREEDY
+    from mlx_lm_b200.sampling.device import DeviceSampler
+    from mlx_lm_b200.weights import load_model
+    weights = make_model_dir(str(tmp_path), config, 9)
+    model, _ = load_model(str(tmp_path), dtype=dtype)
+    eng = Engine(model, page_size=16, n_pages=40, max_requests=4)
+    group = eng.cache.kv_groups[0]
+    for pool in (group.k, group.v):
+        pool.fill_(float("nan"))
+    cleared = set()
+
+    def clear_new_pages():
+        for req in eng.cache.requests.values():
+            for pg in req.pages[0]:
+                if pg not in cleared:
+                    cleared.add(pg)
+                    group.k[:, pg].zero_()
+                    group.v[:, pg].zero_()
+
+    class Req:
+        def __init__(self, uid, tokens):
+            self.uid, self.tokens, self.sampler, self.processors = uid, list(tokens), GREEDY, ()
+
+    def step(entries):
+        # pages a step will take are handed out inside it: reserve by hand first, so that they can be cleared
+        for e in entries:
+            eng.cache.reserve(e.rid, len(e.tokens))
+        clear_new_pages()
+        for e in entries:
+            eng.cache.rollback(e.rid)
+        return eng.step(entries)
+
+    V = config["vocab_size"]
+    seqs = {r: random_tokens(n, V, 40 + i) for i, (r, n) in enumerate([("a", 128), ("b", 37), ("c", 70), ("d", 33)])}
+    refs = {r: plain.logits(t, weights, config) for r, t in seqs.items()}
+    done = {r: 0 for r in seqs}
+
+    def entry(r, n, want="last"):
+        toks = seqs[r][done[r]:done[r] + n]
+        done[r] += len(toks)
+        return StepEntry(r, toks, [len(toks) - 1] if want == "last" else list(range(len(toks))))
+
+    def check(entries, logits):
+        assert bool(torch.isfinite(logits).all())
+        row = 0
+        for e in entries:
+            end = done[e.rid]
+            for w in e.want:
+                assert rel(logits[row], refs[e.rid][end - len(e.tokens) + w]) <= TOL[dtype]
+                row += 1
+
+    for r in ("a", "b"):
+        eng.add_request(r)
+    es = [entry("a", 100), entry("b", 30, "all")]
+    check(es, step(es))
+    eng.add_request("c")
+    es = [entry("a", 1), entry("b", 7, "all"), entry("c", 40)]      # mixed: a decodes, b ends, c starts
+    check(es, step(es))
+    eng.finish("b")                                                  # its pages go back ...
+    eng.add_request("d")
+    es = [entry("d", 33, "all"), entry("a", 2), entry("c", 30)]      # ... and d takes them
+    check(es, step(es))
+    eng.finish("d")
+    eng.finish("c")
+    sampler = DeviceSampler(model.device, seed=0, engine=eng)
+    req = Req(0, seqs["a"][:done["a"]])                               # (the uid only keys the random draws)
+    for _ in range(20):                                              # decode graphs (the tokens are the sequence's own)
+        e = StepEntry("a", [seqs["a"][done["a"]]], [0])
+        eng.cache.reserve("a", 1)
+        clear_new_pages()
+        eng.cache.rollback("a")
+        eng.decode_sampled([e], [req], sampler)
+        done["a"] += 1
+        req.tokens.append(seqs["a"][done["a"] - 1])
+    es = [entry("a", 5, "all")]
+    check(es, step(es))
+    eng.finish("a")
+    eng.check_status()
+    used = eng.cache.kv_groups[0].pool.high_water
+    assert used < 40 and cleared == set(range(used))               # page ids are handed out from 0 up, freed ones first
+    for pool in (group.k, group.v):
+        rest = pool[:, used:]
+        assert bool(torch.isnan(rest).all()), "a page that no request was given has been written"
+    assert eng.cache.pages_in_use() == [0]
 
 
 def test_status_bits_become_errors_and_are_cleared(tmp_path):
