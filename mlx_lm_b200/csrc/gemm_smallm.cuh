@@ -76,8 +76,11 @@ struct NormFold {
 // allocator: without it the compiler keeps these kernels at 76 registers for the sake of occupancy; with it they
 // get 116 and run a decode step of 124 kernels 2-7 % faster (fewer, faster CTAs per SM, and room beside them for
 // the CTAs of the next kernel, which fetch their weights while they wait).
+// Except where the output is float32 at up to 16 rows: that is a vocabulary-sized output head, thousands of
+// short-lived CTAs in ten waves and more, where a third CTA per SM (80 registers) counts for more than a faster
+// CTA: 24.6 against 26.6 microseconds (four CTAs, 64 registers: 28.7).
 template <int MT, int NW, int WARPS, typename TO, int EPI, bool SCATTER, bool FOLD>
-__global__ void __launch_bounds__(WARPS * 32, 1)
+__global__ void __launch_bounds__(WARPS * 32, (sizeof(TO) == 4 && MT == 1 && WARPS == 8) ? 3 : 1)
 gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
                    const float* __restrict__ bias, const __nv_bfloat16* residual, TO* C, int M, int N, int K,
                    int lda, int ldc, KvScatter kv, NormFold fold) {
