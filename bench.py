@@ -366,6 +366,9 @@ def kernel_table(calls, pk, mode, attention_bytes=0.0, attention_flops=0.0, reps
         if kind.endswith("attention"):
             flops, nbytes = attention_flops, attention_bytes
         rec = {"n": len(group), "us": round(us, 2)}
+        if us <= 0.0:          # lost in the noise of the launches it was timed behind (a model of very few layers)
+            out[kind] = rec
+            continue
         if nbytes:
             rec["gbs"] = round(nbytes / us / 1e3, 1)
         if flops:
