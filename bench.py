@@ -386,7 +386,7 @@ def decode_kernels(engine, batch, mean_ctx, cfg, pk):
     import torch
 
     from mlx_lm_b200 import ops
-    graph = engine._graphs[(batch, False)]
+    graph = engine._graphs[(next(b for b in engine.GRAPH_BUCKETS if b >= batch), False)]
     side = torch.cuda.Stream()
     side.wait_stream(torch.cuda.current_stream())
     with torch.cuda.stream(side):
