@@ -397,14 +397,24 @@ sample_split_kernel(const float* __restrict__ logits, int ld, int V, const Sampl
   }
   if (tid == 0) {
     const float* recs = partials + (size_t)row * SAMPLE_SLICES * SAMPLE_SLICE_WORDS;
+    float rm[SAMPLE_SLICES], rs[SAMPLE_SLICES], rg[SAMPLE_SLICES];
+    int ri[SAMPLE_SLICES], rgi[SAMPLE_SLICES];
+#pragma unroll
+    for (int k = 0; k < SAMPLE_SLICES; ++k) {      // all loads first: they do not depend on one another
+      const float* rk = recs + k * SAMPLE_SLICE_WORDS;
+      rm[k] = __ldcg(rk);
+      ri[k] = __float_as_int(__ldcg(rk + 1));
+      rs[k] = __ldcg(rk + 2);
+      rg[k] = __ldcg(rk + 3);
+      rgi[k] = __float_as_int(__ldcg(rk + 4));
+    }
     SoftmaxPart all = {-INFINITY, 0x7fffffff, 0.f};
     float bg = -INFINITY;
     int bgi = 0x7fffffff;
+#pragma unroll
     for (int k = 0; k < SAMPLE_SLICES; ++k) {      // slices in index order: the first of equals wins
-      const float* rk = recs + k * SAMPLE_SLICE_WORDS;
-      all = merge(all, SoftmaxPart{__ldcg(rk), __float_as_int(__ldcg(rk + 1)), __ldcg(rk + 2)});
-      const float gk = __ldcg(rk + 3);
-      if (gk > bg) { bg = gk; bgi = __float_as_int(__ldcg(rk + 4)); }
+      all = merge(all, SoftmaxPart{rm[k], ri[k], rs[k]});
+      if (rg[k] > bg) { bg = rg[k]; bgi = rgi[k]; }
     }
     const float lse = all.m + logf(all.s);
     const int tok = (draws && bgi != 0x7fffffff) ? bgi : all.idx;
